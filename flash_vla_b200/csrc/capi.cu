@@ -1,0 +1,320 @@
+// extern "C" surface of libfvla_b200: argument validation, kernel selection, launches.
+// Nothing here allocates, frees or synchronises.
+#include <cstdarg>
+#include <cstdio>
+
+#include "attention.cuh"
+#include "common.cuh"
+#include "gemm_mma.cuh"
+#include "rowops.cuh"
+
+namespace fvla {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("%s: %s", what, cudaGetErrorString(e));
+        return FVLA_ERR_LAUNCH;
+    }
+    return FVLA_OK;
+}
+
+static inline size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+static inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+static inline const bf16* B(const void* p) { return reinterpret_cast<const bf16*>(p); }
+static inline bf16* Bm(void* p) { return reinterpret_cast<bf16*>(p); }
+
+#define FVLA_REQUIRE(cond, ...)            \
+    do {                                   \
+        if (!(cond)) {                     \
+            set_error(__VA_ARGS__);        \
+            return FVLA_ERR_ARG;           \
+        }                                  \
+    } while (0)
+
+static int rownorm(const void* x, int x_is_f32, const void* w, const void* b, void* out, float* f32,
+                   void* fbf, int M, int K, int mode, cudaStream_t st) {
+    FVLA_REQUIRE(M > 0 && K > 0 && K % 2 == 0, "rownorm: bad shape M=%d K=%d", M, K);
+    if (x_is_f32)
+        rownorm_kernel<float><<<(M + 3) / 4, 128, 0, st>>>((const float*)x, B(w), B(b), Bm(out), f32, Bm(fbf), M, K, mode);
+    else
+        rownorm_kernel<bf16><<<(M + 3) / 4, 128, 0, st>>>(B(x), B(w), B(b), Bm(out), f32, Bm(fbf), M, K, mode);
+    return check_launch("rownorm_kernel");
+}
+
+// Workspace layout of the GEMM-shaped ops:
+//   [per-row fp32 factors | bf16 copy of the normalised rows (fp32 input only) | split-K scratch]
+static size_t ws_factor_bytes(int M) { return align256((size_t)M * sizeof(float)); }
+static size_t ws_xnorm_bytes(int M, int K) { return align256((size_t)M * K * sizeof(bf16)); }
+static size_t op_ws_bytes(int M, int N, int K, bool dual) {
+    return ws_factor_bytes(M) + ws_xnorm_bytes(M, K) + plan_gemm_mma(M, N, K, dual).ws_bytes;
+}
+// Split-K part of an op workspace as (pointer, size); (nullptr, 0) when the caller gave none.
+static void gemm_ws(void* ws, size_t ws_bytes, int M, int K, void** p, size_t* n) {
+    size_t off = ws_factor_bytes(M) + ws_xnorm_bytes(M, K);
+    bool has = ws != nullptr && ws_bytes >= off;
+    *p = has ? (uint8_t*)ws + off : nullptr;
+    *n = has ? ws_bytes - off : 0;
+}
+
+}  // namespace fvla
+
+using namespace fvla;
+
+extern "C" {
+
+const char* fvla_last_error(void) { return g_error; }
+int fvla_abi_version(void) { return 1; }
+
+size_t fvla_gemm_workspace_bytes(int M, int N, int K, int dual) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    return op_ws_bytes(M, N, K, dual != 0);
+}
+
+size_t fvla_decoder_attention_workspace_bytes(int queries, int keys) {
+    if (queries <= 0 || keys <= 0) return 0;
+    int splits = (keys + 127) / 128;
+    size_t qpad = (size_t)(queries + 63) / 64 * 64;
+    return align256(splits * qpad * sizeof(float)) + splits * qpad * 256 * sizeof(float);
+}
+
+size_t fvla_patch_embed_workspace_bytes(int views) {
+    return views > 0 ? (size_t)views * 256 * 592 * sizeof(bf16) : 0;
+}
+
+int fvla_vision_patch_embed(const void* images, const void* patch_w, const void* patch_b,
+                            const void* pos_emb, void* out, int views, void* ws, size_t ws_bytes,
+                            void* stream) {
+    FVLA_REQUIRE(views > 0, "patch_embed: views=%d", views);
+    if (ws == nullptr || ws_bytes < fvla_patch_embed_workspace_bytes(views)) {
+        set_error("patch_embed: workspace of %zu bytes needed", fvla_patch_embed_workspace_bytes(views));
+        return FVLA_ERR_WORKSPACE;
+    }
+    const int M = views * 256;
+    patchify_kernel<<<M, 256, 0, S(stream)>>>(B(images), Bm(ws), views, 592);
+    int rc = check_launch("patchify_kernel");
+    if (rc) return rc;
+    GemmArgs a;
+    a.A = B(ws); a.lda = 592; a.B = B(patch_w); a.ldb = 1152; a.C = out; a.ldc = 1152;
+    a.bias = B(patch_b); a.R = pos_emb; a.ldr = 1152; a.res_mod = 256;
+    a.M = M; a.N = 1152; a.K = 592; a.Kb = 588;
+    return launch_gemm_mma(a, nullptr, 0, S(stream));
+}
+
+static int norm_linear(const void* x, const void* nw, const void* nb, const void* w, const void* b,
+                       void* out, void* x_norm, int M, int N, int K, int act, void* stream) {
+    int rc = rownorm(x, 0, nw, nb, x_norm, nullptr, nullptr, M, K, 0, S(stream));
+    if (rc) return rc;
+    GemmArgs a;
+    a.A = B(x_norm); a.lda = K; a.B = B(w); a.ldb = N; a.C = out; a.ldc = N; a.bias = B(b);
+    a.act = act; a.M = M; a.N = N; a.K = K;
+    return launch_gemm_mma(a, nullptr, 0, S(stream));
+}
+
+int fvla_vision_norm_qkv(const void* x, const void* norm_w, const void* norm_b, const void* qkv_w,
+                         const void* qkv_b, void* out, void* x_norm, int M, int N, int K, void* stream) {
+    return norm_linear(x, norm_w, norm_b, qkv_w, qkv_b, out, x_norm, M, N, K, 0, stream);
+}
+
+int fvla_vision_norm_ffn_up(const void* x, const void* norm_w, const void* norm_b, const void* weight,
+                            const void* bias, void* out, void* x_norm, int M, int N, int K, void* stream) {
+    return norm_linear(x, norm_w, norm_b, weight, bias, out, x_norm, M, N, K, 1, stream);
+}
+
+int fvla_encoder_projector(const void* x, const void* norm_w, const void* norm_b, const void* proj_w,
+                           const void* proj_b, void* out, void* x_norm, int M, int N, int K, void* stream) {
+    return norm_linear(x, norm_w, norm_b, proj_w, proj_b, out, x_norm, M, N, K, 0, stream);
+}
+
+int fvla_vision_attention(const void* qkv, void* out, int views, int tokens, int heads, int head_dim,
+                          void* stream) {
+    FVLA_REQUIRE(views > 0 && tokens > 0 && heads > 0, "vision_attention: bad shape");
+    if (head_dim != 72) { set_error("vision_attention: head_dim %d not built (72 only)", head_dim); return FVLA_ERR_UNSUPPORTED; }
+    const int width = heads * head_dim;
+    AttnArgs a{};
+    a.q = B(qkv); a.k = B(qkv) + width; a.v = B(qkv) + 2 * width; a.out = Bm(out);
+    a.q_stride = a.k_stride = a.v_stride = 3 * width; a.o_stride = width;
+    a.q_bs0 = a.k_bs0 = a.v_bs0 = (long long)tokens * 3 * width; a.q_bs1 = a.k_bs1 = a.v_bs1 = head_dim;
+    a.o_bs0 = (long long)tokens * width; a.o_bs1 = head_dim;
+    a.batch_inner = heads; a.nq = tokens; a.nk = tokens; a.hd = head_dim; a.nq_pad = tokens;
+    a.scale_log2 = kLog2e / sqrtf((float)head_dim);
+    a.mask_rows = 0; a.mask_key_le = 0; a.splits = 1; a.keys_per_split = tokens;
+    return launch_attention<80>(a, dim3((tokens + 63) / 64, views * heads, 1), S(stream));
+}
+
+int fvla_vision_linear_bias_residual(const void* x, const void* weight, const void* bias, const void* res,
+                                     void* out, int M, int N, int K, void* stream) {
+    GemmArgs a;
+    a.A = B(x); a.lda = K; a.B = B(weight); a.ldb = N; a.C = out; a.ldc = N; a.bias = B(bias);
+    a.R = res; a.ldr = N; a.M = M; a.N = N; a.K = K;
+    return launch_gemm_mma(a, nullptr, 0, S(stream));
+}
+
+int fvla_encoder_norm_qkv_rope(const void* x, const void* weight_qkv, const void* rope, void* Q, void* K,
+                               void* V, void* x_norm, int M, int Kdim, int heads, int head_dim, void* stream) {
+    FVLA_REQUIRE(M > 64, "encoder_norm_qkv_rope: M=%d must exceed 64 (no split-K scratch is taken)", M);
+    int rc = rownorm(x, 0, nullptr, nullptr, x_norm, nullptr, nullptr, M, Kdim, 1, S(stream));
+    if (rc) return rc;
+    GemmArgs a;
+    a.A = B(x_norm); a.lda = Kdim; a.B = B(weight_qkv); a.ldb = (heads + 2) * head_dim;
+    a.M = M; a.N = (heads + 2) * head_dim; a.K = Kdim;
+    a.rope = B(rope); a.q = Bm(Q); a.k = Bm(K); a.v = Bm(V); a.heads = heads; a.head_dim = head_dim;
+    a.round_first = 1;
+    return launch_gemm_mma(a, nullptr, 0, S(stream));
+}
+
+int fvla_encoder_attention(const void* Q, const void* K, const void* V, void* out, int queries, int keys,
+                           int head_dim, float scale, void* stream) {
+    FVLA_REQUIRE(queries > 0 && keys > 0, "encoder_attention: bad shape");
+    if (head_dim != 256) { set_error("encoder_attention: head_dim %d not built (256 only)", head_dim); return FVLA_ERR_UNSUPPORTED; }
+    AttnArgs a{};
+    a.q = B(Q); a.k = B(K); a.v = B(V); a.out = Bm(out);
+    a.q_stride = a.k_stride = a.v_stride = a.o_stride = head_dim;
+    a.batch_inner = 1; a.nq = queries; a.nk = keys; a.hd = head_dim; a.nq_pad = queries;
+    a.scale_log2 = scale * kLog2e; a.splits = 1; a.keys_per_split = keys;
+    return launch_attention<256>(a, dim3((queries + 63) / 64, 1, 1), S(stream));
+}
+
+int fvla_linear_residual(const void* x, const void* weight, void* out, int out_is_f32, int M, int N, int K,
+                         void* ws, size_t ws_bytes, void* stream) {
+    GemmArgs a;
+    a.A = B(x); a.lda = K; a.B = B(weight); a.ldb = N; a.C = out; a.ldc = N; a.c_f32 = out_is_f32;
+    a.R = out; a.ldr = N; a.M = M; a.N = N; a.K = K;
+    void* gws; size_t gn;
+    gemm_ws(ws, ws_bytes, M, K, &gws, &gn);
+    return launch_gemm_mma(a, gws, gn, S(stream));
+}
+
+int fvla_encoder_norm_gated_ffn(const void* x, const void* gate_w, const void* up_w, void* out, void* x_norm,
+                                int M, int N, int K, void* stream) {
+    FVLA_REQUIRE(M > 64, "encoder_norm_gated_ffn: M=%d must exceed 64 (no split-K scratch is taken)", M);
+    int rc = rownorm(x, 0, nullptr, nullptr, x_norm, nullptr, nullptr, M, K, 1, S(stream));
+    if (rc) return rc;
+    GemmArgs a;
+    a.A = B(x_norm); a.lda = K; a.B = B(gate_w); a.B2 = B(up_w); a.ldb = N; a.C = out; a.ldc = N;
+    a.M = M; a.N = N; a.K = K;
+    return launch_gemm_mma(a, nullptr, 0, S(stream));
+}
+
+int fvla_decoder_small_proj(const void* x, int x_is_f32, const void* weight, const void* bias, void* out,
+                            int out_is_f32, int M, int N, int K, int act, void* ws, size_t ws_bytes,
+                            void* stream) {
+    FVLA_REQUIRE(M > 0 && N > 0 && K > 0 && (act == 0 || act == 2), "small_proj: bad arguments");
+    if (K <= 64) {
+        dim3 grid((N + 255) / 256, M);
+        cudaStream_t st = S(stream);
+        if (x_is_f32 && out_is_f32)
+            small_k_proj_kernel<float, float><<<grid, 256, 0, st>>>((const float*)x, B(weight), B(bias), (float*)out, M, N, K, act);
+        else if (x_is_f32)
+            small_k_proj_kernel<float, bf16><<<grid, 256, 0, st>>>((const float*)x, B(weight), B(bias), Bm(out), M, N, K, act);
+        else if (out_is_f32)
+            small_k_proj_kernel<bf16, float><<<grid, 256, 0, st>>>(B(x), B(weight), B(bias), (float*)out, M, N, K, act);
+        else
+            small_k_proj_kernel<bf16, bf16><<<grid, 256, 0, st>>>(B(x), B(weight), B(bias), Bm(out), M, N, K, act);
+        return check_launch("small_k_proj_kernel");
+    }
+    FVLA_REQUIRE(!x_is_f32, "small_proj: fp32 input only for K <= 64");
+    GemmArgs a;
+    a.A = B(x); a.lda = K; a.B = B(weight); a.ldb = N; a.C = out; a.ldc = N; a.c_f32 = out_is_f32;
+    a.bias = B(bias); a.act = act; a.M = M; a.N = N; a.K = K;
+    void* gws; size_t gn;
+    gemm_ws(ws, ws_bytes, M, K, &gws, &gn);
+    return launch_gemm_mma(a, gws, gn, S(stream));
+}
+
+// Shared front half of the two decoder norm+GEMM ops: factor (and, for an fp32 residual stream,
+// the bf16 normalised rows) into the workspace; fills A / row_scale of the GEMM accordingly.
+static int decoder_norm_front(const void* x, int x_is_f32, void* norm_factor, int M, int N, int K, bool dual,
+                              void* ws, size_t ws_bytes, const char* who, GemmArgs* a, void* stream) {
+    if (ws == nullptr || ws_bytes < op_ws_bytes(M, N, K, dual)) {
+        set_error("%s: workspace of %zu bytes needed", who, op_ws_bytes(M, N, K, dual));
+        return FVLA_ERR_WORKSPACE;
+    }
+    float* factors = (float*)ws;
+    bf16* xnorm = (bf16*)((uint8_t*)ws + ws_factor_bytes(M));
+    int rc = rownorm(x, x_is_f32, nullptr, nullptr, x_is_f32 ? xnorm : nullptr, factors, norm_factor, M, K, 2, S(stream));
+    if (rc) return rc;
+    if (x_is_f32) { a->A = xnorm; a->row_scale = nullptr; }       // rows already scaled, then rounded once
+    else { a->A = B(x); a->row_scale = factors; }                 // bf16 rows: scale the fp32 accumulators
+    a->lda = K; a->M = M; a->N = N; a->K = K;
+    return FVLA_OK;
+}
+
+int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* weight_qkv, const void* rope, void* Q,
+                               void* K, void* V, void* norm_factor, int M, int Kdim, int heads, int head_dim,
+                               void* ws, size_t ws_bytes, void* stream) {
+    const int N = (heads + 2) * head_dim;
+    GemmArgs a;
+    int rc = decoder_norm_front(x, x_is_f32, norm_factor, M, N, Kdim, false, ws, ws_bytes, "decoder_norm_qkv_rope", &a, stream);
+    if (rc) return rc;
+    a.B = B(weight_qkv); a.ldb = N;
+    a.rope = B(rope); a.q = Bm(Q); a.k = Bm(K); a.v = Bm(V); a.heads = heads; a.head_dim = head_dim;
+    void* gws; size_t gn;
+    gemm_ws(ws, ws_bytes, M, Kdim, &gws, &gn);
+    return launch_gemm_mma(a, gws, gn, S(stream));
+}
+
+int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* out, int queries, int keys,
+                           int head_dim, int heads, int encoder_seq_len, void* ws, size_t ws_bytes,
+                           void* stream) {
+    FVLA_REQUIRE(queries > 0 && keys > 0, "decoder_attention: bad shape");
+    if (head_dim != 256) { set_error("decoder_attention: head_dim %d not built (256 only)", head_dim); return FVLA_ERR_UNSUPPORTED; }
+    if (ws == nullptr || ws_bytes < fvla_decoder_attention_workspace_bytes(queries, keys)) {
+        set_error("decoder_attention: workspace of %zu bytes needed", fvla_decoder_attention_workspace_bytes(queries, keys));
+        return FVLA_ERR_WORKSPACE;
+    }
+    const int splits = (keys + 127) / 128;
+    const int qpad = (queries + 63) / 64 * 64;
+    AttnArgs a{};
+    a.q = B(Q); a.k = B(K); a.v = B(V); a.out = nullptr;
+    a.part_lse = (float*)ws;
+    a.part_o = (float*)((uint8_t*)ws + align256((size_t)splits * qpad * sizeof(float)));
+    a.q_stride = a.k_stride = a.v_stride = a.o_stride = head_dim;
+    a.batch_inner = 1; a.nq = queries; a.nk = keys; a.hd = head_dim; a.nq_pad = qpad;
+    a.scale_log2 = kLog2e / sqrtf((float)head_dim);
+    a.mask_rows = heads; a.mask_key_le = encoder_seq_len;
+    a.splits = splits; a.keys_per_split = 128;
+    int rc = launch_attention<256>(a, dim3(qpad / 64, 1, splits), S(stream));
+    if (rc) return rc;
+    attention_combine_kernel<<<(queries + 1) / 2, 128, 0, S(stream)>>>(a.part_o, a.part_lse, Bm(out), queries, qpad, head_dim, splits);
+    return check_launch("attention_combine_kernel");
+}
+
+int fvla_decoder_norm_gated_ffn(const void* x, int x_is_f32, const void* gate_w, const void* up_w, void* out,
+                                void* norm_factor, int M, int N, int K, void* ws, size_t ws_bytes, void* stream) {
+    GemmArgs a;
+    int rc = decoder_norm_front(x, x_is_f32, norm_factor, M, N, K, true, ws, ws_bytes, "decoder_norm_gated_ffn", &a, stream);
+    if (rc) return rc;
+    a.B = B(gate_w); a.B2 = B(up_w); a.ldb = N; a.C = out; a.ldc = N;
+    void* gws; size_t gn;
+    gemm_ws(ws, ws_bytes, M, K, &gws, &gn);
+    return launch_gemm_mma(a, gws, gn, S(stream));
+}
+
+int fvla_decoder_action_out_proj(const void* x, int x_is_f32, const void* weight, const void* bias, void* out,
+                                 int out_is_f32, void* mirror, void* norm_factor, int M, int N, int K,
+                                 void* stream) {
+    FVLA_REQUIRE(M > 0 && K > 0, "action_out_proj: bad shape");
+    if (N != 32) { set_error("action_out_proj: N=%d not built (32 only)", N); return FVLA_ERR_UNSUPPORTED; }
+    cudaStream_t st = S(stream);
+    if (x_is_f32 && out_is_f32)
+        action_out_kernel<float, float><<<M, 256, 0, st>>>((const float*)x, B(weight), B(bias), (float*)out, Bm(mirror), Bm(norm_factor), K);
+    else if (x_is_f32)
+        action_out_kernel<float, bf16><<<M, 256, 0, st>>>((const float*)x, B(weight), B(bias), Bm(out), Bm(mirror), Bm(norm_factor), K);
+    else if (out_is_f32)
+        action_out_kernel<bf16, float><<<M, 256, 0, st>>>(B(x), B(weight), B(bias), (float*)out, Bm(mirror), Bm(norm_factor), K);
+    else
+        action_out_kernel<bf16, bf16><<<M, 256, 0, st>>>(B(x), B(weight), B(bias), Bm(out), Bm(mirror), Bm(norm_factor), K);
+    return check_launch("action_out_kernel");
+}
+
+}  // extern "C"

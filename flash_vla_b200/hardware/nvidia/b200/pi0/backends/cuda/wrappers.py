@@ -1,0 +1,322 @@
+"""Call-site wrappers of the CUDA backend: one function per Pi0 operation.
+
+Names and positional signatures are those of the reference's TileLang wrappers
+(`.../h100/pi0/backends/tilelang/wrappers.py:108-208`, `:252-306`, `:336-392`): torch
+tensors in, destination passed in and written in place. Each wrapper checks its tensors on
+the host, takes any scratch it needs from the active `ScratchPool`, and makes one call into
+libfvla_b200 on torch's current stream. Two names are added to the reference's nineteen,
+`vision_attention` and `encoder_attention`, which the reference pipeline calls as torch
+functions outside its table (`pipeline.py:16`).
+"""
+from __future__ import annotations
+
+import contextlib
+
+import torch
+
+from flash_vla_b200.runtime.cuda import ScratchPool
+
+from . import _lib
+
+_POOL = ScratchPool()
+
+DECODER_HEADS = 8
+VISION_TOKENS = 256
+VISION_DIM = 1152
+VISION_HEADS = 16
+VISION_HEAD_DIM = 72
+
+
+def set_pool(pool: ScratchPool) -> None:
+    """Install the scratch pool used by every wrapper."""
+    global _POOL
+    _POOL = pool
+
+
+@contextlib.contextmanager
+def use_pool(pool: ScratchPool):
+    """Route scratch requests through `pool` for the duration of the block."""
+    global _POOL
+    previous, _POOL = _POOL, pool
+    try:
+        yield
+    finally:
+        _POOL = previous
+
+
+def scratch(role: str, shape, dtype, device) -> torch.Tensor:
+    """Graph-safe temporary from the pool that is active at call time."""
+    return _POOL.get(role, shape, dtype, device)
+
+
+def _ws(role: str, nbytes: int, device):
+    """(pointer, size) of a zero-initialised byte scratch, or (None, 0)."""
+    if nbytes == 0:
+        return None, 0
+    buf = scratch(role, (nbytes,), torch.uint8, device)
+    return buf.data_ptr(), nbytes
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _is_f32(name: str, t: torch.Tensor) -> int:
+    """1 for an fp32 tensor, 0 for bf16; anything else is rejected."""
+    if t.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError(f"{name}: expected bf16 or fp32, got {t.dtype}")
+    return int(t.dtype == torch.float32)
+
+
+def _chk(name: str, t: torch.Tensor, shape=None, dtype=torch.bfloat16) -> int:
+    """Validate one operand on the host and return its device address."""
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise ValueError(f"{name}: expected a CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError(f"{name}: expected {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name}: expected a contiguous tensor, got strides {t.stride()}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name}: expected shape {tuple(shape)}, got {tuple(t.shape)}")
+    return t.data_ptr()
+
+
+# --------------------------------------------------------------------------- vision
+def vision_patch_embed(images, patch_w, patch_b, pos_emb, out):
+    """out = patches(images) @ patch_w + patch_b + pos_emb[row % 256] (wrappers.py:252-265)."""
+    views = images.shape[0]
+    lib = _lib.load()
+    ws, nb = _ws("patches", lib.fvla_patch_embed_workspace_bytes(views), images.device)
+    _lib.call("fvla_vision_patch_embed", _chk("images", images, (views, 224, 224, 3)),
+              _chk("patch_w", patch_w, (14, 14, 3, VISION_DIM)), _chk("patch_b", patch_b, (VISION_DIM,)),
+              _chk("pos_emb", pos_emb, (VISION_TOKENS, VISION_DIM)),
+              _chk("out", out, (views, VISION_TOKENS, VISION_DIM)), views, ws, nb, _stream())
+    return out
+
+
+def _norm_linear(entry, x, norm_w, norm_b, weight, bias, out, x_norm):
+    M = x.shape[0] * VISION_TOKENS
+    K, N = weight.shape
+    _lib.call(entry, _chk("x", x, (x.shape[0], VISION_TOKENS, K)), _chk("norm_w", norm_w, (K,)),
+              _chk("norm_b", norm_b, (K,)), _chk("weight", weight), _chk("bias", bias, (N,)),
+              _chk("out", out), _chk("x_norm", x_norm, x.shape), M, N, K, _stream())
+    return out
+
+
+def vision_norm_qkv(x, norm_w, norm_b, qkv_w, qkv_b, out, x_norm):
+    """x_norm = LayerNorm(x); out = x_norm @ qkv_w + qkv_b (wrappers.py:268-276)."""
+    if out.numel() != x.shape[0] * VISION_TOKENS * qkv_w.shape[1]:
+        raise ValueError("vision_norm_qkv: out has the wrong size")
+    return _norm_linear("fvla_vision_norm_qkv", x, norm_w, norm_b, qkv_w, qkv_b, out, x_norm)
+
+
+def vision_attention(QKV, out):
+    """Per-view 16-head attention over the packed QKV buffer (kernels/attention.py:20-26)."""
+    views = QKV.shape[0]
+    _lib.call("fvla_vision_attention", _chk("QKV", QKV, (views, VISION_TOKENS, 3 * VISION_DIM)),
+              _chk("out", out, (views, VISION_TOKENS, VISION_DIM)), views, VISION_TOKENS,
+              VISION_HEADS, VISION_HEAD_DIM, _stream())
+    return out
+
+
+def _linear_bias_residual(x, weight, bias, res, out):
+    K, N = weight.shape
+    M = x.numel() // K
+    if res.numel() != M * N or out.numel() != M * N:
+        raise ValueError("linear_bias_residual: res/out have the wrong size")
+    _lib.call("fvla_vision_linear_bias_residual", _chk("x", x), _chk("weight", weight),
+              _chk("bias", bias, (N,)), _chk("res", res), _chk("out", out), M, N, K, _stream())
+    return out
+
+
+def vision_out_proj_residual(x, weight, bias, res, out):
+    """out = x @ weight + bias + res; res and out may be one buffer (wrappers.py:279-288)."""
+    return _linear_bias_residual(x, weight, bias, res, out)
+
+
+def vision_norm_ffn_up(x, norm_w, norm_b, weight, bias, out, x_norm):
+    """x_norm = LayerNorm(x); out = gelu(x_norm @ weight + bias) (wrappers.py:291-298)."""
+    if out.numel() != x.shape[0] * VISION_TOKENS * weight.shape[1]:
+        raise ValueError("vision_norm_ffn_up: out has the wrong size")
+    return _norm_linear("fvla_vision_norm_ffn_up", x, norm_w, norm_b, weight, bias, out, x_norm)
+
+
+def vision_ffn_down_residual(x, weight, bias, res, out):
+    """out = hidden @ weight + bias + res (wrappers.py:301-306)."""
+    return _linear_bias_residual(x, weight, bias, res, out)
+
+
+# -------------------------------------------------------------------------- encoder
+def encoder_projector(x, norm_w, norm_b, proj_w, proj_b, out, x_norm):
+    """Final vision LayerNorm, then projection into encoder width (wrappers.py:336-344)."""
+    M = x.shape[0] * VISION_TOKENS
+    if out.shape[0] < M or out.shape[1] != proj_w.shape[1]:
+        raise ValueError("encoder_projector: out is too small")
+    return _norm_linear("fvla_encoder_projector", x, norm_w, norm_b, proj_w, proj_b, out, x_norm)
+
+
+def encoder_norm_qkv_rope(x, weight_qkv, rope, Q, K, V, x_norm):
+    """RMS norm, QKV projection rounded to bf16, RoPE, scatter to Q/K/V (wrappers.py:347-363)."""
+    M, Kdim = x.shape
+    hd = V.shape[1]
+    heads = Q.shape[0] // M
+    _lib.call("fvla_encoder_norm_qkv_rope", _chk("x", x), _chk("weight_qkv", weight_qkv, (Kdim, (heads + 2) * hd)),
+              _chk("rope", rope[:M], (M, hd)), _chk("Q", Q, (M * heads, hd)), _chk("K", K, (M, hd)),
+              _chk("V", V, (M, hd)), _chk("x_norm", x_norm[:M], (M, Kdim)), M, Kdim, heads, hd, _stream())
+
+
+def encoder_attention(Q, K, V, scale, out):
+    """Unmasked multi-query attention, Q flat (tokens * heads, hd) (kernels/attention.py:29-34)."""
+    queries, hd = Q.shape
+    keys = K.shape[0]
+    if out.numel() != queries * hd:
+        raise ValueError("encoder_attention: out has the wrong size")
+    _lib.call("fvla_encoder_attention", _chk("Q", Q), _chk("K", K, (keys, hd)), _chk("V", V, (keys, hd)),
+              _chk("out", out), queries, keys, hd, float(scale), _stream())
+    return out
+
+
+def _linear_residual(role, x, weight, out):
+    M, K = x.shape
+    N = weight.shape[1]
+    lib = _lib.load()
+    ws, nb = _ws(role, lib.fvla_gemm_workspace_bytes(M, N, K, 0), x.device)
+    _lib.call("fvla_linear_residual", _chk("x", x), _chk("weight", weight, (K, N)),
+              _chk("out", out, (M, N), dtype=None), _is_f32("out", out), M, N, K, ws, nb, _stream())
+    return out
+
+
+def encoder_out_proj_residual(x, weight, out):
+    """out += x @ weight (wrappers.py:366-371)."""
+    return _linear_residual("enc_o_ws", x, weight, out)
+
+
+def encoder_norm_gated_ffn(x, gate_w, up_w, out, x_norm):
+    """x_norm = rms(x); out = gelu(x_norm @ gate_w) * (x_norm @ up_w) (wrappers.py:374-380)."""
+    M, K = x.shape
+    N = gate_w.shape[1]
+    _lib.call("fvla_encoder_norm_gated_ffn", _chk("x", x), _chk("gate_w", gate_w, (K, N)),
+              _chk("up_w", up_w, (K, N)), _chk("out", out[:M], (M, N)), _chk("x_norm", x_norm[:M], (M, K)),
+              M, N, K, _stream())
+    return out
+
+
+def encoder_ffn_down_residual(x, weight, out):
+    """out += hidden @ weight (wrappers.py:383-392)."""
+    return _linear_residual("enc_down_ws", x, weight, out)
+
+
+# -------------------------------------------------------------------------- decoder
+def _small_proj(role, x, weight, bias, out, act):
+    K, N = weight.shape
+    M = x.numel() // K
+    lib = _lib.load()
+    ws, nb = _ws(role, lib.fvla_gemm_workspace_bytes(M, N, K, 0) if K > 64 else 0, x.device)
+    if out.numel() != M * N:
+        raise ValueError(f"{role}: out has the wrong size")
+    _lib.call("fvla_decoder_small_proj", _chk("x", x, dtype=None), _is_f32("x", x),
+              _chk("weight", weight), _chk("bias", bias, (N,)), _chk("out", out, dtype=None),
+              _is_f32("out", out), M, N, K, act, ws, nb, _stream())
+    return out
+
+
+def decoder_state_proj(x, weight, bias, out):
+    """out = x @ weight + bias for the single state token (wrappers.py:108-112)."""
+    return _small_proj("dec_state_ws", x, weight, bias, out, 0)
+
+
+def decoder_action_in_proj(x, weight, bias, out):
+    """out = silu(x @ weight + bias); x may be the fp32 master copy of the noise (wrappers.py:115-120)."""
+    return _small_proj("dec_in_ws", x, weight, bias, out, 2)
+
+
+def decoder_action_mlp(x, weight, bias, out):
+    """out = x @ weight + bias (wrappers.py:123-128)."""
+    return _small_proj("dec_mlp_ws", x, weight, bias, out, 0)
+
+
+def decoder_norm_qkv_rope(x, weight_qkv, rope, Q, K, V, norm_factor):
+    """RMS factor, QKV projection, RoPE in fp32, scatter into Q and the KV-cache tail
+    (wrappers.py:131-144). `norm_factor[:M]` receives the bf16 factor."""
+    M, Kdim = x.shape
+    hd = V.shape[1]
+    heads = Q.shape[0] // M
+    N = (heads + 2) * hd
+    lib = _lib.load()
+    ws, nb = _ws("dec_qkv_ws", lib.fvla_gemm_workspace_bytes(M, N, Kdim, 0), x.device)
+    _lib.call("fvla_decoder_norm_qkv_rope", _chk("x", x, dtype=None), _is_f32("x", x),
+              _chk("weight_qkv", weight_qkv, (Kdim, N)),
+              _chk("rope", rope[:M], (M, hd)), _chk("Q", Q, (M * heads, hd)), _chk("K", K, (M, hd)),
+              _chk("V", V, (M, hd)), _chk("norm_factor", norm_factor[:M], (M,)), M, Kdim, heads, hd,
+              ws, nb, _stream())
+
+
+def decoder_attention(Q, K, V, scores, out, encoder_seq_len):
+    """softmax(Q K^T / sqrt(hd)) V with the Pi0 mask, keys split across CTAs. `scores` is
+    accepted for signature parity and left untouched, as in the reference's fused wrapper
+    (fused_wrappers.py:88-115); `out` may be Q."""
+    del scores
+    queries, hd = Q.shape
+    keys = K.shape[0]
+    lib = _lib.load()
+    ws, nb = _ws("dec_attn_ws", lib.fvla_decoder_attention_workspace_bytes(queries, keys), Q.device)
+    _lib.call("fvla_decoder_attention", _chk("Q", Q), _chk("K", K, (keys, hd)), _chk("V", V, (keys, hd)),
+              _chk("out", out, (queries, hd)), queries, keys, hd, DECODER_HEADS, int(encoder_seq_len),
+              ws, nb, _stream())
+    return out
+
+
+def decoder_out_proj_residual(x, weight, out):
+    """out += x @ weight (wrappers.py:176-181)."""
+    return _linear_residual("dec_o_ws", x, weight, out)
+
+
+def decoder_ffn_down_residual(x, weight, out):
+    """out += x @ weight (wrappers.py:184-189)."""
+    return _linear_residual("dec_down_ws", x, weight, out)
+
+
+def _gated_ffn(x, gate_w, up_w, out, norm_factor):
+    M, K = x.shape
+    N = gate_w.shape[1]
+    lib = _lib.load()
+    ws, nb = _ws("dec_gate_ws", lib.fvla_gemm_workspace_bytes(M, N, K, 1), x.device)
+    nf = None if norm_factor is None else _chk("norm_factor", norm_factor[:M], (M,))
+    _lib.call("fvla_decoder_norm_gated_ffn", _chk("x", x, dtype=None), _is_f32("x", x), _chk("gate_w", gate_w, (K, N)),
+              _chk("up_w", up_w, (K, N)), _chk("out", out, (M, N)), nf, M, N, K, ws, nb, _stream())
+    return out
+
+
+def decoder_norm_gated_ffn(x, gate_w, up_w, out, norm_factor):
+    """out = gelu(rms(x) @ gate_w) * (rms(x) @ up_w); stores the factor (wrappers.py:192-198)."""
+    return _gated_ffn(x, gate_w, up_w, out, norm_factor)
+
+
+def _action_out(x, weight, bias, out, norm_factor):
+    M, K = x.shape
+    N = weight.shape[1]
+    nf = None if norm_factor is None else _chk("norm_factor", norm_factor[:M], (M,))
+    _lib.call("fvla_decoder_action_out_proj", _chk("x", x, dtype=None), _is_f32("x", x),
+              _chk("weight", weight, (K, N)), _chk("bias", bias, (N,)), _chk("out", out, (M, N), dtype=None),
+              _is_f32("out", out), None, nf, M, N, K, _stream())
+    return out
+
+
+def decoder_action_out_proj(x, weight, bias, out, norm_factor):
+    """out += bias + rms(x) @ weight, the Euler update; stores the factor (wrappers.py:201-208).
+    `out` may be bf16 or the fp32 master copy of the noise."""
+    return _action_out(x, weight, bias, out, norm_factor)
+
+
+VISION_WRAPPERS = {f.__name__: f for f in (
+    vision_patch_embed, vision_norm_qkv, vision_attention, vision_out_proj_residual,
+    vision_norm_ffn_up, vision_ffn_down_residual)}
+ENCODER_WRAPPERS = {f.__name__: f for f in (
+    encoder_projector, encoder_norm_qkv_rope, encoder_attention, encoder_out_proj_residual,
+    encoder_norm_gated_ffn, encoder_ffn_down_residual)}
+DECODER_WRAPPERS = {f.__name__: f for f in (
+    decoder_state_proj, decoder_action_in_proj, decoder_action_mlp, decoder_norm_qkv_rope,
+    decoder_attention, decoder_out_proj_residual, decoder_ffn_down_residual,
+    decoder_norm_gated_ffn, decoder_action_out_proj)}
+
+ALL_WRAPPERS = {**VISION_WRAPPERS, **ENCODER_WRAPPERS, **DECODER_WRAPPERS}

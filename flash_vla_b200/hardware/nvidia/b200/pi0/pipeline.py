@@ -1,0 +1,104 @@
+"""The Pi0 forward pass of the B200 target as calls into an operation table.
+
+Three stages, each a pure sequence of `ops.<name>(...)` calls on static buffers, following
+the reference's orchestration (`.../h100/pi0/pipeline.py:21-135`) call for call. Differences,
+all on the B200 side of the drop-in boundary:
+
+  * SigLIP and prefix attention go through the table (`ops.vision_attention`,
+    `ops.encoder_attention`) into preallocated buffers instead of being torch calls.
+  * When the buffer plan holds `diffusion_noise_f32`, the Euler updates accumulate in it and
+    the bf16 `diffusion_noise` is refreshed once at the end of the decoder.
+"""
+from __future__ import annotations
+
+from flash_vla_b200.models.pi0.spec import (DECODER_HEADS, DIFFUSION_STEPS, ENCODER_LAYERS, HEAD_DIM,
+                                           VISION_LAYERS, VISION_TOKENS)
+
+
+def vision_encoder(ops, weights, buffers, num_views):
+    """Patch-embed the views and run the 27 SigLIP layers in place on `vision_x`."""
+    if num_views == 2:
+        raise NotImplementedError("num_views == 2 is not supported (as in the reference, pipeline.py:23)")
+    w, b = weights, buffers
+    x, xn = b["vision_x"], b["vision_x_norm"]
+    ops.vision_patch_embed(b["observation_images_normalized"], w["vision_patch_embedding_w"],
+                           w["vision_patch_embedding_b"], w["vision_position_embedding"], x)
+    for layer in range(VISION_LAYERS):
+        ops.vision_norm_qkv(x, w["vision_pre_attn_norm_w"][layer], w["vision_pre_attn_norm_b"][layer],
+                            w["vision_attn_qkv_w"][layer], w["vision_attn_qkv_b"][layer],
+                            b["vision_QKV"], xn)
+        ops.vision_attention(b["vision_QKV"], b["vision_attn"])
+        ops.vision_out_proj_residual(b["vision_attn"], w["vision_attn_o_w"][layer],
+                                     w["vision_attn_o_b"][layer], x, x)
+        ops.vision_norm_ffn_up(x, w["vision_pre_ffn_norm_w"][layer], w["vision_pre_ffn_norm_b"][layer],
+                               w["vision_ffn_up_w"][layer], w["vision_ffn_up_b"][layer],
+                               b["vision_hidden"], xn)
+        ops.vision_ffn_down_residual(b["vision_hidden"], w["vision_ffn_down_w"][layer],
+                                     w["vision_ffn_down_b"][layer], x, x)
+
+
+def transformer_encoder(ops, weights, buffers, encoder_seq_len):
+    """Project vision tokens to encoder width and fill the prefix KV cache of all 18 layers.
+
+    The last layer only needs its K and V, so it stops after the QKV projection.
+    """
+    w, b, S = weights, buffers, encoder_seq_len
+    x = b["encoder_x"]
+    ops.encoder_projector(b["vision_x"], w["vision_final_norm_w"], w["vision_final_norm_b"],
+                          w["encoder_multi_modal_projector_w"], w["encoder_multi_modal_projector_b"],
+                          x, b["vision_x_norm"])
+    for layer in range(ENCODER_LAYERS):
+        k_prefix, v_prefix = b["encoder_K"][layer, :S], b["encoder_V"][layer, :S]
+        ops.encoder_norm_qkv_rope(x, w["encoder_attn_qkv_w"][layer], b["encoder_rope_weights"],
+                                  b["encoder_Q"], k_prefix, v_prefix, b["encoder_x_norm"])
+        if layer == ENCODER_LAYERS - 1:
+            return
+        ops.encoder_attention(b["encoder_Q"], k_prefix, v_prefix, HEAD_DIM ** -0.5, b["encoder_attn"])
+        ops.encoder_out_proj_residual(b["encoder_attn"], w["encoder_attn_o_w"][layer], x)
+        ops.encoder_norm_gated_ffn(x, w["encoder_ffn_gate_w"][layer], w["encoder_ffn_up_w"][layer],
+                                   b["encoder_hidden"], b["encoder_x_norm"])
+        ops.encoder_ffn_down_residual(b["encoder_hidden"], w["encoder_ffn_down_w"][layer], x)
+
+
+def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LAYERS, noise=None):
+    """One flow-matching Euler step over `noise` (default: the plan's master copy)."""
+    w, b, S = weights, buffers, encoder_seq_len
+    if noise is None:
+        noise = b["diffusion_noise_f32"] if "diffusion_noise_f32" in b else b["diffusion_noise"]
+    x, nf = b["decoder_x"], b["decoder_norm_factor_buf"]
+    x[:1].copy_(b["decoder_state_buf"])
+    ops.decoder_action_in_proj(noise, w["decoder_action_fused_in_proj_w"],
+                               w["decoder_action_fused_time_biases"][step % DIFFUSION_STEPS],
+                               b["decoder_x_buf"])
+    ops.decoder_action_mlp(b["decoder_x_buf"], w["decoder_action_mlp_w"], w["decoder_action_mlp_b"], x[1:])
+    q = b["decoder_q_buf"]
+    for layer in range(layers):
+        k_cache, v_cache = b["encoder_K"][layer], b["encoder_V"][layer]
+        ops.decoder_norm_qkv_rope(x, w["decoder_attn_qkv_w"][layer], b["decoder_rope_weights"], q,
+                                  k_cache[S:], v_cache[S:], nf)
+        ops.decoder_attention(q, k_cache, v_cache, b["decoder_attn_buf"], q, S)
+        ops.decoder_out_proj_residual(q.view(-1, DECODER_HEADS * HEAD_DIM), w["decoder_attn_o_w"][layer], x)
+        ops.decoder_norm_gated_ffn(x, w["decoder_ffn_gate_w"][layer], w["decoder_ffn_up_w"][layer],
+                                   b["decoder_hidden"], nf)
+        ops.decoder_ffn_down_residual(b["decoder_hidden"], w["decoder_ffn_down_w"][layer], x)
+    ops.decoder_action_out_proj(x[1:], w["decoder_action_fused_out_proj_w"],
+                                w["decoder_action_fused_out_proj_b"], noise, nf)
+
+
+def transformer_decoder(ops, weights, buffers, encoder_seq_len, steps=DIFFUSION_STEPS,
+                        layers=ENCODER_LAYERS):
+    """Denoise the action chunk in `diffusion_noise` over `steps` Euler steps."""
+    b = buffers
+    ops.decoder_state_proj(b["observation_state_normalized"], weights["decoder_state_in_proj_w"],
+                           weights["decoder_state_in_proj_b"], b["decoder_state_buf"])
+    master = b.get("diffusion_noise_f32")
+    if master is not None:
+        master.copy_(b["diffusion_noise"])
+    for step in range(steps):
+        decoder_step(ops, weights, b, encoder_seq_len, step, layers, noise=master)
+    if master is not None:
+        b["diffusion_noise"].copy_(master)
+
+
+def num_vision_tokens(num_views: int) -> int:
+    return num_views * VISION_TOKENS

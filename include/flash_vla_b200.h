@@ -1,0 +1,123 @@
+/* C ABI of libfvla_b200: hand-written sm_100a kernels for the Pi0 forward pass.
+ *
+ * Entry points for every call site of the reference's operation table
+ * (revollllt/flash-vla, src/flash_vla/hardware/nvidia/h100/pi0/backends/tilelang/wrappers.py
+ * and fused_wrappers.py), so that a backend module exposing ALL_WRAPPERS / FUSED_WRAPPERS
+ * with the reference's signatures is a thin shim over these functions.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer. Unless a parameter says otherwise, tensors are bf16,
+ *     row-major and contiguous; linear weights are (in, out) with the output axis contiguous.
+ *   - `stream` is a cudaStream_t. Calls only enqueue work: they never allocate, free or
+ *     synchronise, so they may be issued while a CUDA graph is being captured.
+ *   - `ws` / `ws_bytes` is caller-owned scratch of at least the size returned by the matching
+ *     *_workspace_bytes query; it must be zero-filled once before its first use (it holds
+ *     tile semaphores that reset themselves) and must not be shared by kernels that may run
+ *     concurrently. Pass NULL / 0 where the query returns 0.
+ *   - Return value: FVLA_OK or a negative error code; fvla_last_error() gives the text of the
+ *     last failure on the calling thread. Arguments are validated before anything is launched.
+ *   - Aliasing that the reference relies on is supported: a residual may be the destination
+ *     (wrappers.py:176-189, :279-306, :366-392); the decoder attention may write over Q
+ *     (pipeline.py:119-121).
+ */
+#ifndef FLASH_VLA_B200_H_
+#define FLASH_VLA_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FVLA_OK 0
+#define FVLA_ERR_ARG (-1)         /* bad shape, stride or alignment */
+#define FVLA_ERR_WORKSPACE (-2)   /* scratch missing or too small */
+#define FVLA_ERR_LAUNCH (-3)      /* the CUDA runtime rejected a launch or an attribute */
+#define FVLA_ERR_UNSUPPORTED (-4) /* shape outside what the kernels implement */
+
+const char* fvla_last_error(void);
+/* ABI version of this header; bumped on any signature change. */
+int fvla_abi_version(void);
+
+/* Scratch needed by a GEMM-shaped op of the given logical size. `dual` = 1 for gated FFNs. */
+size_t fvla_gemm_workspace_bytes(int M, int N, int K, int dual);
+/* Scratch for the decoder's split-key attention with `queries` flat rows and `keys` keys. */
+size_t fvla_decoder_attention_workspace_bytes(int queries, int keys);
+/* Scratch for the patchified image matrix of `views` camera views. */
+size_t fvla_patch_embed_workspace_bytes(int views);
+
+/* ---- SigLIP vision tower (M = views * 256 tokens, width 1152) -------------------------- */
+/* wrappers.py:252-265: patchify (views,224,224,3), (768,588) @ (588,1152) + bias + pos[row % 256]. */
+int fvla_vision_patch_embed(const void* images, const void* patch_w, const void* patch_b,
+                            const void* pos_emb, void* out, int views, void* ws, size_t ws_bytes,
+                            void* stream);
+/* wrappers.py:268-276: x_norm = LayerNorm(x); out = x_norm @ W(K,N) + b. */
+int fvla_vision_norm_qkv(const void* x, const void* norm_w, const void* norm_b, const void* qkv_w,
+                         const void* qkv_b, void* out, void* x_norm, int M, int N, int K,
+                         void* stream);
+/* kernels/attention.py:20-26: packed (views,256,3,heads,head_dim) -> (views,256,heads*head_dim). */
+int fvla_vision_attention(const void* qkv, void* out, int views, int tokens, int heads,
+                          int head_dim, void* stream);
+/* wrappers.py:279-288 and :301-306: out = x(M,K) @ W(K,N) + b + res; res may alias out. */
+int fvla_vision_linear_bias_residual(const void* x, const void* weight, const void* bias,
+                                     const void* res, void* out, int M, int N, int K, void* stream);
+/* wrappers.py:291-298: x_norm = LayerNorm(x); out = gelu_tanh(x_norm @ W + b). */
+int fvla_vision_norm_ffn_up(const void* x, const void* norm_w, const void* norm_b,
+                            const void* weight, const void* bias, void* out, void* x_norm, int M,
+                            int N, int K, void* stream);
+
+/* ---- Prefix encoder (M = S tokens, width 2048) ------------------------------------------ */
+/* wrappers.py:336-344: x_norm = LayerNorm(x); out = x_norm @ W + b. */
+int fvla_encoder_projector(const void* x, const void* norm_w, const void* norm_b, const void* proj_w,
+                           const void* proj_b, void* out, void* x_norm, int M, int N, int K,
+                           void* stream);
+/* wrappers.py:347-363: x_norm = rms(x); proj = bf16(x_norm @ W); RoPE on adjacent pairs of the
+ * Q heads and K; scatter to Q (M, heads*hd), K (M, hd), V (M, hd). rope is (M, hd) interleaved
+ * cos/sin. */
+int fvla_encoder_norm_qkv_rope(const void* x, const void* weight_qkv, const void* rope, void* Q,
+                               void* K, void* V, void* x_norm, int M, int Kdim, int heads,
+                               int head_dim, void* stream);
+/* kernels/attention.py:29-34: unmasked multi-query attention, Q flat (tokens*heads, hd). */
+int fvla_encoder_attention(const void* Q, const void* K, const void* V, void* out, int queries,
+                           int keys, int head_dim, float scale, void* stream);
+/* wrappers.py:366-371, :383-392 (encoder) and :176-189 (decoder): out += x(M,K) @ W(K,N). out is
+ * bf16, or an fp32 residual stream when out_is_f32 != 0. */
+int fvla_linear_residual(const void* x, const void* weight, void* out, int out_is_f32, int M, int N,
+                         int K, void* ws, size_t ws_bytes, void* stream);
+/* wrappers.py:374-380: x_norm = rms(x); out = gelu(x_norm @ Wg) * (x_norm @ Wu). */
+int fvla_encoder_norm_gated_ffn(const void* x, const void* gate_w, const void* up_w, void* out,
+                                void* x_norm, int M, int N, int K, void* stream);
+
+/* ---- Action-expert decoder (M = chunk + 1 rows, width 1024) ------------------------------ */
+/* wrappers.py:108-128: out = act(x(M,K) @ W(K,N) + b); act 0 none, 2 silu; K <= 64 uses a
+ * dedicated kernel. x is bf16, or fp32 when x_is_f32 != 0 (K <= 64 only); out likewise. */
+int fvla_decoder_small_proj(const void* x, int x_is_f32, const void* weight, const void* bias,
+                            void* out, int out_is_f32, int M, int N, int K, int act, void* ws,
+                            size_t ws_bytes, void* stream);
+/* wrappers.py:131-144: factor = rsqrt(mean(x^2)+1e-6) (also stored, bf16, in norm_factor when
+ * not NULL); projection scaled by it, RoPE in fp32, single rounding, scatter to Q / K / V.
+ * x is the bf16 residual stream, or an fp32 one when x_is_f32 != 0. */
+int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* weight_qkv, const void* rope, void* Q,
+                               void* K, void* V, void* norm_factor, int M, int Kdim, int heads,
+                               int head_dim, void* ws, size_t ws_bytes, void* stream);
+/* fused_wrappers.py:88-115 (and the unfused chain wrappers.py:147-173): softmax(Q K^T / sqrt(hd))
+ * V over all `keys`, with rows < heads (the state token) limited to keys j <= encoder_seq_len.
+ * out may alias Q. */
+int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* out, int queries,
+                           int keys, int head_dim, int heads, int encoder_seq_len, void* ws,
+                           size_t ws_bytes, void* stream);
+/* fused_wrappers.py:45-54 / wrappers.py:192-198: out = gelu(rms(x) @ Wg) * (rms(x) @ Wu). When
+ * norm_factor is not NULL the bf16 factor is also stored there (the unfused side effect). */
+int fvla_decoder_norm_gated_ffn(const void* x, int x_is_f32, const void* gate_w, const void* up_w,
+                                void* out, void* norm_factor, int M, int N, int K, void* ws,
+                                size_t ws_bytes, void* stream);
+/* fused_wrappers.py:57-67 / wrappers.py:201-208: out += b + rms(x)(M,K) @ W(K,32). x and out are
+ * bf16, or fp32 when the matching flag != 0; `mirror`, if not NULL, receives the new value as bf16. */
+int fvla_decoder_action_out_proj(const void* x, int x_is_f32, const void* weight, const void* bias, void* out,
+                                 int out_is_f32, void* mirror, void* norm_factor, int M, int N,
+                                 int K, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASH_VLA_B200_H_ */

@@ -1,0 +1,172 @@
+"""Host-side logic that needs no GPU: schema, op table, scratch pool, buffer plan, the package
+pipeline driven by the oracle's ops, and the C-ABI library's exported symbols."""
+from __future__ import annotations
+
+import ctypes
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT
+from oracle import pi0_ref as O
+
+
+def test_weight_schema():
+    from flash_vla_b200.models.pi0 import weight_shapes
+    shapes = weight_shapes(48)
+    assert len(shapes) == 38
+    assert shapes["language_embeds"] == (48, 2048)
+    assert shapes["vision_ffn_up_w"] == (27, 1152, 4304)
+    assert shapes["decoder_attn_qkv_w"] == (18, 1024, 2560)
+    total = sum(torch.Size(s).numel() for s in weight_shapes(0).values())
+    assert abs(total - 2.709e9) < 2e6
+    assert list(shapes)[0] == "vision_patch_embedding_w" and list(shapes)[-1] == "language_embeds"
+
+
+def test_random_checkpoint_is_deterministic_and_filterable():
+    from flash_vla_b200.models.pi0 import random_checkpoint
+    a = random_checkpoint(prompt_len=0, wscale=0.02, seed=0, device="cpu", only=("decoder_action", "decoder_state"))
+    b = random_checkpoint(prompt_len=0, wscale=0.02, seed=0, device="cpu", only=("decoder_action", "decoder_state"))
+    assert set(a) == {"decoder_state_in_proj_w", "decoder_state_in_proj_b", "decoder_action_fused_in_proj_w",
+                      "decoder_action_fused_time_biases", "decoder_action_mlp_w", "decoder_action_mlp_b",
+                      "decoder_action_fused_out_proj_w", "decoder_action_fused_out_proj_b"}
+    assert all(torch.equal(a[k], b[k]) and a[k].dtype == torch.bfloat16 for k in a)
+    assert 0.015 < a["decoder_action_mlp_w"].float().std().item() < 0.025
+
+
+def test_op_table_contract():
+    from flash_vla_b200 import op_table
+    from flash_vla_b200.hardware.nvidia.b200.pi0.backends import BACKENDS, DEFAULT_FUSED_OPS
+    from flash_vla_b200.hardware.nvidia.b200.pi0.ops import op_names
+    cuda = BACKENDS["cuda"]
+    reference_names = {
+        "vision_patch_embed", "vision_norm_qkv", "vision_out_proj_residual", "vision_norm_ffn_up",
+        "vision_ffn_down_residual", "encoder_projector", "encoder_norm_qkv_rope", "encoder_out_proj_residual",
+        "encoder_norm_gated_ffn", "encoder_ffn_down_residual", "decoder_state_proj", "decoder_action_in_proj",
+        "decoder_action_mlp", "decoder_norm_qkv_rope", "decoder_attention", "decoder_out_proj_residual",
+        "decoder_ffn_down_residual", "decoder_norm_gated_ffn", "decoder_action_out_proj"}
+    assert reference_names <= set(cuda.ALL_WRAPPERS)
+    assert set(cuda.ALL_WRAPPERS) - reference_names == {"vision_attention", "encoder_attention"}
+    assert set(DEFAULT_FUSED_OPS) == {"decoder_norm_gated_ffn", "decoder_action_out_proj", "decoder_attention"}
+    fused, unfused = op_table(True), op_table(False)
+    assert fused.decoder_attention is cuda.FUSED_WRAPPERS["decoder_attention"]
+    assert unfused.decoder_attention is cuda.ALL_WRAPPERS["decoder_attention"]
+    assert fused.vision_norm_qkv is unfused.vision_norm_qkv
+    planned = op_table(True, plan={"decoder_attention": "cuda"})
+    assert set(vars(planned)) == set(op_names(True))
+    with pytest.raises(KeyError):
+        op_table(True, plan={"decoder_attention": "tilelang"})
+    # signatures are positional and match the oracle's (which follow the reference's wrappers)
+    import inspect
+    for name in reference_names:
+        want = list(inspect.signature(getattr(O.op_table(True), name)).parameters)
+        got = list(inspect.signature(getattr(fused, name)).parameters)
+        assert got == want, name
+
+
+def test_scratch_pool_freeze():
+    from flash_vla_b200.runtime.cuda import ScratchPool
+    pool = ScratchPool()
+    a = pool.get("partials", (3, 4), torch.float32, "cpu")
+    assert a.abs().sum() == 0 and pool.get("partials", (3, 4), torch.float32, "cpu") is a
+    assert pool.get("partials", (3, 5), torch.float32, "cpu") is not a and len(pool) == 2
+    pool.freeze()
+    assert pool.get("partials", (3, 4), torch.float32, "cpu") is a
+    with pytest.raises(RuntimeError, match="frozen"):
+        pool.get("partials", (9,), torch.float32, "cpu")
+
+
+def test_buffer_plan():
+    from flash_vla_b200.hardware.nvidia.b200.pi0.buffers import allocate_static_buffers, rope_table
+    b, S = allocate_static_buffers(3, 50, 49, "cpu")
+    assert S == 817
+    assert b["encoder_K"].shape == (18, 868, 256) and b["encoder_Q"].shape == (817 * 8, 256)
+    assert b["decoder_attn_buf"].shape == (408, 868) and b["decoder_q_buf"].shape == (408, 256)
+    assert b["diffusion_noise"].dtype == torch.bfloat16 and b["diffusion_noise_f32"].dtype == torch.float32
+    assert b["decoder_x"].dtype == torch.float32
+    assert torch.equal(b["decoder_rope_weights"], O.rope_table(51, 817))
+    assert torch.equal(rope_table(13, 5, 256, "cpu"), O.rope_table(13, 5))
+
+
+def test_package_pipeline_with_oracle_ops(monkeypatch):
+    """The package's orchestration, driven by the oracle's op table on the CPU, must equal the
+    oracle's own orchestration (which make_golden checks against the reference's pipeline.py).
+    Layer counts are cut to 2 to keep this fast; stacked weights are drawn directly."""
+    from flash_vla_b200.hardware.nvidia.b200.pi0 import pipeline
+    from flash_vla_b200.models.pi0.spec import weight_shapes
+    L = 2
+    monkeypatch.setattr(pipeline, "VISION_LAYERS", L)
+    monkeypatch.setattr(pipeline, "ENCODER_LAYERS", L)
+    monkeypatch.setattr(O, "VISION_LAYERS", L)
+    monkeypatch.setattr(O, "ENCODER_LAYERS", L)
+    g = torch.Generator().manual_seed(0)
+    w = {}
+    for name, shape in weight_shapes(5).items():
+        shape = tuple(L if (i == 0 and s in (27, 18) and len(shape) > 1 and name != "decoder_action_fused_time_biases") else s
+                      for i, s in enumerate(shape))
+        w[name] = torch.randn(shape, generator=g) * 0.02
+    images = torch.rand(3, 224, 224, 3, generator=g) * 2 - 1
+    state, noise = torch.randn(32, generator=g), torch.randn(50, 32, generator=g)
+
+    want, ref_buffers = O.forward(w, images, state, noise, steps=3, layers=L)
+    want = want.clone()
+
+    b, S = O.allocate_buffers(3, 50, 5)
+    b["diffusion_noise_f32"] = torch.zeros(50, 32)
+    ops = O.op_table(True)
+    b["observation_images_normalized"].copy_(images)
+    b["observation_state_normalized"].copy_(state)
+    b["diffusion_noise"].copy_(noise)
+    b["encoder_x"][768:].copy_(w["language_embeds"])
+    pipeline.vision_encoder(ops, w, b, 3)
+    pipeline.transformer_encoder(ops, w, b, S)
+    pipeline.transformer_decoder(ops, w, b, S, steps=3, layers=L)
+    assert torch.allclose(b["diffusion_noise"], want, atol=1e-5)
+    assert torch.allclose(b["encoder_K"][:L], ref_buffers["encoder_K"][:L], atol=1e-5)
+    with pytest.raises(NotImplementedError):
+        pipeline.vision_encoder(ops, w, b, 2)
+
+
+def test_engine_refuses_to_run_without_cuda():
+    if torch.cuda.is_available():
+        pytest.skip("CUDA present")
+    from flash_vla_b200 import Pi0Inference
+    with pytest.raises(RuntimeError, match="CUDA"):
+        Pi0Inference({"language_embeds": torch.zeros(0, 2048)}, num_views=3, chunk_size=50)
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "flash_vla_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fvla_\w+)\s*\(", text)))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    from flash_vla_b200 import build
+    from flash_vla_b200.hardware.nvidia.b200.pi0.backends.cuda import _lib
+    path = build.build()
+    lib = ctypes.CDLL(str(path))
+    names = declared_symbols()
+    assert len(names) >= 20
+    for name in names:
+        assert hasattr(lib, name), name
+    assert set(_lib.SIGNATURES) | set(_lib.QUERIES) == set(names)
+    loaded = _lib.load()
+    assert loaded.fvla_abi_version() >= 1
+    # pure host queries: sizes grow with the problem and are zero for empty problems
+    assert loaded.fvla_gemm_workspace_bytes(0, 8, 8, 0) == 0
+    assert loaded.fvla_gemm_workspace_bytes(51, 4096, 1024, 1) > loaded.fvla_gemm_workspace_bytes(51, 4096, 1024, 0) > 0
+    assert loaded.fvla_decoder_attention_workspace_bytes(408, 868) >= 7 * 448 * 256 * 4
+    assert loaded.fvla_patch_embed_workspace_bytes(3) == 3 * 256 * 592 * 2
+
+
+def test_header_argument_counts_match_ctypes_table():
+    from flash_vla_b200.hardware.nvidia.b200.pi0.backends.cuda import _lib
+    text = re.sub(r"/\*.*?\*/", "", (ROOT / "include" / "flash_vla_b200.h").read_text(), flags=re.S)
+    for name, argtypes in {**_lib.SIGNATURES, **{k: v[0] for k, v in _lib.QUERIES.items()}}.items():
+        m = re.search(rf"\b{name}\s*\((.*?)\)\s*;", text, flags=re.S)
+        assert m, name
+        args = m.group(1).strip()
+        count = 0 if args in ("", "void") else args.count(",") + 1
+        assert count == len(argtypes), f"{name}: header has {count} parameters, ctypes table {len(argtypes)}"
