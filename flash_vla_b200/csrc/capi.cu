@@ -1,11 +1,15 @@
 // extern "C" surface of libfvla_b200: argument validation, kernel selection, launches.
 // Nothing here allocates, frees or synchronises.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
+#include <cstring>
 
 #include "attention.cuh"
 #include "common.cuh"
 #include "gemm_mma.cuh"
+#include "gemm_tc5.cuh"
 #include "rowops.cuh"
 
 namespace fvla {
@@ -19,7 +23,10 @@ void set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
+static std::atomic<unsigned long long> g_launches{0};
+
 int check_launch(const char* what) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         set_error("%s: %s", what, cudaGetErrorString(e));
@@ -66,6 +73,40 @@ static void gemm_ws(void* ws, size_t ws_bytes, int M, int K, void** p, size_t* n
     *n = has ? ws_bytes - off : 0;
 }
 
+// Device status word written by kernels whose bounded waits ran out (0 = healthy).
+__device__ int g_device_status;
+
+static int* device_status_ptr() {
+    static thread_local int cached_dev = -1;
+    static thread_local int* cached_ptr = nullptr;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev != cached_dev) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_device_status) != cudaSuccess) return nullptr;
+        cached_ptr = static_cast<int*>(ptr);
+        cached_dev = dev;
+    }
+    return cached_ptr;
+}
+
+// FVLA_GEMM=mma forces every GEMM onto the warp-level kernel (a diagnostic switch for
+// comparing the two tensor paths; the default is tcgen05 wherever the shape allows).
+static bool tc5_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* v = getenv("FVLA_GEMM");
+        enabled = (v != nullptr && strcmp(v, "mma") == 0) ? 0 : 1;
+    }
+    return enabled == 1;
+}
+
+// GEMM dispatch: tcgen05 for M > 64, the warp-level kernel (with split-K) for the skinny shapes.
+static int launch_gemm(const GemmArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
+    if (tc5_enabled() && tc5::tc5_supports(a)) return tc5::launch_gemm_tc5(a, device_status_ptr(), st);
+    return launch_gemm_mma(a, ws, ws_bytes, st);
+}
+
 }  // namespace fvla
 
 using namespace fvla;
@@ -74,6 +115,17 @@ extern "C" {
 
 const char* fvla_last_error(void) { return g_error; }
 int fvla_abi_version(void) { return 1; }
+unsigned long long fvla_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int fvla_device_status(void* stream) {
+    int* ptr = device_status_ptr();
+    if (ptr == nullptr) { set_error("device_status: no CUDA device"); return FVLA_ERR_LAUNCH; }
+    int value = 0;
+    cudaError_t e = cudaMemcpyAsync(&value, ptr, sizeof(int), cudaMemcpyDeviceToHost, S(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(S(stream));
+    if (e != cudaSuccess) { set_error("device_status: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
+    return value;
+}
 
 size_t fvla_gemm_workspace_bytes(int M, int N, int K, int dual) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -107,7 +159,7 @@ int fvla_vision_patch_embed(const void* images, const void* patch_w, const void*
     a.A = B(ws); a.lda = 592; a.B = B(patch_w); a.ldb = 1152; a.C = out; a.ldc = 1152;
     a.bias = B(patch_b); a.R = pos_emb; a.ldr = 1152; a.res_mod = 256;
     a.M = M; a.N = 1152; a.K = 592; a.Kb = 588;
-    return launch_gemm_mma(a, nullptr, 0, S(stream));
+    return launch_gemm(a, nullptr, 0, S(stream));
 }
 
 static int norm_linear(const void* x, const void* nw, const void* nb, const void* w, const void* b,
@@ -117,7 +169,7 @@ static int norm_linear(const void* x, const void* nw, const void* nb, const void
     GemmArgs a;
     a.A = B(x_norm); a.lda = K; a.B = B(w); a.ldb = N; a.C = out; a.ldc = N; a.bias = B(b);
     a.act = act; a.M = M; a.N = N; a.K = K;
-    return launch_gemm_mma(a, nullptr, 0, S(stream));
+    return launch_gemm(a, nullptr, 0, S(stream));
 }
 
 int fvla_vision_norm_qkv(const void* x, const void* norm_w, const void* norm_b, const void* qkv_w,
@@ -156,7 +208,7 @@ int fvla_vision_linear_bias_residual(const void* x, const void* weight, const vo
     GemmArgs a;
     a.A = B(x); a.lda = K; a.B = B(weight); a.ldb = N; a.C = out; a.ldc = N; a.bias = B(bias);
     a.R = res; a.ldr = N; a.M = M; a.N = N; a.K = K;
-    return launch_gemm_mma(a, nullptr, 0, S(stream));
+    return launch_gemm(a, nullptr, 0, S(stream));
 }
 
 int fvla_encoder_norm_qkv_rope(const void* x, const void* weight_qkv, const void* rope, void* Q, void* K,
@@ -169,7 +221,7 @@ int fvla_encoder_norm_qkv_rope(const void* x, const void* weight_qkv, const void
     a.M = M; a.N = (heads + 2) * head_dim; a.K = Kdim;
     a.rope = B(rope); a.q = Bm(Q); a.k = Bm(K); a.v = Bm(V); a.heads = heads; a.head_dim = head_dim;
     a.round_first = 1;
-    return launch_gemm_mma(a, nullptr, 0, S(stream));
+    return launch_gemm(a, nullptr, 0, S(stream));
 }
 
 int fvla_encoder_attention(const void* Q, const void* K, const void* V, void* out, int queries, int keys,
@@ -191,7 +243,7 @@ int fvla_linear_residual(const void* x, const void* weight, void* out, int out_i
     a.R = out; a.ldr = N; a.M = M; a.N = N; a.K = K;
     void* gws; size_t gn;
     gemm_ws(ws, ws_bytes, M, K, &gws, &gn);
-    return launch_gemm_mma(a, gws, gn, S(stream));
+    return launch_gemm(a, gws, gn, S(stream));
 }
 
 int fvla_encoder_norm_gated_ffn(const void* x, const void* gate_w, const void* up_w, void* out, void* x_norm,
@@ -202,7 +254,7 @@ int fvla_encoder_norm_gated_ffn(const void* x, const void* gate_w, const void* u
     GemmArgs a;
     a.A = B(x_norm); a.lda = K; a.B = B(gate_w); a.B2 = B(up_w); a.ldb = N; a.C = out; a.ldc = N;
     a.M = M; a.N = N; a.K = K;
-    return launch_gemm_mma(a, nullptr, 0, S(stream));
+    return launch_gemm(a, nullptr, 0, S(stream));
 }
 
 int fvla_decoder_small_proj(const void* x, int x_is_f32, const void* weight, const void* bias, void* out,
@@ -228,7 +280,7 @@ int fvla_decoder_small_proj(const void* x, int x_is_f32, const void* weight, con
     a.bias = B(bias); a.act = act; a.M = M; a.N = N; a.K = K;
     void* gws; size_t gn;
     gemm_ws(ws, ws_bytes, M, K, &gws, &gn);
-    return launch_gemm_mma(a, gws, gn, S(stream));
+    return launch_gemm(a, gws, gn, S(stream));
 }
 
 // Shared front half of the two decoder norm+GEMM ops: factor (and, for an fp32 residual stream,
@@ -260,7 +312,7 @@ int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* weight_q
     a.rope = B(rope); a.q = Bm(Q); a.k = Bm(K); a.v = Bm(V); a.heads = heads; a.head_dim = head_dim;
     void* gws; size_t gn;
     gemm_ws(ws, ws_bytes, M, Kdim, &gws, &gn);
-    return launch_gemm_mma(a, gws, gn, S(stream));
+    return launch_gemm(a, gws, gn, S(stream));
 }
 
 int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* out, int queries, int keys,
@@ -297,7 +349,7 @@ int fvla_decoder_norm_gated_ffn(const void* x, int x_is_f32, const void* gate_w,
     a.B = B(gate_w); a.B2 = B(up_w); a.ldb = N; a.C = out; a.ldc = N;
     void* gws; size_t gn;
     gemm_ws(ws, ws_bytes, M, K, &gws, &gn);
-    return launch_gemm_mma(a, gws, gn, S(stream));
+    return launch_gemm(a, gws, gn, S(stream));
 }
 
 int fvla_decoder_action_out_proj(const void* x, int x_is_f32, const void* weight, const void* bias, void* out,

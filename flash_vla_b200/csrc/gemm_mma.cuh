@@ -206,6 +206,8 @@ __global__ void __launch_bounds__(WM * WN * 32) gemm_mma_kernel(const GemmArgs p
         __syncthreads();
         if (!s_last) return;
         __threadfence();
+        // Sum the splits in fixed order 0..splits-1 (deterministic). The split loop is the outer
+        // one so that each iteration issues all of this thread's loads before any is consumed.
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
@@ -213,18 +215,25 @@ __global__ void __launch_bounds__(WM * WN * 32) gemm_mma_kernel(const GemmArgs p
 #pragma unroll
                 for (int ni = 0; ni < NI; ++ni)
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        int row = row_base + mi * 16 + h * 8, col = col_base + ni * 8;
-                        float s0 = 0.f, s1 = 0.f;
-                        if (row < p.M && col < p.N) {
-                            for (int s = 0; s < p.splits; ++s) {
+                    for (int e = 0; e < 4; ++e) acc[nb][mi][ni][e] = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < p.splits; ++s) {
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int mi = 0; mi < MI; ++mi)
+#pragma unroll
+                    for (int ni = 0; ni < NI; ++ni)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            int row = row_base + mi * 16 + h * 8, col = col_base + ni * 8;
+                            if (row < p.M && col < p.N) {
                                 float2 v = __ldcg(reinterpret_cast<const float2*>(
                                     p.partial + nb * plane + ((size_t)s * p.M + row) * p.N + col));
-                                s0 += v.x; s1 += v.y;
+                                acc[nb][mi][ni][2 * h] += v.x; acc[nb][mi][ni][2 * h + 1] += v.y;
                             }
                         }
-                        acc[nb][mi][ni][2 * h] = s0; acc[nb][mi][ni][2 * h + 1] = s1;
-                    }
+        }
     }
 
 #pragma unroll
@@ -254,7 +263,7 @@ inline GemmPlan plan_gemm_mma(int M, int N, int K, bool dual) {
     g.splits = 1; g.k_per_split = (K + 63) / 64 * 64;
     if (g.skinny) {
         int ktiles = (K + 63) / 64;
-        int want = (296 + g.tiles_n - 1) / g.tiles_n;          // about two CTAs per SM
+        int want = (160 + g.tiles_n - 1) / g.tiles_n;          // about one CTA per SM
         int max_splits = ktiles / 2 > 0 ? ktiles / 2 : 1;      // at least 128 of K per split
         int s = want < max_splits ? want : max_splits;
         if (s < 1) s = 1;

@@ -1,0 +1,431 @@
+// Blackwell-native bf16 GEMM: TMA -> shared memory -> tcgen05.mma -> TMEM -> fused epilogue.
+//
+//   C[M,N] = epilogue(A[M,K] @ B[K,N])   (optionally two B operands: gated FFN)
+//
+// A is row-major with K contiguous ("K-major" operand); B is the checkpoint's (K, N) layout with
+// N contiguous, consumed in place as an "MN-major" operand, so no weight is ever re-packed.
+// One CTA computes 128 x BN output tiles in a persistent loop. Warp roles:
+//   warp 0     TMA producer: 128B-swizzled boxes of A (64 k x 128 rows) and B (64 n x 64 k rows)
+//              into a STAGES-deep ring, completion counted on mbarriers.
+//   warp 1     allocates TMEM; one elected lane issues tcgen05.mma (M=128, N=BN, K=16, fp32
+//              accumulate) and commits ring slots / accumulator stages back through mbarriers.
+//   warps 2-5  epilogue: tcgen05.ld of the accumulator (one TMEM lane = one output row per
+//              thread), bias / GELU / GeGLU / residual / RoPE+scatter in fp32, bf16 stores.
+// Accumulators are double-buffered in TMEM, so the epilogue of tile i overlaps the MMAs of
+// tile i+1. Every wait is bounded: when a limit is hit the kernel records a code in `status`
+// and every role leaves its loop; TMEM is released on all paths.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_mma.cuh"
+
+namespace fvla {
+namespace tc5 {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+// Bounded wait; false when the limit ran out (the caller then abandons its loop).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]; kind::f16 covers bf16 inputs with fp32 accumulation.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets
+// (all >> 4), version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;            // descriptor version for tcgen05
+    d |= (uint64_t)2 << 61;            // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor for kind::f16: fp32 accumulator, bf16 A (K-major) and B (MN-major).
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(BM >> 4) << 24);
+}
+
+struct Tc5Args {
+    GemmArgs g;                // epilogue description, shapes, C / R / bias / rope pointers
+    int tiles_m, tiles_n, k_iters;
+    int* status;               // device word: set non-zero when a bounded wait ran out
+};
+
+// Epilogue for 8 adjacent columns of one row (a: first / gate accumulator, u: up accumulator).
+template <bool DUAL>
+__device__ __forceinline__ void epilogue8(const GemmArgs& p, int row, int col, float (&a)[8], const float (&u)[8]) {
+    if (DUAL) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] = gelu_f(a[i]) * u[i];
+    }
+    if (p.bias) {
+        uint4 b = *reinterpret_cast<const uint4*>(p.bias + col);
+        float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
+        a[0] += b0.x; a[1] += b0.y; a[2] += b1.x; a[3] += b1.y; a[4] += b2.x; a[5] += b2.y; a[6] += b3.x; a[7] += b3.y;
+    }
+    if (p.act == 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] = gelu_f(a[i]);
+    } else if (p.act == 2) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] = silu_f(a[i]);
+    }
+    if (p.R) {
+        int rr = p.res_mod > 0 ? row % p.res_mod : row;
+        if (p.c_f32) {
+            const float4* r = reinterpret_cast<const float4*>(static_cast<const float*>(p.R) + (size_t)rr * p.ldr + col);
+            float4 r0 = r[0], r1 = r[1];
+            a[0] += r0.x; a[1] += r0.y; a[2] += r0.z; a[3] += r0.w; a[4] += r1.x; a[5] += r1.y; a[6] += r1.z; a[7] += r1.w;
+        } else {
+            uint4 r = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.R) + (size_t)rr * p.ldr + col);
+            float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y), r2 = unpack_bf16x2(r.z), r3 = unpack_bf16x2(r.w);
+            a[0] += r0.x; a[1] += r0.y; a[2] += r1.x; a[3] += r1.y; a[4] += r2.x; a[5] += r2.y; a[6] += r3.x; a[7] += r3.y;
+        }
+    }
+    bf16* dst;
+    if (p.rope) {
+        const int hd = p.head_dim, qd = p.heads * hd;
+        if (col < qd + hd) {
+            uint4 cs = *reinterpret_cast<const uint4*>(p.rope + (size_t)row * hd + (col % hd));
+            const uint32_t csw[4] = {cs.x, cs.y, cs.z, cs.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float x0 = a[2 * i], x1 = a[2 * i + 1];
+                if (p.round_first) { x0 = round_bf16(x0); x1 = round_bf16(x1); }
+                float2 c = unpack_bf16x2(csw[i]);
+                a[2 * i] = x0 * c.x - x1 * c.y;
+                a[2 * i + 1] = x1 * c.x + x0 * c.y;
+            }
+            dst = col < qd ? p.q + (size_t)row * qd + col : p.k + (size_t)row * hd + (col - qd);
+        } else {
+            dst = p.v + (size_t)row * hd + (col - qd - hd);
+        }
+    } else if (p.c_f32) {
+        float4* d = reinterpret_cast<float4*>(static_cast<float*>(p.C) + (size_t)row * p.ldc + col);
+        d[0] = make_float4(a[0], a[1], a[2], a[3]);
+        d[1] = make_float4(a[4], a[5], a[6], a[7]);
+        return;
+    } else {
+        dst = static_cast<bf16*>(p.C) + (size_t)row * p.ldc + col;
+    }
+    *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]),
+                                                pack_bf16x2(a[4], a[5]), pack_bf16x2(a[6], a[7]));
+}
+
+template <int BN, bool DUAL, int STAGES>
+struct Tc5Cfg {
+    static constexpr int NB = DUAL ? 2 : 1;
+    static constexpr int A_BYTES = BM * BK * 2;                 // 16 KB: 128 rows x 128 B
+    static constexpr int SLAB = BK * 128;                       // 8 KB: 64 k-rows x (64 n = 128 B)
+    static constexpr int B_BYTES = (BN / 64) * SLAB;
+    static constexpr int STAGE_BYTES = A_BYTES + NB * B_BYTES;
+    static constexpr int ACC_COLS = NB * BN;                    // TMEM columns per accumulator stage
+    static constexpr int TMEM_COLS = 2 * ACC_COLS <= 32 ? 32 : (2 * ACC_COLS <= 64 ? 64 : (2 * ACC_COLS <= 128 ? 128 : (2 * ACC_COLS <= 256 ? 256 : 512)));
+    static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BAR_BYTES;
+    static_assert(2 * ACC_COLS <= 512, "two accumulator stages must fit in TMEM");
+    static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN");
+};
+
+template <int BN, bool DUAL, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
+                const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2) {
+    using Cfg = Tc5Cfg<BN, DUAL, STAGES>;
+    constexpr int NB = Cfg::NB;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = smem_base + STAGES * Cfg::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + s * 8; };
+    auto empty_bar = [&](int s) { return bars + (STAGES + s) * 8; };
+    auto accfull_bar = [&](int a) { return bars + (2 * STAGES + a) * 8; };
+    auto accempty_bar = [&](int a) { return bars + (2 * STAGES + 2 + a) * 8; };
+    const uint32_t tmem_slot = bars + (2 * STAGES + 4) * 8;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES + (2 * STAGES + 4) * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + STAGES * Cfg::STAGE_BYTES + (2 * STAGES + 4) * 8 + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const GemmArgs& p = args.g;
+    const int num_tiles = args.tiles_m * args.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            prefetch_tensormap(&tmA);
+            prefetch_tensormap(&tmB);
+            if (DUAL) prefetch_tensormap(&tmB2);
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+                const int m0 = (tile % args.tiles_m) * BM, n0 = (tile / args.tiles_m) * BN;
+                for (int kt = 0; kt < args.k_iters; ++kt, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) goto producer_done;
+                    mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
+                    const uint32_t sA = smem_base + s * Cfg::STAGE_BYTES;
+                    tma_load_2d(sA, &tmA, full_bar(s), kt * BK, m0);
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(sA + Cfg::A_BYTES + nb * Cfg::B_BYTES + j * Cfg::SLAB, nb == 0 ? &tmB : &tmB2,
+                                        full_bar(s), n0 + j * 64, kt * BK);
+                }
+            }
+        }
+    producer_done:;
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BN);
+            uint32_t it = 0, tcount = 0;
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
+                const int acc = tcount & 1;
+                const uint32_t acc_ph = (tcount >> 1) & 1u;
+                if (!mbar_wait(accempty_bar(acc), acc_ph ^ 1u, abort_flag)) goto mma_done;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_COLS;
+                for (int kt = 0; kt < args.k_iters; ++kt, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(full_bar(s), ph, abort_flag)) goto mma_done;
+                    tc_fence_after();
+                    const uint32_t sA = smem_base + s * Cfg::STAGE_BYTES;
+#pragma unroll
+                    for (int k16 = 0; k16 < BK / 16; ++k16) {
+                        const uint64_t adesc = smem_desc(sA + k16 * 32, 16, 1024);
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb) {
+                            const uint64_t bdesc = smem_desc(sA + Cfg::A_BYTES + nb * Cfg::B_BYTES + k16 * 2048, Cfg::SLAB, 1024);
+                            umma_bf16(d_tmem + nb * BN, adesc, bdesc, idesc, (kt > 0 || k16 > 0) ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(empty_bar(s));              // slot reusable once these MMAs have read it
+                }
+                umma_commit(accfull_bar(acc));              // accumulator complete
+            }
+        }
+    mma_done:;
+    } else {
+        const int quad = warp & 3;                          // TMEM lanes [32*quad, 32*quad+32)
+        uint32_t tcount = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
+            const int acc = tcount & 1;
+            const uint32_t acc_ph = (tcount >> 1) & 1u;
+            const int m0 = (tile % args.tiles_m) * BM, n0 = (tile / args.tiles_m) * BN;
+            if (!mbar_wait(accfull_bar(acc), acc_ph, abort_flag)) break;
+            tc_fence_after();
+            const int row = m0 + quad * 32 + lane;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * Cfg::ACC_COLS;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                float a[32], u[32];
+                tmem_ld32(t_row + c, a);
+                if (DUAL) tmem_ld32(t_row + BN + c, u);
+                if (row < p.M) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        const int col = n0 + c + j;
+                        if (col < p.N) {
+                            float a8[8], u8[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) { a8[i] = a[j + i]; u8[i] = DUAL ? u[j + i] : 0.f; }
+                            epilogue8<DUAL>(p, row, col, a8, u8);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(accempty_bar(acc));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *abort_flag && args.status) atomicExch(args.status, 1);
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows of pitch `ld` elements;
+// box = box_inner x box_outer, 128-byte swizzle, out-of-bounds reads give zero.
+inline int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                    uint32_t box_inner, uint32_t box_outer) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return FVLA_ERR_LAUNCH; }
+    cuuint64_t gdim[2] = {inner, outer};
+    cuuint64_t gstride[1] = {ld * sizeof(bf16)};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r); return FVLA_ERR_ARG; }
+    return FVLA_OK;
+}
+
+inline int num_sms() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    return sms;
+}
+
+template <int BN, bool DUAL, int STAGES>
+inline int launch_tc5_cfg(const GemmArgs& g, int* status, cudaStream_t st) {
+    using Cfg = Tc5Cfg<BN, DUAL, STAGES>;
+    auto kern = tc5_gemm_kernel<BN, DUAL, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
+        configured = true;
+    }
+    CUtensorMap tmA, tmB, tmB2;
+    int rc = make_map(&tmA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, BM);
+    if (rc) return rc;
+    rc = make_map(&tmB, g.B, (uint64_t)g.N, (uint64_t)g.Kb, (uint64_t)g.ldb, 64, BK);
+    if (rc) return rc;
+    rc = make_map(&tmB2, DUAL ? g.B2 : g.B, (uint64_t)g.N, (uint64_t)g.Kb, (uint64_t)g.ldb, 64, BK);
+    if (rc) return rc;
+    Tc5Args a;
+    a.g = g;
+    a.tiles_m = (g.M + BM - 1) / BM;
+    a.tiles_n = (g.N + BN - 1) / BN;
+    a.k_iters = (g.K + BK - 1) / BK;
+    a.status = status;
+    int tiles = a.tiles_m * a.tiles_n;
+    int grid = tiles < num_sms() ? tiles : num_sms();
+    kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(a, tmA, tmB, tmB2);
+    return check_launch("tc5_gemm_kernel");
+}
+
+// Shapes this path takes: at least one full 128-row tile of work and 16-byte aligned rows.
+inline bool tc5_supports(const GemmArgs& g) {
+    return g.M > 64 && g.N % 8 == 0 && g.K % 8 == 0 && g.lda % 8 == 0 && g.ldb % 8 == 0 && g.row_scale == nullptr &&
+           aligned16(g.A) && aligned16(g.B) && (g.B2 == nullptr || aligned16(g.B2));
+}
+
+inline int launch_gemm_tc5(GemmArgs g, int* status, cudaStream_t st) {
+    if (g.Kb == 0) g.Kb = g.K;
+    if (g.B2 != nullptr) return launch_tc5_cfg<128, true, 4>(g, status, st);
+    return launch_tc5_cfg<128, false, 6>(g, status, st);
+}
+
+}  // namespace tc5
+}  // namespace fvla

@@ -34,6 +34,8 @@ SIGNATURES: dict[str, list] = {
 QUERIES: dict[str, tuple] = {
     "fvla_last_error": ([], c_char_p),
     "fvla_abi_version": ([], c_int),
+    "fvla_launch_count": ([], ctypes.c_ulonglong),
+    "fvla_device_status": ([_P], c_int),
     "fvla_gemm_workspace_bytes": ([_I, _I, _I, _I], c_size_t),
     "fvla_decoder_attention_workspace_bytes": ([_I, _I], c_size_t),
     "fvla_patch_embed_workspace_bytes": ([_I], c_size_t),

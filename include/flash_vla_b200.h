@@ -38,6 +38,12 @@ extern "C" {
 const char* fvla_last_error(void);
 /* ABI version of this header; bumped on any signature change. */
 int fvla_abi_version(void);
+/* Number of kernel launches this library has enqueued in this process so far (captured launches
+ * count once, at capture time). Lets a caller report how much of a pass ran in these kernels. */
+unsigned long long fvla_launch_count(void);
+/* Health word of the current device: 0, or 1 once a kernel gave up on one of its bounded waits
+ * (its output is then invalid). Negative: error code. This one call synchronises `stream`. */
+int fvla_device_status(void* stream);
 
 /* Scratch needed by a GEMM-shaped op of the given logical size. `dual` = 1 for gated FFNs. */
 size_t fvla_gemm_workspace_bytes(int M, int N, int K, int dual);

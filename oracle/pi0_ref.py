@@ -349,11 +349,12 @@ def allocate_buffers(num_views: int, chunk_size: int, prompt_len: int, dtype=tor
     return b, S
 
 
-def vision_encoder(ops, w, b, num_views):
+def vision_encoder(ops, w, b, num_views, layers=None):
+    """`layers` < 27 runs a prefix of the tower (used only for bounded timing samples)."""
     ops.vision_patch_embed(b["observation_images_normalized"], w["vision_patch_embedding_w"],
                            w["vision_patch_embedding_b"], w["vision_position_embedding"],
                            b["vision_x"])
-    for i in range(VISION_LAYERS):
+    for i in range(VISION_LAYERS if layers is None else layers):
         ops.vision_norm_qkv(b["vision_x"], w["vision_pre_attn_norm_w"][i],
                             w["vision_pre_attn_norm_b"][i], w["vision_attn_qkv_w"][i],
                             w["vision_attn_qkv_b"][i], b["vision_QKV"], b["vision_x_norm"])
@@ -367,15 +368,16 @@ def vision_encoder(ops, w, b, num_views):
                                      w["vision_ffn_down_b"][i], b["vision_x"], b["vision_x"])
 
 
-def transformer_encoder(ops, w, b, S):
+def transformer_encoder(ops, w, b, S, layers=None):
+    """`layers` < 18 runs that many full layers (used only for bounded timing samples)."""
     ops.encoder_projector(b["vision_x"], w["vision_final_norm_w"], w["vision_final_norm_b"],
                           w["encoder_multi_modal_projector_w"],
                           w["encoder_multi_modal_projector_b"], b["encoder_x"], b["vision_x_norm"])
-    for i in range(ENCODER_LAYERS):
+    for i in range(ENCODER_LAYERS if layers is None else layers):
         ops.encoder_norm_qkv_rope(b["encoder_x"], w["encoder_attn_qkv_w"][i],
                                   b["encoder_rope_weights"], b["encoder_Q"],
                                   b["encoder_K"][i, :S], b["encoder_V"][i, :S], b["encoder_x_norm"])
-        if i == ENCODER_LAYERS - 1:
+        if layers is None and i == ENCODER_LAYERS - 1:
             break
         ops.encoder_attention(b["encoder_Q"], b["encoder_K"][i, :S], b["encoder_V"][i, :S],
                               HEAD_DIM ** -0.5, b["encoder_attn"])
