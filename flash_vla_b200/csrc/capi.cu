@@ -10,6 +10,7 @@
 #include "common.cuh"
 #include "gemm_mma.cuh"
 #include "gemm_tc5.cuh"
+#include "gemm_skinny.cuh"
 #include "rowops.cuh"
 
 namespace fvla {
@@ -99,6 +100,13 @@ static bool tc5_enabled() {
         enabled = (v != nullptr && strcmp(v, "mma") == 0) ? 0 : 1;
     }
     return enabled == 1;
+}
+
+// FVLA_DEBUG_TIMESTAMPS=<device address, decimal> makes the skinny GEMM record per-CTA
+// globaltimer stamps there (development aid; unset in normal use).
+static unsigned long long* debug_timestamps() {
+    const char* v = getenv("FVLA_DEBUG_TIMESTAMPS");
+    return v ? reinterpret_cast<unsigned long long*>(strtoull(v, nullptr, 10)) : nullptr;
 }
 
 // GEMM dispatch: tcgen05 for M > 64, the warp-level kernel (with split-K) for the skinny shapes.
@@ -238,6 +246,12 @@ int fvla_encoder_attention(const void* Q, const void* K, const void* V, void* ou
 
 int fvla_linear_residual(const void* x, const void* weight, void* out, int out_is_f32, int M, int N, int K,
                          void* ws, size_t ws_bytes, void* stream) {
+    if (tc5_enabled() && skinny::plan_skinny(M, N, K, false).ok && aligned16(x) && aligned16(weight)) {
+        skinny::SkinnyArgs sa{};
+        sa.x = x; sa.x_f32 = 0; sa.ldx = K; sa.M = M; sa.N = N; sa.K = K;
+        sa.out = out; sa.out_f32 = out_is_f32; sa.ldo = N; sa.status = device_status_ptr(); sa.dbg = debug_timestamps();
+        return skinny::launch_skinny<skinny::EPI_RESIDUAL>(sa, weight, nullptr, N, S(stream));
+    }
     GemmArgs a;
     a.A = B(x); a.lda = K; a.B = B(weight); a.ldb = N; a.C = out; a.ldc = N; a.c_f32 = out_is_f32;
     a.R = out; a.ldr = N; a.M = M; a.N = N; a.K = K;
@@ -274,6 +288,13 @@ int fvla_decoder_small_proj(const void* x, int x_is_f32, const void* weight, con
             small_k_proj_kernel<bf16, bf16><<<grid, 256, 0, st>>>(B(x), B(weight), B(bias), Bm(out), M, N, K, act);
         return check_launch("small_k_proj_kernel");
     }
+    if (tc5_enabled() && skinny::plan_skinny(M, N, K, false).ok && aligned16(x) && aligned16(weight)) {
+        skinny::SkinnyArgs sa{};
+        sa.x = x; sa.x_f32 = x_is_f32; sa.ldx = K; sa.M = M; sa.N = N; sa.K = K;
+        sa.out = out; sa.out_f32 = out_is_f32; sa.ldo = N; sa.bias = B(bias); sa.act = act;
+        sa.status = device_status_ptr(); sa.dbg = debug_timestamps();
+        return skinny::launch_skinny<skinny::EPI_BIAS>(sa, weight, nullptr, N, S(stream));
+    }
     FVLA_REQUIRE(!x_is_f32, "small_proj: fp32 input only for K <= 64");
     GemmArgs a;
     a.A = B(x); a.lda = K; a.B = B(weight); a.ldb = N; a.C = out; a.ldc = N; a.c_f32 = out_is_f32;
@@ -305,6 +326,14 @@ int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* weight_q
                                void* K, void* V, void* norm_factor, int M, int Kdim, int heads, int head_dim,
                                void* ws, size_t ws_bytes, void* stream) {
     const int N = (heads + 2) * head_dim;
+    if (tc5_enabled() && skinny::plan_skinny(M, N, Kdim, false).ok && aligned16(x) && aligned16(weight_qkv) &&
+        head_dim % 2 == 0) {
+        skinny::SkinnyArgs sa{};
+        sa.x = x; sa.x_f32 = x_is_f32; sa.ldx = Kdim; sa.M = M; sa.N = N; sa.K = Kdim; sa.need_factor = 1;
+        sa.rope = B(rope); sa.q = Bm(Q); sa.k = Bm(K); sa.v = Bm(V); sa.heads = heads; sa.head_dim = head_dim;
+        sa.factor_out = Bm(norm_factor); sa.status = device_status_ptr(); sa.dbg = debug_timestamps();
+        return skinny::launch_skinny<skinny::EPI_QKV_ROPE>(sa, weight_qkv, nullptr, N, S(stream));
+    }
     GemmArgs a;
     int rc = decoder_norm_front(x, x_is_f32, norm_factor, M, N, Kdim, false, ws, ws_bytes, "decoder_norm_qkv_rope", &a, stream);
     if (rc) return rc;
@@ -343,6 +372,12 @@ int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* ou
 
 int fvla_decoder_norm_gated_ffn(const void* x, int x_is_f32, const void* gate_w, const void* up_w, void* out,
                                 void* norm_factor, int M, int N, int K, void* ws, size_t ws_bytes, void* stream) {
+    if (tc5_enabled() && skinny::plan_skinny(M, N, K, true).ok && aligned16(x) && aligned16(gate_w) && aligned16(up_w)) {
+        skinny::SkinnyArgs sa{};
+        sa.x = x; sa.x_f32 = x_is_f32; sa.ldx = K; sa.M = M; sa.N = N; sa.K = K; sa.need_factor = 1;
+        sa.out = out; sa.out_f32 = 0; sa.ldo = N; sa.factor_out = Bm(norm_factor); sa.status = device_status_ptr(); sa.dbg = debug_timestamps();
+        return skinny::launch_skinny<skinny::EPI_GEGLU>(sa, gate_w, up_w, N, S(stream));
+    }
     GemmArgs a;
     int rc = decoder_norm_front(x, x_is_f32, norm_factor, M, N, K, true, ws, ws_bytes, "decoder_norm_gated_ffn", &a, stream);
     if (rc) return rc;

@@ -8,6 +8,8 @@
 // deterministic, and resets its semaphore so a captured graph can be replayed.
 #pragma once
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace fvla {
@@ -28,9 +30,19 @@ struct GemmArgs {
     int splits = 1, k_per_split = 0; float* partial = nullptr; int* counters = nullptr;
 };
 
+// Residual values of one (row, col..col+1) pair. Loaded for every fragment BEFORE any store of
+// the epilogue: the residual may alias the destination, so the compiler cannot move a load above
+// an earlier store, and interleaving them would serialise one memory latency per fragment.
+__device__ __forceinline__ float2 load_residual_pair(const GemmArgs& p, int row, int col) {
+    int rr = p.res_mod > 0 ? row % p.res_mod : row;
+    return p.c_f32
+        ? *reinterpret_cast<const float2*>(static_cast<const float*>(p.R) + (size_t)rr * p.ldr + col)
+        : unpack_bf16x2(*reinterpret_cast<const uint32_t*>(static_cast<const bf16*>(p.R) + (size_t)rr * p.ldr + col));
+}
+
 template <bool DUAL>
 __device__ __forceinline__ void gemm_epilogue_pair(const GemmArgs& p, int row, int col, float a0,
-                                                   float a1, float u0, float u1) {
+                                                   float a1, float u0, float u1, float2 res) {
     if (p.row_scale) {
         float s = p.row_scale[row];
         a0 *= s; a1 *= s;
@@ -38,25 +50,19 @@ __device__ __forceinline__ void gemm_epilogue_pair(const GemmArgs& p, int row, i
     }
     if (DUAL) { a0 = gelu_f(a0) * u0; a1 = gelu_f(a1) * u1; }
     if (p.bias) {
-        float2 b = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p.bias + col));
+        float2 b = unpack_bf16x2(__ldg(reinterpret_cast<const uint32_t*>(p.bias + col)));
         a0 += b.x; a1 += b.y;
     }
     if (p.act == 1) { a0 = gelu_f(a0); a1 = gelu_f(a1); }
     else if (p.act == 2) { a0 = silu_f(a0); a1 = silu_f(a1); }
-    if (p.R) {
-        int rr = p.res_mod > 0 ? row % p.res_mod : row;
-        float2 r = p.c_f32
-            ? *reinterpret_cast<const float2*>(static_cast<const float*>(p.R) + (size_t)rr * p.ldr + col)
-            : unpack_bf16x2(*reinterpret_cast<const uint32_t*>(static_cast<const bf16*>(p.R) + (size_t)rr * p.ldr + col));
-        a0 += r.x; a1 += r.y;
-    }
+    a0 += res.x; a1 += res.y;
     if (p.rope) {
         const int hd = p.head_dim, qd = p.heads * hd;
         bf16* dst;
         if (col < qd + hd) {
             if (p.round_first) { a0 = round_bf16(a0); a1 = round_bf16(a1); }
             float2 cs = unpack_bf16x2(
-                *reinterpret_cast<const uint32_t*>(p.rope + (size_t)row * hd + (col % hd)));
+                __ldg(reinterpret_cast<const uint32_t*>(p.rope + (size_t)row * hd + (col % hd))));
             float r0 = a0 * cs.x - a1 * cs.y, r1 = a1 * cs.x + a0 * cs.y;
             a0 = r0; a1 = r1;
             dst = col < qd ? p.q + (size_t)row * qd + col : p.k + (size_t)row * hd + (col - qd);
@@ -236,6 +242,17 @@ __global__ void __launch_bounds__(WM * WN * 32) gemm_mma_kernel(const GemmArgs p
         }
     }
 
+    float2 res[MI][NI][2];
+#pragma unroll
+    for (int mi = 0; mi < MI; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < NI; ++ni)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                int row = row_base + mi * 16 + h * 8, col = col_base + ni * 8;
+                res[mi][ni][h] = (p.R && row < p.M && col < p.N) ? load_residual_pair(p, row, col)
+                                                                 : make_float2(0.f, 0.f);
+            }
 #pragma unroll
     for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
@@ -247,7 +264,7 @@ __global__ void __launch_bounds__(WM * WN * 32) gemm_mma_kernel(const GemmArgs p
                     gemm_epilogue_pair<DUAL>(p, row, col, acc[0][mi][ni][2 * h],
                                              acc[0][mi][ni][2 * h + 1],
                                              DUAL ? acc[NB - 1][mi][ni][2 * h] : 0.f,
-                                             DUAL ? acc[NB - 1][mi][ni][2 * h + 1] : 0.f);
+                                             DUAL ? acc[NB - 1][mi][ni][2 * h + 1] : 0.f, res[mi][ni][h]);
             }
 }
 
@@ -266,6 +283,7 @@ inline GemmPlan plan_gemm_mma(int M, int N, int K, bool dual) {
         int want = (160 + g.tiles_n - 1) / g.tiles_n;          // about one CTA per SM
         int max_splits = ktiles / 2 > 0 ? ktiles / 2 : 1;      // at least 128 of K per split
         int s = want < max_splits ? want : max_splits;
+        if (const char* dbg = getenv("FVLA_DEBUG_SPLITS")) s = atoi(dbg);
         if (s < 1) s = 1;
         int per = (ktiles + s - 1) / s;
         g.k_per_split = per * 64;

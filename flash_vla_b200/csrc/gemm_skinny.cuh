@@ -1,0 +1,445 @@
+// Weight-streaming GEMM for the action-expert decoder (M <= 64 tokens): out = x[M,K] @ W[K,N].
+//
+// These GEMMs are bound by the HBM read of W (5-17 MB per call, read once, always cold), so the
+// kernel is built around getting every byte of W in flight at once:
+//   * the problem is transposed: the 128-wide slice of N is the MMA's M (TMEM lanes), the tokens
+//     are its N = 64 (TMEM columns), so no tensor-core or shared-memory work is spent on padding
+//     51 rows to 128;
+//   * grid = (N / 128 tiles) x (S K-splits); each CTA owns a W[KC, 128] block, asks TMA for all
+//     of it at kernel start (<= 8 boxes of 64 k x 128 n, 128B-swizzled, used in place as an
+//     MN-major operand) and issues KC/16 tcgen05.mma into one TMEM accumulator;
+//   * the S CTAs of a K-split form a thread-block cluster. Each reads its partial accumulator
+//     from TMEM and scatters it over distributed shared memory so that CTA r receives the
+//     partials of its slice of tokens; after one cluster barrier CTA r sums them in rank order
+//     (deterministic) and runs the fused epilogue: RMS-factor + RoPE + scatter to Q/K/V, GeGLU,
+//     bias, or in-place residual add into the fp32 stream.
+// The activation operand is read straight from the residual stream (fp32 or bf16), converted to
+// bf16 in registers and written into the swizzled operand layout by the CTA itself; the per-token
+// sum of squares for the RMS factor is taken from the same registers and reduced with the
+// partials. No separate norm kernel, no global-memory scratch, no semaphores.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_tc5.cuh"
+
+namespace fvla {
+namespace skinny {
+
+using tc5::mbar_init;
+using tc5::mbar_expect_tx;
+using tc5::mbar_wait;
+using tc5::tma_load_2d;
+using tc5::smem_desc;
+
+constexpr int TN = 128;          // N columns per CTA (MMA M)
+constexpr int TOK = 64;          // token slots (MMA N)
+constexpr int MAX_KB = 8;        // k-blocks of 64 per CTA
+
+enum Epi { EPI_QKV_ROPE = 0, EPI_RESIDUAL = 1, EPI_GEGLU = 2, EPI_BIAS = 3 };
+
+struct SkinnyArgs {
+    const void* x; int x_f32; int ldx;        // activations [M, K]
+    int M, N, K;
+    int kblocks;                              // 64-wide k-blocks per CTA (K / 64 / splits)
+    int splits;                               // cluster size along K
+    int need_factor;                          // compute rsqrt(mean(x^2)+1e-6) per token
+    // epilogue operands
+    void* out; int out_f32; int ldo;          // RESIDUAL / BIAS / GEGLU destination
+    const bf16* bias; int act;
+    const bf16* rope; bf16* q; bf16* k; bf16* v; int heads, head_dim;
+    bf16* factor_out;                         // optional bf16 copy of the factors
+    int* status;
+    unsigned long long* dbg;                   // optional development aid: 8 globaltimer stamps per CTA
+};
+
+// MMA: A = W tile (MN-major, 128 n x 16 k), B = x tile (K-major, 64 tokens x 16 k), D fp32 128x64.
+__host__ __device__ constexpr uint32_t skinny_idesc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (0u << 16) | ((uint32_t)(TOK >> 3) << 17) |
+           ((uint32_t)(TN >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Shared memory map (offsets from a 1024-byte aligned base):
+//   W      max(kblocks, 2) x 16 KB  [kb][atom(2)][64 k rows x 128 B]  (atom = 64 of the tile's 128 n);
+//          after the MMAs it is reused as the staging area of this CTA's partial tile
+//          ([token 64][n 128] fp32 + 64 partial sums of squares)
+//   X      kblocks x 8 KB    [kb][64 tokens x 128 B]           (K-major, 128B swizzle)
+//   RED    S x TS x 128 fp32 = 32 KB   partials received from the S ranks, [src][token][n]
+//   SSQ    S x TS fp32       partial sums of squares received, [src][token]
+//   ssq_local 64 x 2 fp32, barriers, tmem slot, abort flag
+constexpr int THREADS = 512;
+
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define FVLA_STAMP(i) do { if (dbg && tid == 0) dbg[i] = gtime(); } while (0)
+
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster_addr, uint32_t src_cta_addr, uint32_t bytes,
+                                                 uint32_t mbar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst_cluster_addr), "r"(src_cta_addr), "r"(bytes), "r"(mbar_cluster_addr) : "memory");
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const int KB = p.kblocks, S = p.splits, TS = TOK / S;
+    const uint32_t w_bytes = (KB < 2 ? 2 : KB) * 16384u + 1024u;        // + room for the staged sums of squares
+    const uint32_t sW = base, sX = sW + w_bytes;
+    const uint32_t off_red = w_bytes + KB * 8192u;
+    float* stage = reinterpret_cast<float*>(gen);                                // aliases W
+    float* red = reinterpret_cast<float*>(gen + off_red);                        // [S][TS][128]
+    float* ssq_in = reinterpret_cast<float*>(gen + off_red + 32768);             // [S][TS]
+    float* ssq_local = reinterpret_cast<float*>(gen + off_red + 32768 + 256);    // [64][2]
+    const uint32_t off_bar = off_red + 32768 + 256 + 512;
+    const uint32_t bars = base + off_bar;                                        // KB full barriers, done, incoming
+    const uint32_t done_bar = bars + MAX_KB * 8, in_bar = bars + (MAX_KB + 1) * 8;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + off_bar + (MAX_KB + 2) * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + off_bar + (MAX_KB + 2) * 8 + 8);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    unsigned long long* dbg = p.dbg ? p.dbg + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8 : nullptr;
+    FVLA_STAMP(0);
+    const uint32_t rank = cluster_ctarank();                 // position along K within the cluster
+    const int tile = blockIdx.x;
+    const int k0 = (int)rank * KB * 64;
+    const int owners = (p.M + TS - 1) / TS;                  // ranks that own at least one real token
+    const bool i_own = (int)rank < owners;
+
+    if (tid == 0) {
+        for (int i = 0; i < KB; ++i) mbar_init(bars + i * 8, 1);
+        mbar_init(done_bar, 1);
+        mbar_init(in_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (i_own) mbar_expect_tx(in_bar, (uint32_t)S * (uint32_t)TS * (512u + (p.need_factor ? 4u : 0u)));
+        // all of this CTA's weights, requested at once
+        for (int kb = 0; kb < KB; ++kb) {
+            mbar_expect_tx(bars + kb * 8, 16384);
+            if (EPI == EPI_GEGLU) {
+                tma_load_2d(sW + kb * 16384, &tmW, bars + kb * 8, tile * 64, k0 + kb * 64);          // gate columns
+                tma_load_2d(sW + kb * 16384 + 8192, &tmW2, bars + kb * 8, tile * 64, k0 + kb * 64);  // up columns
+            } else {
+                tma_load_2d(sW + kb * 16384, &tmW, bars + kb * 8, tile * TN, k0 + kb * 64);
+                tma_load_2d(sW + kb * 16384 + 8192, &tmW, bars + kb * 8, tile * TN + 64, k0 + kb * 64);
+            }
+        }
+    }
+    __syncwarp();
+    if (warp == 0) {
+        tc5::tmem_alloc(base + off_bar + (MAX_KB + 2) * 8, 64);
+        tc5::tmem_relinquish();
+    }
+    // Programmatic dependent launch: everything above touched only weights and this CTA's own
+    // shared memory, so it may run while the previous kernel in the stream is still finishing.
+    // From here on activations written by that kernel are read, so wait for it; then let the
+    // next kernel in the stream start its own prologue.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // Tell the cluster this CTA is running (barriers initialised); peers wait for that before
+    // sending anything into its shared memory.
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+
+    // Epilogue operands that do not depend on the product (RoPE entries, residual values, bias) are
+    // fetched now, so that their latency overlaps the weight stream instead of following the MMA.
+    // Owner work is spread as: n = tid % 128, tokens tl = tid / 128 + 4 j.
+    const int n_local = tid & 127, tg = tid >> 7;
+    constexpr int PRE = 8;                                    // TS <= 32 -> at most 8 tokens per thread
+    uint32_t pre[PRE];
+    float bias_v = 0.f;
+    {
+        const int n = tile * TN + n_local;
+        if (EPI == EPI_BIAS) bias_v = __bfloat162float(__ldg(p.bias + n));
+#pragma unroll
+        for (int j = 0; j < PRE; ++j) {
+            pre[j] = 0u;
+            const int tl = tg + 4 * j;
+            const int token = (int)rank * TS + tl;
+            if (tl < TS && token < p.M) {
+                if (EPI == EPI_QKV_ROPE) {
+                    if (n < (p.heads + 1) * p.head_dim)
+                        pre[j] = __ldg(reinterpret_cast<const uint32_t*>(p.rope + (size_t)token * p.head_dim + ((n % p.head_dim) & ~1)));
+                } else if (EPI == EPI_RESIDUAL) {
+                    pre[j] = p.out_f32 ? __float_as_uint(static_cast<const float*>(p.out)[(size_t)token * p.ldo + n])
+                                       : __float_as_uint(__bfloat162float(static_cast<const bf16*>(p.out)[(size_t)token * p.ldo + n]));
+                }
+            }
+        }
+    }
+
+    FVLA_STAMP(1);
+    // Activation slice -> bf16 K-major operand (manual 128B swizzle), plus partial sums of squares.
+    // Each thread has four 32-byte loads in flight at a time.
+    {
+        const int chunks_per_row = KB * 8;                   // 16-byte (8 x bf16) chunks per token
+        const int total = TOK * chunks_per_row;              // 512 (KB = 1) ... 4096 (KB = 8)
+        for (int it0 = 0; it0 * THREADS < total; it0 += 4) {
+            float4 ra[4], rb[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = (it0 + u) * THREADS + tid;
+                const int t = idx / chunks_per_row, c = idx % chunks_per_row;
+                ra[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                rb[u] = ra[u];
+                if (idx < total && t < p.M) {
+                    const size_t off = (size_t)t * p.ldx + k0 + c * 8;
+                    if (p.x_f32) {
+                        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + off);
+                        ra[u] = src[0];
+                        rb[u] = src[1];
+                    } else {
+                        uint4 a = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.x) + off);
+                        float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+                        ra[u] = make_float4(f0.x, f0.y, f1.x, f1.y);
+                        rb[u] = make_float4(f2.x, f2.y, f3.x, f3.y);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = (it0 + u) * THREADS + tid;
+                if ((it0 + u) * THREADS < total) {           // uniform across the CTA
+                    const int t = idx / chunks_per_row, c = idx % chunks_per_row;
+                    const int kb = c >> 3, cc = c & 7;
+                    uint4 packed = make_uint4(pack_bf16x2(ra[u].x, ra[u].y), pack_bf16x2(ra[u].z, ra[u].w),
+                                              pack_bf16x2(rb[u].x, rb[u].y), pack_bf16x2(rb[u].z, rb[u].w));
+                    *reinterpret_cast<uint4*>(gen + w_bytes + kb * 8192 + t * 128 + ((cc ^ (t & 7)) << 4)) = packed;
+                    if (p.need_factor) {
+                        float ss = ra[u].x * ra[u].x + ra[u].y * ra[u].y + ra[u].z * ra[u].z + ra[u].w * ra[u].w +
+                                   rb[u].x * rb[u].x + rb[u].y * rb[u].y + rb[u].z * rb[u].z + rb[u].w * rb[u].w;
+                        // chunks of one token sit in consecutive lanes: reduce over groups of min(32, chunks_per_row)
+                        const int group = chunks_per_row < 32 ? chunks_per_row : 32;
+                        for (int o = group >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                        if ((lane & (group - 1)) == 0) ssq_local[t * 2 + (c >> 5)] = ss;      // slot 1 only when KB = 8
+                    }
+                }
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
+    }
+    tc5::tc_fence_before();
+    __syncthreads();
+    tc5::tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    FVLA_STAMP(2);
+
+    if (tid == 0) {
+        constexpr uint32_t idesc = skinny_idesc();
+        bool ok = true;
+        for (int kb = 0; kb < KB && ok; ++kb) {
+            ok = mbar_wait(bars + kb * 8, 0, abort_flag);
+            tc5::tc_fence_after();
+            if (!ok) break;
+#pragma unroll
+            for (int k16 = 0; k16 < 4; ++k16) {
+                const uint64_t adesc = smem_desc(sW + kb * 16384 + k16 * 2048, 8192, 1024);
+                const uint64_t bdesc = smem_desc(sX + kb * 8192 + k16 * 32, 16, 1024);
+                tc5::umma_bf16(tmem, adesc, bdesc, idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
+            }
+        }
+        tc5::umma_commit(done_bar);
+    }
+    __syncwarp();
+    const bool done = mbar_wait(done_bar, 0, abort_flag);
+    tc5::tc_fence_after();
+    FVLA_STAMP(3);
+
+    // Stage this CTA's partial tile as [token][n] fp32 over the (now idle) weight region.
+    if (warp < 4) {
+        float lo[32], hi[32];
+        tc5::tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16), lo);
+        tc5::tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + 32, hi);
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+            stage[t * TN + tid] = done ? lo[t] : 0.f;
+            stage[(32 + t) * TN + tid] = done ? hi[t] : 0.f;
+        }
+    } else if (p.need_factor && tid >= 128 && tid < 128 + TOK) {
+        const int t = tid - 128;
+        stage[TOK * TN + t] = t < p.M ? ssq_local[t * 2] + (KB == 8 ? ssq_local[t * 2 + 1] : 0.f) : 0.f;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // staging writes -> visible to the bulk copies
+    tc5::tc_fence_before();
+    __syncthreads();
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // every peer has initialised its barriers
+    if (tid == 0) {
+        // one bulk copy per owner: its slice of tokens goes to slot [src = my rank] of its RED buffer
+        for (int r = 0; r < owners; ++r) {
+            bulk_copy_to_cta(map_to_cta(base + off_red + (uint32_t)(rank * TS) * 512u, (uint32_t)r),
+                             base + (uint32_t)(r * TS) * 512u, (uint32_t)TS * 512u, map_to_cta(in_bar, (uint32_t)r));
+            if (p.need_factor)
+                bulk_copy_to_cta(map_to_cta(base + off_red + 32768 + (uint32_t)(rank * TS) * 4u, (uint32_t)r),
+                                 base + (uint32_t)(TOK * TN) * 4u + (uint32_t)(r * TS) * 4u, (uint32_t)TS * 4u,
+                                 map_to_cta(in_bar, (uint32_t)r));
+        }
+    }
+
+    FVLA_STAMP(4);
+    // Owner phase: this CTA finishes tokens [rank*TS, rank*TS + TS), summing partials in rank order.
+    if (i_own) {
+        mbar_wait(in_bar, 0, abort_flag);
+        FVLA_STAMP(5);
+#pragma unroll
+        for (int j = 0; j < PRE; ++j) {
+            const int tl = tg + 4 * j;
+            const int token = (int)rank * TS + tl;
+            if (tl >= TS || token >= p.M) continue;
+            float sum = 0.f;
+            for (int s = 0; s < S; ++s) sum += red[(s * TS + tl) * TN + n_local];
+            float factor = 1.f;
+            if (p.need_factor) {
+                float ss = 0.f;
+                for (int s = 0; s < S; ++s) ss += ssq_in[s * TS + tl];
+                factor = rsqrtf(ss / (float)p.K + 1e-6f);
+                if (p.factor_out && tile == 0 && n_local == 0) p.factor_out[token] = __float2bfloat16_rn(factor);
+            }
+            if (EPI == EPI_QKV_ROPE) {
+                const int n = tile * TN + n_local;
+                float v = sum * factor;
+                const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+                const int hd = p.head_dim, qd = p.heads * hd;
+                bf16* dst;
+                if (n < qd + hd) {
+                    const float2 cs = unpack_bf16x2(pre[j]);
+                    v = (n & 1) ? v * cs.x + partner * cs.y : v * cs.x - partner * cs.y;
+                    dst = n < qd ? p.q + (size_t)token * qd + n : p.k + (size_t)token * hd + (n - qd);
+                } else {
+                    dst = p.v + (size_t)token * hd + (n - qd - hd);
+                }
+                *dst = __float2bfloat16_rn(v);
+            } else if (EPI == EPI_GEGLU) {
+                // lanes 0..63 of the tile hold gate columns, 64..127 the matching up columns
+                if (n_local < 64) {
+                    float up = 0.f;
+                    for (int s = 0; s < S; ++s) up += red[(s * TS + tl) * TN + n_local + 64];
+                    const float g = sum * factor, u = up * factor;
+                    static_cast<bf16*>(p.out)[(size_t)token * p.ldo + tile * 64 + n_local] = __float2bfloat16_rn(gelu_f(g) * u);
+                }
+            } else {
+                const int n = tile * TN + n_local;
+                float v = sum;
+                if (EPI == EPI_BIAS) {
+                    v += bias_v;
+                    if (p.act == 2) v = silu_f(v);
+                }
+                if (EPI == EPI_RESIDUAL) v += __uint_as_float(pre[j]);
+                if (p.out_f32) static_cast<float*>(p.out)[(size_t)token * p.ldo + n] = v;
+                else static_cast<bf16*>(p.out)[(size_t)token * p.ldo + n] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+
+    // No CTA may leave while a peer can still be reading its staging area: once every owner has
+    // received all of its slices, every outgoing copy of every CTA has completed.
+    FVLA_STAMP(6);
+    tc5::tc_fence_before();
+    cluster_sync_all();
+    if (warp == 0) {
+        tc5::tc_fence_after();
+        tc5::tmem_dealloc(tmem, 64);
+    }
+    FVLA_STAMP(7);
+    if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 2);
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+struct SkinnyPlan { int splits, kblocks, tiles; size_t smem; bool ok; };
+
+inline SkinnyPlan plan_skinny(int M, int N, int K, bool geglu) {
+    SkinnyPlan pl{};
+    pl.ok = false;
+    const int tile_n = geglu ? 64 : TN;
+    if (M <= 0 || M > TOK || N % tile_n || K % 64) return pl;
+    pl.tiles = N / tile_n;
+    const int kb_total = K / 64;
+    // largest cluster (<= 8) that divides the k-blocks, keeps <= 8 k-blocks per CTA and stays near one wave
+    int best = 0;
+    for (int s = 1; s <= 8; s *= 2) {       // 8 = largest portable cluster; larger ones schedule in waves
+        if (kb_total % s) continue;
+        const int kb = kb_total / s;
+        if (kb > MAX_KB || kb < 1 || (kb & (kb - 1))) continue;
+        if (pl.tiles * s > 148 && best) break;
+        best = s;
+    }
+    if (!best) return pl;
+    pl.splits = best;
+    pl.kblocks = kb_total / best;
+    pl.smem = 1024 + (size_t)(pl.kblocks < 2 ? 2 : pl.kblocks) * 16384 + 1024 + (size_t)pl.kblocks * 8192 + 32768 + 256 + 512 +
+              (MAX_KB + 2) * 8 + 32;
+    pl.ok = true;
+    return pl;
+}
+
+// FVLA_PDL=0 turns programmatic dependent launch off (diagnostic switch).
+inline bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* v = getenv("FVLA_PDL");
+        on = (v != nullptr && v[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <int EPI>
+inline int launch_skinny(SkinnyArgs a, const void* W, const void* W2, int ldw, cudaStream_t st) {
+    SkinnyPlan pl = plan_skinny(a.M, a.N, a.K, EPI == EPI_GEGLU);
+    if (!pl.ok) { set_error("skinny gemm: shape %dx%dx%d not supported", a.M, a.N, a.K); return FVLA_ERR_UNSUPPORTED; }
+    a.splits = pl.splits; a.kblocks = pl.kblocks;
+    auto kern = skinny_gemm_kernel<EPI>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
+        configured = true;
+    }
+    CUtensorMap tmW, tmW2;
+    int rc = tc5::make_map(&tmW, W, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)ldw, 64, 64);
+    if (rc) return rc;
+    rc = tc5::make_map(&tmW2, W2 ? W2 : W, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)ldw, 64, 64);
+    if (rc) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(pl.tiles, pl.splits, 1);
+    cfg.blockDim = dim3(THREADS, 1, 1);
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = pl.splits;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, tmW, tmW2);
+    if (e != cudaSuccess) { set_error("skinny_gemm_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
+    return check_launch("skinny_gemm_kernel");
+}
+
+}  // namespace skinny
+}  // namespace fvla

@@ -129,14 +129,17 @@ struct Tc5Args {
 };
 
 // Epilogue for 8 adjacent columns of one row (a: first / gate accumulator, u: up accumulator).
+// `rpre`: the bf16 residual of these 8 columns, loaded by the caller before any store of the tile
+// (the residual may alias the destination, so loads issued after a store would each wait for it).
 template <bool DUAL>
-__device__ __forceinline__ void epilogue8(const GemmArgs& p, int row, int col, float (&a)[8], const float (&u)[8]) {
+__device__ __forceinline__ void epilogue8(const GemmArgs& p, int row, int col, float (&a)[8], const float (&u)[8],
+                                          uint4 rpre) {
     if (DUAL) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) a[i] = gelu_f(a[i]) * u[i];
     }
     if (p.bias) {
-        uint4 b = *reinterpret_cast<const uint4*>(p.bias + col);
+        uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
         float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
         a[0] += b0.x; a[1] += b0.y; a[2] += b1.x; a[3] += b1.y; a[4] += b2.x; a[5] += b2.y; a[6] += b3.x; a[7] += b3.y;
     }
@@ -154,7 +157,7 @@ __device__ __forceinline__ void epilogue8(const GemmArgs& p, int row, int col, f
             float4 r0 = r[0], r1 = r[1];
             a[0] += r0.x; a[1] += r0.y; a[2] += r0.z; a[3] += r0.w; a[4] += r1.x; a[5] += r1.y; a[6] += r1.z; a[7] += r1.w;
         } else {
-            uint4 r = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.R) + (size_t)rr * p.ldr + col);
+            uint4 r = rpre;
             float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y), r2 = unpack_bf16x2(r.z), r3 = unpack_bf16x2(r.w);
             a[0] += r0.x; a[1] += r0.y; a[2] += r1.x; a[3] += r1.y; a[4] += r2.x; a[5] += r2.y; a[6] += r3.x; a[7] += r3.y;
         }
@@ -163,7 +166,7 @@ __device__ __forceinline__ void epilogue8(const GemmArgs& p, int row, int col, f
     if (p.rope) {
         const int hd = p.head_dim, qd = p.heads * hd;
         if (col < qd + hd) {
-            uint4 cs = *reinterpret_cast<const uint4*>(p.rope + (size_t)row * hd + (col % hd));
+            uint4 cs = __ldg(reinterpret_cast<const uint4*>(p.rope + (size_t)row * hd + (col % hd)));
             const uint32_t csw[4] = {cs.x, cs.y, cs.z, cs.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -304,11 +307,22 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
             const int acc = tcount & 1;
             const uint32_t acc_ph = (tcount >> 1) & 1u;
             const int m0 = (tile % args.tiles_m) * BM, n0 = (tile / args.tiles_m) * BN;
+            const int row = m0 + quad * 32 + lane;
+            // bf16 residual of this thread's whole output row, fetched while the MMAs still run
+            uint4 rpre[BN / 8];
+            if (!DUAL && p.R && !p.c_f32 && row < p.M) {
+                const int rr = p.res_mod > 0 ? row % p.res_mod : row;
+                const bf16* rrow = static_cast<const bf16*>(p.R) + (size_t)rr * p.ldr + n0;
+#pragma unroll
+                for (int j = 0; j < BN / 8; ++j)
+                    rpre[j] = (n0 + j * 8 < p.N) ? *reinterpret_cast<const uint4*>(rrow + j * 8) : make_uint4(0, 0, 0, 0);
+            }
             if (!mbar_wait(accfull_bar(acc), acc_ph, abort_flag)) break;
             tc_fence_after();
-            const int row = m0 + quad * 32 + lane;
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * Cfg::ACC_COLS;
-#pragma unroll 1
+            // fully unrolled when a residual is preloaded (register array indexed by chunk);
+            // the gated form keeps one chunk live at a time
+#pragma unroll(DUAL ? 1 : BN / 32)
             for (int c = 0; c < BN; c += 32) {
                 float a[32], u[32];
                 tmem_ld32(t_row + c, a);
@@ -321,7 +335,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                             float a8[8], u8[8];
 #pragma unroll
                             for (int i = 0; i < 8; ++i) { a8[i] = a[j + i]; u8[i] = DUAL ? u[j + i] : 0.f; }
-                            epilogue8<DUAL>(p, row, col, a8, u8);
+                            epilogue8<DUAL>(p, row, col, a8, u8, DUAL ? make_uint4(0, 0, 0, 0) : rpre[(c + j) / 8]);
                         }
                     }
                 }
