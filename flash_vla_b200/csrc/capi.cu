@@ -353,6 +353,15 @@ int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* ou
         set_error("decoder_attention: workspace of %zu bytes needed", fvla_decoder_attention_workspace_bytes(queries, keys));
         return FVLA_ERR_WORKSPACE;
     }
+    if (tc5_enabled() && keys <= 1024) {        // cluster kernel: 8 key splits of at most 128 keys
+        DecAttnArgs d{};
+        d.q = B(Q); d.k = B(K); d.v = B(V); d.out = Bm(out);
+        d.nq = queries; d.nk = keys; d.keys_per_split = ((keys + 7) / 8 + 7) / 8 * 8;
+        d.scale_log2 = kLog2e / sqrtf((float)head_dim);
+        d.mask_rows = heads; d.mask_key_le = encoder_seq_len; d.prefix_keys = encoder_seq_len;
+        d.status = device_status_ptr();
+        return launch_decoder_attention_cluster(d, skinny::pdl_enabled(), S(stream));
+    }
     const int splits = (keys + 127) / 128;
     const int qpad = (queries + 63) / 64 * 64;
     AttnArgs a{};

@@ -19,9 +19,9 @@ constexpr float kLog2e = 1.4426950408889634f;
 // kernels (kernels/base.py:77-78), which is algebraically the tanh approximation.
 __device__ __forceinline__ float gelu_f(float v) {
     float t = kGeluC0 * v * (1.0f + kGeluC1 * v * v);
-    return v / (1.0f + __expf(-t));
+    return __fdividef(v, 1.0f + __expf(-t));
 }
-__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + __expf(-v)); }
+__device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

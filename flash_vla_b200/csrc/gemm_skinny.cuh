@@ -103,7 +103,8 @@ __device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster_addr, uint
 
 template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
-skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2) {
+skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2,
+                   const __grid_constant__ CUtensorMap tmX) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
@@ -130,23 +131,29 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
     const int owners = (p.M + TS - 1) / TS;                  // ranks that own at least one real token
     const bool i_own = (int)rank < owners;
 
+    // bf16 activations are fetched by TMA straight into the operand layout (rows past M read as
+    // zero); fp32 activations are converted by the CTA further down.
+    const bool x_by_tma = !p.x_f32;
     if (tid == 0) {
-        for (int i = 0; i < KB; ++i) mbar_init(bars + i * 8, 1);
         mbar_init(done_bar, 1);
         mbar_init(in_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         if (i_own) mbar_expect_tx(in_bar, (uint32_t)S * (uint32_t)TS * (512u + (p.need_factor ? 4u : 0u)));
-        // all of this CTA's weights, requested at once
-        for (int kb = 0; kb < KB; ++kb) {
-            mbar_expect_tx(bars + kb * 8, 16384);
-            if (EPI == EPI_GEGLU) {
-                tma_load_2d(sW + kb * 16384, &tmW, bars + kb * 8, tile * 64, k0 + kb * 64);          // gate columns
-                tma_load_2d(sW + kb * 16384 + 8192, &tmW2, bars + kb * 8, tile * 64, k0 + kb * 64);  // up columns
-            } else {
-                tma_load_2d(sW + kb * 16384, &tmW, bars + kb * 8, tile * TN, k0 + kb * 64);
-                tma_load_2d(sW + kb * 16384 + 8192, &tmW, bars + kb * 8, tile * TN + 64, k0 + kb * 64);
-            }
+    }
+    // One lane per k-block sets up that block's barrier and requests its weights: all of this
+    // CTA's share of W is in flight within a few hundred cycles of kernel start.
+    if (lane == 0 && warp < KB) {
+        const int kb = warp;
+        mbar_init(bars + kb * 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(bars + kb * 8, x_by_tma ? 16384 + 8192 : 16384);
+        if (EPI == EPI_GEGLU) {
+            tma_load_2d(sW + kb * 16384, &tmW, bars + kb * 8, tile * 64, k0 + kb * 64);          // gate columns
+            tma_load_2d(sW + kb * 16384 + 8192, &tmW2, bars + kb * 8, tile * 64, k0 + kb * 64);  // up columns
+        } else {
+            tma_load_2d(sW + kb * 16384, &tmW, bars + kb * 8, tile * TN, k0 + kb * 64);
+            tma_load_2d(sW + kb * 16384 + 8192, &tmW, bars + kb * 8, tile * TN + 64, k0 + kb * 64);
         }
     }
     __syncwarp();
@@ -160,33 +167,44 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
     // next kernel in the stream start its own prologue.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (x_by_tma && lane == 0 && warp < KB)
+        tma_load_2d(sX + warp * 8192, &tmX, bars + warp * 8, k0 + warp * 64, 0);
     // Tell the cluster this CTA is running (barriers initialised); peers wait for that before
     // sending anything into its shared memory.
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
     // Epilogue operands that do not depend on the product (RoPE entries, residual values, bias) are
     // fetched now, so that their latency overlaps the weight stream instead of following the MMA.
-    // Owner work is spread as: n = tid % 128, tokens tl = tid / 128 + 4 j.
-    const int n_local = tid & 127, tg = tid >> 7;
-    constexpr int PRE = 8;                                    // TS <= 32 -> at most 8 tokens per thread
-    uint32_t pre[PRE];
-    float bias_v = 0.f;
-    {
-        const int n = tile * TN + n_local;
-        if (EPI == EPI_BIAS) bias_v = __bfloat162float(__ldg(p.bias + n));
+    // Owner work items: (token of this rank's slice) x (group of 4 adjacent columns).
+    constexpr int QPT = (EPI == EPI_GEGLU) ? 16 : 32;         // column quads per token
+    constexpr int PRE = 4;                                    // TS * QPT <= 2048 = 4 x THREADS
+    const int items = TS * QPT;
+    uint4 pre[PRE];
 #pragma unroll
-        for (int j = 0; j < PRE; ++j) {
-            pre[j] = 0u;
-            const int tl = tg + 4 * j;
-            const int token = (int)rank * TS + tl;
-            if (tl < TS && token < p.M) {
-                if (EPI == EPI_QKV_ROPE) {
-                    if (n < (p.heads + 1) * p.head_dim)
-                        pre[j] = __ldg(reinterpret_cast<const uint32_t*>(p.rope + (size_t)token * p.head_dim + ((n % p.head_dim) & ~1)));
-                } else if (EPI == EPI_RESIDUAL) {
-                    pre[j] = p.out_f32 ? __float_as_uint(static_cast<const float*>(p.out)[(size_t)token * p.ldo + n])
-                                       : __float_as_uint(__bfloat162float(static_cast<const bf16*>(p.out)[(size_t)token * p.ldo + n]));
+    for (int j = 0; j < PRE; ++j) {
+        pre[j] = make_uint4(0, 0, 0, 0);
+        const int item = tid + j * THREADS;
+        const int tl = item / QPT, c4 = (item % QPT) * 4;
+        const int token = (int)rank * TS + tl;
+        if (item < items && token < p.M) {
+            const int n = tile * TN + c4;
+            if (EPI == EPI_QKV_ROPE) {
+                if (n < (p.heads + 1) * p.head_dim) {
+                    const uint2 cs = __ldg(reinterpret_cast<const uint2*>(p.rope + (size_t)token * p.head_dim + (n % p.head_dim)));
+                    pre[j].x = cs.x; pre[j].y = cs.y;
                 }
+            } else if (EPI == EPI_RESIDUAL) {
+                if (p.out_f32) {
+                    pre[j] = *reinterpret_cast<const uint4*>(static_cast<const float*>(p.out) + (size_t)token * p.ldo + n);
+                } else {
+                    const uint2 r = *reinterpret_cast<const uint2*>(static_cast<const bf16*>(p.out) + (size_t)token * p.ldo + n);
+                    const float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y);
+                    pre[j] = make_uint4(__float_as_uint(r0.x), __float_as_uint(r0.y), __float_as_uint(r1.x), __float_as_uint(r1.y));
+                }
+            } else if (EPI == EPI_BIAS) {
+                const uint2 bv = __ldg(reinterpret_cast<const uint2*>(p.bias + n));
+                const float2 b0 = unpack_bf16x2(bv.x), b1 = unpack_bf16x2(bv.y);
+                pre[j] = make_uint4(__float_as_uint(b0.x), __float_as_uint(b0.y), __float_as_uint(b1.x), __float_as_uint(b1.y));
             }
         }
     }
@@ -194,7 +212,7 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
     FVLA_STAMP(1);
     // Activation slice -> bf16 K-major operand (manual 128B swizzle), plus partial sums of squares.
     // Each thread has four 32-byte loads in flight at a time.
-    {
+    if (!x_by_tma) {
         const int chunks_per_row = KB * 8;                   // 16-byte (8 x bf16) chunks per token
         const int total = TOK * chunks_per_row;              // 512 (KB = 1) ... 4096 (KB = 8)
         for (int it0 = 0; it0 * THREADS < total; it0 += 4) {
@@ -206,17 +224,9 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
                 ra[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                 rb[u] = ra[u];
                 if (idx < total && t < p.M) {
-                    const size_t off = (size_t)t * p.ldx + k0 + c * 8;
-                    if (p.x_f32) {
-                        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + off);
-                        ra[u] = src[0];
-                        rb[u] = src[1];
-                    } else {
-                        uint4 a = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.x) + off);
-                        float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
-                        ra[u] = make_float4(f0.x, f0.y, f1.x, f1.y);
-                        rb[u] = make_float4(f2.x, f2.y, f3.x, f3.y);
-                    }
+                    const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + (size_t)t * p.ldx + k0 + c * 8);
+                    ra[u] = src[0];
+                    rb[u] = src[1];
                 }
             }
 #pragma unroll
@@ -240,6 +250,18 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
             }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
+    } else if (p.need_factor) {
+        // bf16 activations: sums of squares over this CTA's K slice, straight from global memory
+        for (int t = warp; t < p.M; t += THREADS / 32) {
+            float ss = 0.f;
+            for (int c = lane; c < KB * 8; c += 32) {
+                uint4 a = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.x) + (size_t)t * p.ldx + k0 + c * 8);
+                float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+                ss += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y + f2.x * f2.x + f2.y * f2.y + f3.x * f3.x + f3.y * f3.y;
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) { ssq_local[t * 2] = ss; ssq_local[t * 2 + 1] = 0.f; }
+        }
     }
     tc5::tc_fence_before();
     __syncthreads();
@@ -305,50 +327,59 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
         FVLA_STAMP(5);
 #pragma unroll
         for (int j = 0; j < PRE; ++j) {
-            const int tl = tg + 4 * j;
+            const int item = tid + j * THREADS;
+            const int tl = item / QPT, c4 = (item % QPT) * 4;
             const int token = (int)rank * TS + tl;
-            if (tl >= TS || token >= p.M) continue;
-            float sum = 0.f;
-            for (int s = 0; s < S; ++s) sum += red[(s * TS + tl) * TN + n_local];
+            if (item >= items || token >= p.M) continue;
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < S; ++s) {
+                const float4 v = *reinterpret_cast<const float4*>(red + (s * TS + tl) * TN + c4);
+                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+            }
             float factor = 1.f;
             if (p.need_factor) {
                 float ss = 0.f;
                 for (int s = 0; s < S; ++s) ss += ssq_in[s * TS + tl];
-                factor = rsqrtf(ss / (float)p.K + 1e-6f);
-                if (p.factor_out && tile == 0 && n_local == 0) p.factor_out[token] = __float2bfloat16_rn(factor);
+                factor = rsqrtf(ss * (1.0f / (float)p.K) + 1e-6f);
+                if (p.factor_out && tile == 0 && c4 == 0) p.factor_out[token] = __float2bfloat16_rn(factor);
             }
+            const int n = tile * TN + c4;
             if (EPI == EPI_QKV_ROPE) {
-                const int n = tile * TN + n_local;
-                float v = sum * factor;
-                const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+                float v0 = sum.x * factor, v1 = sum.y * factor, v2 = sum.z * factor, v3 = sum.w * factor;
                 const int hd = p.head_dim, qd = p.heads * hd;
                 bf16* dst;
                 if (n < qd + hd) {
-                    const float2 cs = unpack_bf16x2(pre[j]);
-                    v = (n & 1) ? v * cs.x + partner * cs.y : v * cs.x - partner * cs.y;
+                    const float2 c0 = unpack_bf16x2(pre[j].x), c1 = unpack_bf16x2(pre[j].y);
+                    const float r0 = v0 * c0.x - v1 * c0.y, r1 = v1 * c0.x + v0 * c0.y;
+                    const float r2 = v2 * c1.x - v3 * c1.y, r3 = v3 * c1.x + v2 * c1.y;
+                    v0 = r0; v1 = r1; v2 = r2; v3 = r3;
                     dst = n < qd ? p.q + (size_t)token * qd + n : p.k + (size_t)token * hd + (n - qd);
                 } else {
                     dst = p.v + (size_t)token * hd + (n - qd - hd);
                 }
-                *dst = __float2bfloat16_rn(v);
+                *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(v0, v1), pack_bf16x2(v2, v3));
             } else if (EPI == EPI_GEGLU) {
-                // lanes 0..63 of the tile hold gate columns, 64..127 the matching up columns
-                if (n_local < 64) {
-                    float up = 0.f;
-                    for (int s = 0; s < S; ++s) up += red[(s * TS + tl) * TN + n_local + 64];
-                    const float g = sum * factor, u = up * factor;
-                    static_cast<bf16*>(p.out)[(size_t)token * p.ldo + tile * 64 + n_local] = __float2bfloat16_rn(gelu_f(g) * u);
+                // columns 0..63 of the tile are gate columns, 64..127 the matching up columns
+                float4 up = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int s = 0; s < S; ++s) {
+                    const float4 v = *reinterpret_cast<const float4*>(red + (s * TS + tl) * TN + 64 + c4);
+                    up.x += v.x; up.y += v.y; up.z += v.z; up.w += v.w;
                 }
+                const float f2 = factor;
+                *reinterpret_cast<uint2*>(static_cast<bf16*>(p.out) + (size_t)token * p.ldo + tile * 64 + c4) =
+                    make_uint2(pack_bf16x2(gelu_f(sum.x * f2) * (up.x * f2), gelu_f(sum.y * f2) * (up.y * f2)),
+                               pack_bf16x2(gelu_f(sum.z * f2) * (up.z * f2), gelu_f(sum.w * f2) * (up.w * f2)));
             } else {
-                const int n = tile * TN + n_local;
-                float v = sum;
-                if (EPI == EPI_BIAS) {
-                    v += bias_v;
-                    if (p.act == 2) v = silu_f(v);
-                }
-                if (EPI == EPI_RESIDUAL) v += __uint_as_float(pre[j]);
-                if (p.out_f32) static_cast<float*>(p.out)[(size_t)token * p.ldo + n] = v;
-                else static_cast<bf16*>(p.out)[(size_t)token * p.ldo + n] = __float2bfloat16_rn(v);
+                float v0 = sum.x, v1 = sum.y, v2 = sum.z, v3 = sum.w;
+                // pre = bias (EPI_BIAS) or residual (EPI_RESIDUAL), as four floats
+                v0 += __uint_as_float(pre[j].x); v1 += __uint_as_float(pre[j].y);
+                v2 += __uint_as_float(pre[j].z); v3 += __uint_as_float(pre[j].w);
+                if (EPI == EPI_BIAS && p.act == 2) { v0 = silu_f(v0); v1 = silu_f(v1); v2 = silu_f(v2); v3 = silu_f(v3); }
+                if (p.out_f32)
+                    *reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)token * p.ldo + n) = make_float4(v0, v1, v2, v3);
+                else
+                    *reinterpret_cast<uint2*>(static_cast<bf16*>(p.out) + (size_t)token * p.ldo + n) =
+                        make_uint2(pack_bf16x2(v0, v1), pack_bf16x2(v2, v3));
             }
         }
     }
@@ -417,10 +448,13 @@ inline int launch_skinny(SkinnyArgs a, const void* W, const void* W2, int ldw, c
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
         configured = true;
     }
-    CUtensorMap tmW, tmW2;
+    CUtensorMap tmW, tmW2, tmX;
     int rc = tc5::make_map(&tmW, W, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)ldw, 64, 64);
     if (rc) return rc;
     rc = tc5::make_map(&tmW2, W2 ? W2 : W, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)ldw, 64, 64);
+    if (rc) return rc;
+    if (a.x_f32) tmX = tmW;         // unused by the kernel in this case
+    else rc = tc5::make_map(&tmX, a.x, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.ldx, 64, 64);
     if (rc) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(pl.tiles, pl.splits, 1);
@@ -436,7 +470,7 @@ inline int launch_skinny(SkinnyArgs a, const void* W, const void* W2, int ldw, c
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, tmW, tmW2);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, tmW, tmW2, tmX);
     if (e != cudaSuccess) { set_error("skinny_gemm_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("skinny_gemm_kernel");
 }
