@@ -103,19 +103,27 @@ def dist_env():
 
 
 def max_over_ranks(value: float, world: int) -> float:
+    """Slowest rank's figure: replicas run independently, so the job is as fast as its slowest GPU."""
     if world == 1:
         return value
     import torch.distributed as dist
-    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    device = "cuda" if dist.get_backend() == "nccl" else "cpu"
+    t = torch.tensor([value], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
+
+
+def job_throughput(n_replicas: int, steps: int, ms_slowest: float) -> float:
+    """Forwards/s of the whole job: every replica did `steps` forwards within the slowest rank's time."""
+    return n_replicas * steps / (ms_slowest / 1e3)
 
 
 def barrier(world: int):
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
-    torch.cuda.synchronize()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
 
 
 # ----------------------------------------------------------------------------- CPU oracle timing
@@ -296,11 +304,11 @@ def run_ours(args):
 
     peaks = measured_peaks()
     line = {
-        "metric": "pi0_forwards_per_s", "value": args.gpus * K / (ms_total / 1e3), "unit": "forwards/s",
+        "metric": "pi0_forwards_per_s", "value": job_throughput(args.gpus, K, ms_total), "unit": "forwards/s",
         "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": ms_total / K, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args.gpus),
-        "e2e": {"value": args.gpus * K / (ms_e2e / 1e3), "unit": "forwards/s", "ms_per_forward": ms_e2e / K,
+        "e2e": {"value": job_throughput(args.gpus, K, ms_e2e), "unit": "forwards/s", "ms_per_forward": ms_e2e / K,
                 "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (images, state, noise)),
                 "d2h_bytes_per_step": host_out.numel() * host_out.element_size()},
         "gpu_launches": int(per_forward * K), "gpu_launches_per_forward": int(per_forward),
@@ -341,6 +349,57 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+SWEEP = {   # name: (M, K, N, gated, residual, layers cycled)
+    "dec_gate": (51, 1024, 4096, True, False, 18),
+    "dec_down": (51, 4096, 1024, False, True, 18),
+    "enc_gate": (768, 2048, 16384, True, False, 6),
+    "enc_down": (768, 16384, 2048, False, True, 6),
+}
+
+
+def run_sweep(args):
+    """Isolated GEMM roofline sweep (the four decoder / encoder FFN GEMMs): bf16 weights ~ N(0, 0.02),
+    activations ~ N(0, 1), fp32 accumulate, distinct weight copies cycled inside one CUDA graph so every
+    launch streams its weights cold. One JSON line with HBM GB/s and TFLOP/s against the measured peaks."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --sweep needs a CUDA device")
+    from flash_vla_b200 import op_table
+    from flash_vla_b200.hardware.nvidia.b200.pi0.backends.cuda import wrappers
+    from flash_vla_b200.runtime.cuda import ScratchPool
+    ops, peaks, bf16 = op_table(True), measured_peaks(), torch.bfloat16
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rows = {}
+    names = [args.sweep_only] if args.sweep_only else list(SWEEP)
+    with wrappers.use_pool(ScratchPool()):
+        for name in names:
+            M, K, N, gated, residual, layers = SWEEP[name]
+            layers = min(layers, args.sweep_layers) if args.sweep_layers else layers
+            w = [(torch.randn(K, N, device="cuda", generator=g) * 0.02).to(bf16) for _ in range(layers * (2 if gated else 1))]
+            x32 = torch.randn(M, K, device="cuda", generator=g)
+            x = x32 if (name == "dec_gate") else x32.to(bf16)          # the decoder's residual stream is fp32
+            out = torch.zeros(M, N, device="cuda", dtype=torch.float32 if name == "dec_down" else bf16)
+            xn = torch.zeros(M, K, device="cuda", dtype=bf16)
+            if name == "dec_gate":
+                fn = lambda i: ops.decoder_norm_gated_ffn(x, w[2 * i], w[2 * i + 1], out, None)
+            elif name == "enc_gate":
+                fn = lambda i: ops.encoder_norm_gated_ffn(x, w[2 * i], w[2 * i + 1], out, xn)
+            elif name == "dec_down":
+                fn = lambda i: ops.decoder_ffn_down_residual(x, w[i], out)
+            else:
+                fn = lambda i: ops.encoder_ffn_down_residual(x, w[i], out)
+            ms = time_isolated_op(fn, layers, args.sweep_reps)
+            flops = 2.0 * M * K * N * (2 if gated else 1)
+            nbytes = K * N * 2 * (2 if gated else 1) + M * K * x.element_size() + M * N * out.element_size() * (2 if residual else 1)
+            rows[name] = {"M": M, "K": K, "N": N, "ms_per_launch": ms, "tflops": flops / ms / 1e9,
+                          "gbs": nbytes / ms / 1e6, "algorithmic_bytes": nbytes, "flops": flops,
+                          "frac_of_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                          "frac_of_bf16": flops / ms / 1e9 / peaks["bf16_tflops"]}
+            del w
+            torch.cuda.empty_cache()
+    print(json.dumps({"metric": "isolated_gemm_roofline", "peaks": peaks, "kernels": rows,
+                      "note": "fractions are of the measured copy bandwidth and measured cuBLAS bf16 burst rate"}))
+
+
 def main():
     p = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     p.add_argument("--gpus", type=int, default=1)
@@ -348,8 +407,14 @@ def main():
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", choices=["ours", "reference"], default="ours")
     p.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle leg (faster iteration)")
+    p.add_argument("--sweep", action="store_true", help="isolated GEMM roofline sweep instead of the forward pass")
+    p.add_argument("--sweep-only", choices=list(SWEEP), default=None)
+    p.add_argument("--sweep-layers", type=int, default=0, help="cap on distinct weight copies (small profiler runs)")
+    p.add_argument("--sweep-reps", type=int, default=20)
     args = p.parse_args()
-    if args.impl == "reference":
+    if args.sweep:
+        run_sweep(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

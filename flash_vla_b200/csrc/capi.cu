@@ -244,14 +244,16 @@ int fvla_encoder_attention(const void* Q, const void* K, const void* V, void* ou
     return launch_attention<256>(a, dim3((queries + 63) / 64, 1, 1), S(stream));
 }
 
-int fvla_linear_residual(const void* x, const void* weight, void* out, int out_is_f32, int M, int N, int K,
-                         void* ws, size_t ws_bytes, void* stream) {
+int fvla_linear_residual(const void* x, const void* weight, void* out, int out_is_f32, void* out_shadow, int M,
+                         int N, int K, void* ws, size_t ws_bytes, void* stream) {
     if (tc5_enabled() && skinny::plan_skinny(M, N, K, false).ok && aligned16(x) && aligned16(weight)) {
         skinny::SkinnyArgs sa{};
         sa.x = x; sa.x_f32 = 0; sa.ldx = K; sa.M = M; sa.N = N; sa.K = K;
-        sa.out = out; sa.out_f32 = out_is_f32; sa.ldo = N; sa.status = device_status_ptr(); sa.dbg = debug_timestamps();
+        sa.out = out; sa.out_f32 = out_is_f32; sa.ldo = N; sa.out_shadow = Bm(out_shadow);
+        sa.status = device_status_ptr(); sa.dbg = debug_timestamps();
         return skinny::launch_skinny<skinny::EPI_RESIDUAL>(sa, weight, nullptr, N, S(stream));
     }
+    FVLA_REQUIRE(out_shadow == nullptr, "linear_residual: a bf16 shadow is only maintained for M <= 64 shapes");
     GemmArgs a;
     a.A = B(x); a.lda = K; a.B = B(weight); a.ldb = N; a.C = out; a.ldc = N; a.c_f32 = out_is_f32;
     a.R = out; a.ldr = N; a.M = M; a.N = N; a.K = K;
@@ -272,10 +274,11 @@ int fvla_encoder_norm_gated_ffn(const void* x, const void* gate_w, const void* u
 }
 
 int fvla_decoder_small_proj(const void* x, int x_is_f32, const void* weight, const void* bias, void* out,
-                            int out_is_f32, int M, int N, int K, int act, void* ws, size_t ws_bytes,
-                            void* stream) {
+                            int out_is_f32, void* out_shadow, int M, int N, int K, int act, void* ws,
+                            size_t ws_bytes, void* stream) {
     FVLA_REQUIRE(M > 0 && N > 0 && K > 0 && (act == 0 || act == 2), "small_proj: bad arguments");
     if (K <= 64) {
+        FVLA_REQUIRE(out_shadow == nullptr, "small_proj: no bf16 shadow for K <= 64");
         dim3 grid((N + 255) / 256, M);
         cudaStream_t st = S(stream);
         if (x_is_f32 && out_is_f32)
@@ -292,10 +295,11 @@ int fvla_decoder_small_proj(const void* x, int x_is_f32, const void* weight, con
         skinny::SkinnyArgs sa{};
         sa.x = x; sa.x_f32 = x_is_f32; sa.ldx = K; sa.M = M; sa.N = N; sa.K = K;
         sa.out = out; sa.out_f32 = out_is_f32; sa.ldo = N; sa.bias = B(bias); sa.act = act;
-        sa.status = device_status_ptr(); sa.dbg = debug_timestamps();
+        sa.out_shadow = Bm(out_shadow); sa.status = device_status_ptr(); sa.dbg = debug_timestamps();
         return skinny::launch_skinny<skinny::EPI_BIAS>(sa, weight, nullptr, N, S(stream));
     }
     FVLA_REQUIRE(!x_is_f32, "small_proj: fp32 input only for K <= 64");
+    FVLA_REQUIRE(out_shadow == nullptr, "small_proj: a bf16 shadow is only maintained by the cluster kernel");
     GemmArgs a;
     a.A = B(x); a.lda = K; a.B = B(weight); a.ldb = N; a.C = out; a.ldc = N; a.c_f32 = out_is_f32;
     a.bias = B(bias); a.act = act; a.M = M; a.N = N; a.K = K;
@@ -322,14 +326,14 @@ static int decoder_norm_front(const void* x, int x_is_f32, void* norm_factor, in
     return FVLA_OK;
 }
 
-int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* weight_qkv, const void* rope, void* Q,
+int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* x_shadow, const void* weight_qkv, const void* rope, void* Q,
                                void* K, void* V, void* norm_factor, int M, int Kdim, int heads, int head_dim,
                                void* ws, size_t ws_bytes, void* stream) {
     const int N = (heads + 2) * head_dim;
     if (tc5_enabled() && skinny::plan_skinny(M, N, Kdim, false).ok && aligned16(x) && aligned16(weight_qkv) &&
         head_dim % 2 == 0) {
         skinny::SkinnyArgs sa{};
-        sa.x = x; sa.x_f32 = x_is_f32; sa.ldx = Kdim; sa.M = M; sa.N = N; sa.K = Kdim; sa.need_factor = 1;
+        sa.x = x; sa.x_f32 = x_is_f32; sa.x_shadow = B(x_shadow); sa.ldx = Kdim; sa.M = M; sa.N = N; sa.K = Kdim; sa.need_factor = 1;
         sa.rope = B(rope); sa.q = Bm(Q); sa.k = Bm(K); sa.v = Bm(V); sa.heads = heads; sa.head_dim = head_dim;
         sa.factor_out = Bm(norm_factor); sa.status = device_status_ptr(); sa.dbg = debug_timestamps();
         return skinny::launch_skinny<skinny::EPI_QKV_ROPE>(sa, weight_qkv, nullptr, N, S(stream));
@@ -379,11 +383,11 @@ int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* ou
     return check_launch("attention_combine_kernel");
 }
 
-int fvla_decoder_norm_gated_ffn(const void* x, int x_is_f32, const void* gate_w, const void* up_w, void* out,
+int fvla_decoder_norm_gated_ffn(const void* x, int x_is_f32, const void* x_shadow, const void* gate_w, const void* up_w, void* out,
                                 void* norm_factor, int M, int N, int K, void* ws, size_t ws_bytes, void* stream) {
     if (tc5_enabled() && skinny::plan_skinny(M, N, K, true).ok && aligned16(x) && aligned16(gate_w) && aligned16(up_w)) {
         skinny::SkinnyArgs sa{};
-        sa.x = x; sa.x_f32 = x_is_f32; sa.ldx = K; sa.M = M; sa.N = N; sa.K = K; sa.need_factor = 1;
+        sa.x = x; sa.x_f32 = x_is_f32; sa.x_shadow = B(x_shadow); sa.ldx = K; sa.M = M; sa.N = N; sa.K = K; sa.need_factor = 1;
         sa.out = out; sa.out_f32 = 0; sa.ldo = N; sa.factor_out = Bm(norm_factor); sa.status = device_status_ptr(); sa.dbg = debug_timestamps();
         return skinny::launch_skinny<skinny::EPI_GEGLU>(sa, gate_w, up_w, N, S(stream));
     }

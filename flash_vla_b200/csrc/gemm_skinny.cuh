@@ -41,6 +41,8 @@ enum Epi { EPI_QKV_ROPE = 0, EPI_RESIDUAL = 1, EPI_GEGLU = 2, EPI_BIAS = 3 };
 
 struct SkinnyArgs {
     const void* x; int x_f32; int ldx;        // activations [M, K]
+    const bf16* x_shadow;                     // optional bf16 copy of an fp32 x, kept current by its writers
+    bf16* out_shadow;                         // optional bf16 copy of `out` to maintain (RESIDUAL / BIAS)
     int M, N, K;
     int kblocks;                              // 64-wide k-blocks per CTA (K / 64 / splits)
     int splits;                               // cluster size along K
@@ -133,7 +135,7 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
 
     // bf16 activations are fetched by TMA straight into the operand layout (rows past M read as
     // zero); fp32 activations are converted by the CTA further down.
-    const bool x_by_tma = !p.x_f32;
+    const bool x_by_tma = !p.x_f32 || p.x_shadow != nullptr;
     if (tid == 0) {
         mbar_init(done_bar, 1);
         mbar_init(in_bar, 1);
@@ -250,18 +252,6 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
             }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
-    } else if (p.need_factor) {
-        // bf16 activations: sums of squares over this CTA's K slice, straight from global memory
-        for (int t = warp; t < p.M; t += THREADS / 32) {
-            float ss = 0.f;
-            for (int c = lane; c < KB * 8; c += 32) {
-                uint4 a = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.x) + (size_t)t * p.ldx + k0 + c * 8);
-                float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
-                ss += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y + f2.x * f2.x + f2.y * f2.y + f3.x * f3.x + f3.y * f3.y;
-            }
-            ss = warp_sum(ss);
-            if (lane == 0) { ssq_local[t * 2] = ss; ssq_local[t * 2 + 1] = 0.f; }
-        }
     }
     tc5::tc_fence_before();
     __syncthreads();
@@ -286,10 +276,27 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
         tc5::umma_commit(done_bar);
     }
     __syncwarp();
+    if (x_by_tma && p.need_factor) {
+        // Sums of squares over this CTA's K slice, read back from the bf16 operand tile in shared
+        // memory while the MMAs run (8 lanes per token, one 16-byte chunk per k-block each).
+        const int t = tid >> 3, sub = tid & 7;
+        float ss = 0.f;
+        for (int kb = 0; kb < KB; ++kb) {
+            mbar_wait(bars + kb * 8, 0, abort_flag);
+            const uint4 a = *reinterpret_cast<const uint4*>(gen + w_bytes + kb * 8192 + t * 128 + sub * 16);
+            const float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+            ss += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y + f2.x * f2.x + f2.y * f2.y + f3.x * f3.x + f3.y * f3.y;
+        }
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+        if (sub == 0) { ssq_local[t * 2] = ss; ssq_local[t * 2 + 1] = 0.f; }
+    }
     const bool done = mbar_wait(done_bar, 0, abort_flag);
     tc5::tc_fence_after();
     FVLA_STAMP(3);
 
+    __syncthreads();                                   // sums of squares are complete
     // Stage this CTA's partial tile as [token][n] fp32 over the (now idle) weight region.
     if (warp < 4) {
         float lo[32], hi[32];
@@ -375,6 +382,9 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
                 v0 += __uint_as_float(pre[j].x); v1 += __uint_as_float(pre[j].y);
                 v2 += __uint_as_float(pre[j].z); v3 += __uint_as_float(pre[j].w);
                 if (EPI == EPI_BIAS && p.act == 2) { v0 = silu_f(v0); v1 = silu_f(v1); v2 = silu_f(v2); v3 = silu_f(v3); }
+                if (p.out_shadow)
+                    *reinterpret_cast<uint2*>(p.out_shadow + (size_t)token * p.ldo + n) =
+                        make_uint2(pack_bf16x2(v0, v1), pack_bf16x2(v2, v3));
                 if (p.out_f32)
                     *reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)token * p.ldo + n) = make_float4(v0, v1, v2, v3);
                 else
@@ -453,8 +463,8 @@ inline int launch_skinny(SkinnyArgs a, const void* W, const void* W2, int ldw, c
     if (rc) return rc;
     rc = tc5::make_map(&tmW2, W2 ? W2 : W, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)ldw, 64, 64);
     if (rc) return rc;
-    if (a.x_f32) tmX = tmW;         // unused by the kernel in this case
-    else rc = tc5::make_map(&tmX, a.x, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.ldx, 64, 64);
+    if (a.x_f32 && a.x_shadow == nullptr) tmX = tmW;         // unused by the kernel in this case
+    else rc = tc5::make_map(&tmX, a.x_f32 ? (const void*)a.x_shadow : a.x, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.ldx, 64, 64);
     if (rc) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(pl.tiles, pl.splits, 1);

@@ -309,8 +309,9 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
             const int m0 = (tile % args.tiles_m) * BM, n0 = (tile / args.tiles_m) * BN;
             const int row = m0 + quad * 32 + lane;
             // bf16 residual of this thread's whole output row, fetched while the MMAs still run
-            uint4 rpre[BN / 8];
-            if (!DUAL && p.R && !p.c_f32 && row < p.M) {
+            constexpr bool kPreload = !DUAL && BN <= 128;      // wider tiles are only used without a residual
+            uint4 rpre[kPreload ? BN / 8 : 1];
+            if (kPreload && p.R && !p.c_f32 && row < p.M) {
                 const int rr = p.res_mod > 0 ? row % p.res_mod : row;
                 const bf16* rrow = static_cast<const bf16*>(p.R) + (size_t)rr * p.ldr + n0;
 #pragma unroll
@@ -322,7 +323,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * Cfg::ACC_COLS;
             // fully unrolled when a residual is preloaded (register array indexed by chunk);
             // the gated form keeps one chunk live at a time
-#pragma unroll(DUAL ? 1 : BN / 32)
+#pragma unroll(kPreload ? BN / 32 : 1)
             for (int c = 0; c < BN; c += 32) {
                 float a[32], u[32];
                 tmem_ld32(t_row + c, a);
@@ -335,7 +336,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                             float a8[8], u8[8];
 #pragma unroll
                             for (int i = 0; i < 8; ++i) { a8[i] = a[j + i]; u8[i] = DUAL ? u[j + i] : 0.f; }
-                            epilogue8<DUAL>(p, row, col, a8, u8, DUAL ? make_uint4(0, 0, 0, 0) : rpre[(c + j) / 8]);
+                            epilogue8<DUAL>(p, row, col, a8, u8, kPreload ? rpre[(c + j) / 8] : make_uint4(0, 0, 0, 0));
                         }
                     }
                 }
@@ -435,10 +436,29 @@ inline bool tc5_supports(const GemmArgs& g) {
            aligned16(g.A) && aligned16(g.B) && (g.B2 == nullptr || aligned16(g.B2));
 }
 
+// Tile width for a plain GEMM: the one that minimises (waves over the SMs) x (tile width), i.e. the
+// time of the slowest SM. Wider tiles also need less shared-memory fill per MMA. A residual is
+// preloaded per output row and is only supported at width 128.
+inline int pick_bn(const GemmArgs& g) {
+    if (g.R != nullptr) return 128;
+    const int tiles_m = (g.M + BM - 1) / BM, sms = num_sms();
+    int best = 128, best_cost = 1 << 30;
+    for (int bn = 128; bn <= 256; bn += 64) {
+        const int tiles = tiles_m * ((g.N + bn - 1) / bn);
+        const int cost = ((tiles + sms - 1) / sms) * bn;
+        if (cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
 inline int launch_gemm_tc5(GemmArgs g, int* status, cudaStream_t st) {
     if (g.Kb == 0) g.Kb = g.K;
     if (g.B2 != nullptr) return launch_tc5_cfg<128, true, 4>(g, status, st);
-    return launch_tc5_cfg<128, false, 6>(g, status, st);
+    switch (pick_bn(g)) {
+        case 256: return launch_tc5_cfg<256, false, 4>(g, status, st);
+        case 192: return launch_tc5_cfg<192, false, 5>(g, status, st);
+        default: return launch_tc5_cfg<128, false, 6>(g, status, st);
+    }
 }
 
 }  // namespace tc5

@@ -44,6 +44,51 @@ def use_pool(pool: ScratchPool):
         _POOL = previous
 
 
+# fp32 tensor (by base address) -> (its bf16 shadow, the fp32 tensor). A shadow is a bf16 copy
+# that every op of this backend refreshes when it writes the fp32 tensor, so that the GEMMs reading
+# the tensor can fetch ready-made bf16 rows by TMA instead of converting fp32 in the kernel. Code
+# that writes a registered tensor by other means must call `sync_shadow` afterwards.
+_SHADOWS: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def register_bf16_shadow(master: torch.Tensor, shadow: torch.Tensor) -> None:
+    """Declare `shadow` (bf16, same shape, contiguous) as the maintained copy of fp32 `master`."""
+    if master.dtype != torch.float32 or shadow.dtype != torch.bfloat16 or master.shape != shadow.shape:
+        raise ValueError("register_bf16_shadow: need an fp32 master and a bf16 shadow of equal shape")
+    if not (master.is_contiguous() and shadow.is_contiguous()):
+        raise ValueError("register_bf16_shadow: tensors must be contiguous")
+    _SHADOWS[master.data_ptr()] = (shadow, master)
+    shadow.copy_(master)
+
+
+def unregister_bf16_shadow(master: torch.Tensor) -> None:
+    _SHADOWS.pop(master.data_ptr(), None)
+
+
+def _shadow_of(t: torch.Tensor):
+    """Device address inside the registered shadow that mirrors the first element of `t` (which may be
+    a row-offset view of the master), or None."""
+    if t.dtype != torch.float32:
+        return None
+    ptr = t.data_ptr()
+    for base, (shadow, master) in _SHADOWS.items():
+        offset = ptr - base
+        if 0 <= offset < master.numel() * 4 and offset % 4 == 0:
+            return shadow.data_ptr() + offset // 2
+    return None
+
+
+def sync_shadow(t: torch.Tensor) -> None:
+    """Refresh the shadow rows mirroring `t` after `t` was written outside this backend."""
+    ptr = t.data_ptr()
+    for base, (shadow, master) in _SHADOWS.items():
+        offset = ptr - base
+        if 0 <= offset < master.numel() * 4:
+            first = offset // 4
+            shadow.view(-1)[first:first + t.numel()].copy_(t.reshape(-1))
+            return
+
+
 def scratch(role: str, shape, dtype, device) -> torch.Tensor:
     """Graph-safe temporary from the pool that is active at call time."""
     return _POOL.get(role, shape, dtype, device)
@@ -182,7 +227,8 @@ def _linear_residual(role, x, weight, out):
     lib = _lib.load()
     ws, nb = _ws(role, lib.fvla_gemm_workspace_bytes(M, N, K, 0), x.device)
     _lib.call("fvla_linear_residual", _chk("x", x), _chk("weight", weight, (K, N)),
-              _chk("out", out, (M, N), dtype=None), _is_f32("out", out), M, N, K, ws, nb, _stream())
+              _chk("out", out, (M, N), dtype=None), _is_f32("out", out), _shadow_of(out), M, N, K, ws, nb,
+              _stream())
     return out
 
 
@@ -216,7 +262,7 @@ def _small_proj(role, x, weight, bias, out, act):
         raise ValueError(f"{role}: out has the wrong size")
     _lib.call("fvla_decoder_small_proj", _chk("x", x, dtype=None), _is_f32("x", x),
               _chk("weight", weight), _chk("bias", bias, (N,)), _chk("out", out, dtype=None),
-              _is_f32("out", out), M, N, K, act, ws, nb, _stream())
+              _is_f32("out", out), _shadow_of(out) if K > 64 else None, M, N, K, act, ws, nb, _stream())
     return out
 
 
@@ -244,7 +290,7 @@ def decoder_norm_qkv_rope(x, weight_qkv, rope, Q, K, V, norm_factor):
     N = (heads + 2) * hd
     lib = _lib.load()
     ws, nb = _ws("dec_qkv_ws", lib.fvla_gemm_workspace_bytes(M, N, Kdim, 0), x.device)
-    _lib.call("fvla_decoder_norm_qkv_rope", _chk("x", x, dtype=None), _is_f32("x", x),
+    _lib.call("fvla_decoder_norm_qkv_rope", _chk("x", x, dtype=None), _is_f32("x", x), _shadow_of(x),
               _chk("weight_qkv", weight_qkv, (Kdim, N)),
               _chk("rope", rope[:M], (M, hd)), _chk("Q", Q, (M * heads, hd)), _chk("K", K, (M, hd)),
               _chk("V", V, (M, hd)), _chk("norm_factor", norm_factor[:M], (M,)), M, Kdim, heads, hd,
@@ -282,7 +328,8 @@ def _gated_ffn(x, gate_w, up_w, out, norm_factor):
     lib = _lib.load()
     ws, nb = _ws("dec_gate_ws", lib.fvla_gemm_workspace_bytes(M, N, K, 1), x.device)
     nf = None if norm_factor is None else _chk("norm_factor", norm_factor[:M], (M,))
-    _lib.call("fvla_decoder_norm_gated_ffn", _chk("x", x, dtype=None), _is_f32("x", x), _chk("gate_w", gate_w, (K, N)),
+    _lib.call("fvla_decoder_norm_gated_ffn", _chk("x", x, dtype=None), _is_f32("x", x), _shadow_of(x),
+              _chk("gate_w", gate_w, (K, N)),
               _chk("up_w", up_w, (K, N)), _chk("out", out, (M, N)), nf, M, N, K, ws, nb, _stream())
     return out
 
@@ -319,4 +366,5 @@ DECODER_WRAPPERS = {f.__name__: f for f in (
     decoder_attention, decoder_out_proj_residual, decoder_ffn_down_residual,
     decoder_norm_gated_ffn, decoder_action_out_proj)}
 
-ALL_WRAPPERS = {**VISION_WRAPPERS, **ENCODER_WRAPPERS, **DECODER_WRAPPERS}
+# `sync_shadow` rides in the table so that orchestration code can reach it through `ops`.
+ALL_WRAPPERS = {**VISION_WRAPPERS, **ENCODER_WRAPPERS, **DECODER_WRAPPERS, "sync_shadow": sync_shadow}

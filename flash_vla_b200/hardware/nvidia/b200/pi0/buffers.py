@@ -9,6 +9,9 @@ shapes and bf16 dtype (`.../h100/pi0/buffers.py:26-64`) and adds what the B200 k
   * `decoder_x` is fp32 instead of bf16: the action expert's residual stream reaches |x| ~ 10,
     where a bf16 ulp is 2^-4, and 36 in-place residual adds per step would each round it. The
     GEMMs that read it take a bf16 copy of the normalised rows; the adds stay exact in fp32.
+  * `decoder_x_bf16`: bf16 shadow of `decoder_x`, refreshed by every op that writes `decoder_x`
+    (the engine registers the pair with the backend), so the QKV and gate/up GEMMs fetch their
+    activation operand by TMA instead of converting fp32 rows inside the kernel.
   * `diffusion_noise_f32`: fp32 master copy of the action chunk. The ten Euler updates
     accumulate here so that each step adds its update without first rounding the running
     value to bf16; `diffusion_noise` (bf16) is refreshed from it at the end of the pass.
@@ -64,6 +67,7 @@ def allocate_static_buffers(num_views: int, chunk_size: int, prompt_len: int,
     add("encoder_hidden", S, ENCODER_FFN)
     add("decoder_rope_weights", D, HEAD_DIM)
     add("decoder_x", D, DECODER_DIM, dtype=torch.float32)
+    add("decoder_x_bf16", D, DECODER_DIM)
     add("decoder_x_buf", chunk_size, DECODER_DIM)
     add("decoder_state_buf", 1, DECODER_DIM)
     add("decoder_norm_factor_buf", D)

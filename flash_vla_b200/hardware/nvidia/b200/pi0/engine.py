@@ -50,6 +50,7 @@ class Pi0Inference:
         self.buffers, self.encoder_seq_len = allocate_static_buffers(
             num_views, chunk_size, self.prompt_len, device)
 
+        wrappers.register_bf16_shadow(self.buffers["decoder_x"], self.buffers["decoder_x_bf16"])
         self.pool = ScratchPool()
         self.graph = None
         if capture:
@@ -81,6 +82,12 @@ class Pi0Inference:
             self.graph.capture_end()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+
+    def __del__(self):
+        try:
+            wrappers.unregister_bf16_shadow(self.buffers["decoder_x"])
+        except Exception:
+            pass
 
     def forward(self, images, state, noise):
         """Copy the inputs into their static buffers, replay, return the denoised chunk.

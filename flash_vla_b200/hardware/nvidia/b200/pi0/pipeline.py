@@ -67,6 +67,8 @@ def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LA
         noise = b["diffusion_noise_f32"] if "diffusion_noise_f32" in b else b["diffusion_noise"]
     x, nf = b["decoder_x"], b["decoder_norm_factor_buf"]
     x[:1].copy_(b["decoder_state_buf"])
+    if hasattr(ops, "sync_shadow"):          # a backend keeping a bf16 copy of x must see this write
+        ops.sync_shadow(x[:1])
     ops.decoder_action_in_proj(noise, w["decoder_action_fused_in_proj_w"],
                                w["decoder_action_fused_time_biases"][step % DIFFUSION_STEPS],
                                b["decoder_x_buf"])

@@ -87,9 +87,10 @@ int fvla_encoder_norm_qkv_rope(const void* x, const void* weight_qkv, const void
 int fvla_encoder_attention(const void* Q, const void* K, const void* V, void* out, int queries,
                            int keys, int head_dim, float scale, void* stream);
 /* wrappers.py:366-371, :383-392 (encoder) and :176-189 (decoder): out += x(M,K) @ W(K,N). out is
- * bf16, or an fp32 residual stream when out_is_f32 != 0. */
-int fvla_linear_residual(const void* x, const void* weight, void* out, int out_is_f32, int M, int N,
-                         int K, void* ws, size_t ws_bytes, void* stream);
+ * bf16, or an fp32 residual stream when out_is_f32 != 0. out_shadow (may be NULL; M <= 64 only) is a
+ * bf16 tensor of out's shape that receives the rounded new value, for a later GEMM to read. */
+int fvla_linear_residual(const void* x, const void* weight, void* out, int out_is_f32, void* out_shadow,
+                         int M, int N, int K, void* ws, size_t ws_bytes, void* stream);
 /* wrappers.py:374-380: x_norm = rms(x); out = gelu(x_norm @ Wg) * (x_norm @ Wu). */
 int fvla_encoder_norm_gated_ffn(const void* x, const void* gate_w, const void* up_w, void* out,
                                 void* x_norm, int M, int N, int K, void* stream);
@@ -98,12 +99,13 @@ int fvla_encoder_norm_gated_ffn(const void* x, const void* gate_w, const void* u
 /* wrappers.py:108-128: out = act(x(M,K) @ W(K,N) + b); act 0 none, 2 silu; K <= 64 uses a
  * dedicated kernel. x is bf16, or fp32 when x_is_f32 != 0 (K <= 64 only); out likewise. */
 int fvla_decoder_small_proj(const void* x, int x_is_f32, const void* weight, const void* bias,
-                            void* out, int out_is_f32, int M, int N, int K, int act, void* ws,
-                            size_t ws_bytes, void* stream);
+                            void* out, int out_is_f32, void* out_shadow, int M, int N, int K, int act,
+                            void* ws, size_t ws_bytes, void* stream);
 /* wrappers.py:131-144: factor = rsqrt(mean(x^2)+1e-6) (also stored, bf16, in norm_factor when
  * not NULL); projection scaled by it, RoPE in fp32, single rounding, scatter to Q / K / V.
- * x is the bf16 residual stream, or an fp32 one when x_is_f32 != 0. */
-int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* weight_qkv, const void* rope, void* Q,
+ * x is the bf16 residual stream, or an fp32 one when x_is_f32 != 0; x_shadow (may be NULL) is a
+ * current bf16 copy of an fp32 x, which spares the kernel the conversion. */
+int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* x_shadow, const void* weight_qkv, const void* rope, void* Q,
                                void* K, void* V, void* norm_factor, int M, int Kdim, int heads,
                                int head_dim, void* ws, size_t ws_bytes, void* stream);
 /* fused_wrappers.py:88-115 (and the unfused chain wrappers.py:147-173): softmax(Q K^T / sqrt(hd))
@@ -114,7 +116,7 @@ int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* ou
                            size_t ws_bytes, void* stream);
 /* fused_wrappers.py:45-54 / wrappers.py:192-198: out = gelu(rms(x) @ Wg) * (rms(x) @ Wu). When
  * norm_factor is not NULL the bf16 factor is also stored there (the unfused side effect). */
-int fvla_decoder_norm_gated_ffn(const void* x, int x_is_f32, const void* gate_w, const void* up_w,
+int fvla_decoder_norm_gated_ffn(const void* x, int x_is_f32, const void* x_shadow, const void* gate_w, const void* up_w,
                                 void* out, void* norm_factor, int M, int N, int K, void* ws,
                                 size_t ws_bytes, void* stream);
 /* fused_wrappers.py:57-67 / wrappers.py:201-208: out += b + rms(x)(M,K) @ W(K,32). x and out are
