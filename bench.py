@@ -400,6 +400,19 @@ def run_sweep(args):
                       "note": "fractions are of the measured copy bandwidth and measured cuBLAS bf16 burst rate"}))
 
 
+def run_profile_pass():
+    """Two eager (uncaptured) forwards and nothing else: the command to put under a profiler, e.g.
+    `ncu --metrics gpu__time_duration.sum --clock-control none -s <launches of pass 1> -c <same> ...`."""
+    from flash_vla_b200 import Pi0Inference, random_checkpoint
+    from flash_vla_b200.synthetic import bench_inputs
+    engine = Pi0Inference(random_checkpoint(prompt_len=0, wscale=0.02, seed=0, device="cuda"), 3, 50, capture=False)
+    images, state, noise = [t.cuda() for t in bench_inputs()]
+    for _ in range(2):
+        out = engine.forward(images, state, noise)
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_pass": "ok", "max_abs_action": float(out.float().abs().max())}))
+
+
 def main():
     p = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     p.add_argument("--gpus", type=int, default=1)
@@ -411,8 +424,11 @@ def main():
     p.add_argument("--sweep-only", choices=list(SWEEP), default=None)
     p.add_argument("--sweep-layers", type=int, default=0, help="cap on distinct weight copies (small profiler runs)")
     p.add_argument("--sweep-reps", type=int, default=20)
+    p.add_argument("--profile-pass", action="store_true", help="two eager forwards only (for ncu launch lists)")
     args = p.parse_args()
-    if args.sweep:
+    if args.profile_pass:
+        run_profile_pass()
+    elif args.sweep:
         run_sweep(args)
     elif args.impl == "reference":
         run_reference(args)
