@@ -41,6 +41,7 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnArgs p) {
     const uint32_t sQ = smem_u32(smem);
     const uint32_t sKV = sQ + TILE;             // stage s: K at sKV + s*2*TILE, V right after
 
+    asm volatile("griddepcontrol.wait;" ::: "memory");      // no-op unless launched as a dependent
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int q0 = blockIdx.x * BQ;
     const int b0 = blockIdx.y / p.batch_inner, b1 = blockIdx.y % p.batch_inner;
@@ -249,7 +250,8 @@ inline int launch_attention(const AttnArgs& a, dim3 grid, cudaStream_t st) {
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
         configured = true;
     }
-    kern<<<grid, 128, smem, st>>>(a);
+    cudaError_t e = launch_pdl(kern, grid, dim3(128), smem, st, a);
+    if (e != cudaSuccess) { set_error("attention_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("attention_kernel");
 }
 

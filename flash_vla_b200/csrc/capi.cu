@@ -52,10 +52,12 @@ static inline bf16* Bm(void* p) { return reinterpret_cast<bf16*>(p); }
 static int rownorm(const void* x, int x_is_f32, const void* w, const void* b, void* out, float* f32,
                    void* fbf, int M, int K, int mode, cudaStream_t st) {
     FVLA_REQUIRE(M > 0 && K > 0 && K % 2 == 0, "rownorm: bad shape M=%d K=%d", M, K);
+    cudaError_t e;
     if (x_is_f32)
-        rownorm_kernel<float><<<(M + 3) / 4, 128, 0, st>>>((const float*)x, B(w), B(b), Bm(out), f32, Bm(fbf), M, K, mode);
+        e = launch_pdl(rownorm_kernel<float>, dim3((M + 3) / 4), dim3(128), 0, st, (const float*)x, B(w), B(b), Bm(out), f32, Bm(fbf), M, K, mode);
     else
-        rownorm_kernel<bf16><<<(M + 3) / 4, 128, 0, st>>>(B(x), B(w), B(b), Bm(out), f32, Bm(fbf), M, K, mode);
+        e = launch_pdl(rownorm_kernel<bf16>, dim3((M + 3) / 4), dim3(128), 0, st, B(x), B(w), B(b), Bm(out), f32, Bm(fbf), M, K, mode);
+    if (e != cudaSuccess) { set_error("rownorm_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("rownorm_kernel");
 }
 
@@ -281,14 +283,16 @@ int fvla_decoder_small_proj(const void* x, int x_is_f32, const void* weight, con
         FVLA_REQUIRE(out_shadow == nullptr, "small_proj: no bf16 shadow for K <= 64");
         dim3 grid((N + 255) / 256, M);
         cudaStream_t st = S(stream);
+        cudaError_t e;
         if (x_is_f32 && out_is_f32)
-            small_k_proj_kernel<float, float><<<grid, 256, 0, st>>>((const float*)x, B(weight), B(bias), (float*)out, M, N, K, act);
+            e = launch_pdl(small_k_proj_kernel<float, float>, grid, dim3(256), 0, st, (const float*)x, B(weight), B(bias), (float*)out, M, N, K, act);
         else if (x_is_f32)
-            small_k_proj_kernel<float, bf16><<<grid, 256, 0, st>>>((const float*)x, B(weight), B(bias), Bm(out), M, N, K, act);
+            e = launch_pdl(small_k_proj_kernel<float, bf16>, grid, dim3(256), 0, st, (const float*)x, B(weight), B(bias), Bm(out), M, N, K, act);
         else if (out_is_f32)
-            small_k_proj_kernel<bf16, float><<<grid, 256, 0, st>>>(B(x), B(weight), B(bias), (float*)out, M, N, K, act);
+            e = launch_pdl(small_k_proj_kernel<bf16, float>, grid, dim3(256), 0, st, B(x), B(weight), B(bias), (float*)out, M, N, K, act);
         else
-            small_k_proj_kernel<bf16, bf16><<<grid, 256, 0, st>>>(B(x), B(weight), B(bias), Bm(out), M, N, K, act);
+            e = launch_pdl(small_k_proj_kernel<bf16, bf16>, grid, dim3(256), 0, st, B(x), B(weight), B(bias), Bm(out), M, N, K, act);
+        if (e != cudaSuccess) { set_error("small_k_proj_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
         return check_launch("small_k_proj_kernel");
     }
     if (tc5_enabled() && skinny::plan_skinny(M, N, K, false).ok && aligned16(x) && aligned16(weight)) {
@@ -364,7 +368,7 @@ int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* ou
         d.scale_log2 = kLog2e / sqrtf((float)head_dim);
         d.mask_rows = heads; d.mask_key_le = encoder_seq_len; d.prefix_keys = encoder_seq_len;
         d.status = device_status_ptr();
-        return launch_decoder_attention_cluster(d, skinny::pdl_enabled(), S(stream));
+        return launch_decoder_attention_cluster(d, pdl_enabled(), S(stream));
     }
     const int splits = (keys + 127) / 128;
     const int qpad = (queries + 63) / 64 * 64;
@@ -406,14 +410,16 @@ int fvla_decoder_action_out_proj(const void* x, int x_is_f32, const void* weight
     FVLA_REQUIRE(M > 0 && K > 0, "action_out_proj: bad shape");
     if (N != 32) { set_error("action_out_proj: N=%d not built (32 only)", N); return FVLA_ERR_UNSUPPORTED; }
     cudaStream_t st = S(stream);
+    cudaError_t e;
     if (x_is_f32 && out_is_f32)
-        action_out_kernel<float, float><<<M, 256, 0, st>>>((const float*)x, B(weight), B(bias), (float*)out, Bm(mirror), Bm(norm_factor), K);
+        e = launch_pdl(action_out_kernel<float, float>, dim3(M), dim3(256), 0, st, (const float*)x, B(weight), B(bias), (float*)out, Bm(mirror), Bm(norm_factor), K);
     else if (x_is_f32)
-        action_out_kernel<float, bf16><<<M, 256, 0, st>>>((const float*)x, B(weight), B(bias), Bm(out), Bm(mirror), Bm(norm_factor), K);
+        e = launch_pdl(action_out_kernel<float, bf16>, dim3(M), dim3(256), 0, st, (const float*)x, B(weight), B(bias), Bm(out), Bm(mirror), Bm(norm_factor), K);
     else if (out_is_f32)
-        action_out_kernel<bf16, float><<<M, 256, 0, st>>>(B(x), B(weight), B(bias), (float*)out, Bm(mirror), Bm(norm_factor), K);
+        e = launch_pdl(action_out_kernel<bf16, float>, dim3(M), dim3(256), 0, st, B(x), B(weight), B(bias), (float*)out, Bm(mirror), Bm(norm_factor), K);
     else
-        action_out_kernel<bf16, bf16><<<M, 256, 0, st>>>(B(x), B(weight), B(bias), Bm(out), Bm(mirror), Bm(norm_factor), K);
+        e = launch_pdl(action_out_kernel<bf16, bf16>, dim3(M), dim3(256), 0, st, B(x), B(weight), B(bias), Bm(out), Bm(mirror), Bm(norm_factor), K);
+    if (e != cudaSuccess) { set_error("action_out_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("action_out_kernel");
 }
 

@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/flash_vla_b200.h"
 
@@ -80,6 +81,31 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
+}
+
+// FVLA_PDL=0 turns programmatic dependent launch off (diagnostic switch).
+inline bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* v = getenv("FVLA_PDL");
+        on = (v != nullptr && v[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+// Launch `kern` as a programmatic dependent of the previous kernel in the stream: its CTAs may be
+// scheduled while that kernel drains, and it must execute griddepcontrol.wait before touching
+// anything the previous kernel wrote (every kernel launched through here does so first thing).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
 // Host-side: record the message of the last failing call on this thread.

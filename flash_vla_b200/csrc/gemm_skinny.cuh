@@ -435,16 +435,6 @@ inline SkinnyPlan plan_skinny(int M, int N, int K, bool geglu) {
     return pl;
 }
 
-// FVLA_PDL=0 turns programmatic dependent launch off (diagnostic switch).
-inline bool pdl_enabled() {
-    static int on = -1;
-    if (on < 0) {
-        const char* v = getenv("FVLA_PDL");
-        on = (v != nullptr && v[0] == '0') ? 0 : 1;
-    }
-    return on == 1;
-}
-
 template <int EPI>
 inline int launch_skinny(SkinnyArgs a, const void* W, const void* W2, int ldw, cudaStream_t st) {
     SkinnyPlan pl = plan_skinny(a.M, a.N, a.K, EPI == EPI_GEGLU);

@@ -243,6 +243,9 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    // Set-up above touched only this CTA's own shared memory and TMEM; from here on the operands
+    // written by the previous kernel in the stream are read.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0) {
@@ -426,7 +429,8 @@ inline int launch_tc5_cfg(const GemmArgs& g, int* status, cudaStream_t st) {
     a.status = status;
     int tiles = a.tiles_m * a.tiles_n;
     int grid = tiles < num_sms() ? tiles : num_sms();
-    kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(a, tmA, tmB, tmB2);
+    cudaError_t e = launch_pdl(kern, dim3(grid), dim3(192), Cfg::SMEM_BYTES, st, a, tmA, tmB, tmB2);
+    if (e != cudaSuccess) { set_error("tc5_gemm_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("tc5_gemm_kernel");
 }
 

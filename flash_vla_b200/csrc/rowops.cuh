@@ -27,6 +27,7 @@ __global__ void __launch_bounds__(128) rownorm_kernel(const XT* __restrict__ x, 
                                                       const bf16* __restrict__ b, bf16* __restrict__ out,
                                                       float* __restrict__ factor_f32,
                                                       bf16* __restrict__ factor_bf16, int M, int K, int mode) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");      // no-op unless launched as a dependent
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= M) return;
     const XT* xr = x + (size_t)row * K;
@@ -89,6 +90,7 @@ __global__ void __launch_bounds__(256) small_k_proj_kernel(const XT* __restrict_
                                                            const bf16* __restrict__ bias, OT* __restrict__ out,
                                                            int M, int N, int K, int act) {
     __shared__ float xs[64];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int m = blockIdx.y;
     if (threadIdx.x < K) xs[threadIdx.x] = static_cast<float>(x[(size_t)m * K + threadIdx.x]);
     __syncthreads();
@@ -103,6 +105,7 @@ __global__ void __launch_bounds__(256) small_k_proj_kernel(const XT* __restrict_
 // The Euler update: out[m, :] += bias + rsqrt(mean(x[m]^2) + 1e-6) * (x[m, :] @ W), W (K, 32).
 // One CTA per row; the sum of squares rides along with the dot products so x is read once.
 // `out` is fp32 or bf16; when `mirror` is given the new value is also written there as bf16.
+// Each warp walks its share of K eight rows at a time so that eight loads are in flight.
 template <typename XT, typename OT>
 __global__ void __launch_bounds__(256) action_out_kernel(const XT* __restrict__ x, const bf16* __restrict__ W,
                                                          const bf16* __restrict__ bias, OT* __restrict__ out,
@@ -110,15 +113,28 @@ __global__ void __launch_bounds__(256) action_out_kernel(const XT* __restrict__ 
                                                          int K) {
     constexpr int N = 32;
     __shared__ float red[8][N + 1];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n = lane;                          // each warp covers all 32 outputs for its k slice
-    float acc = 0.f, ss = 0.f;
-    for (int k = warp; k < K; k += 8) {
-        float xv = static_cast<float>(x[(size_t)m * K + k]);
-        acc += xv * __bfloat162float(W[(size_t)k * N + n]);
-        ss += xv * xv;                           // identical in every lane of the warp
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, ss = 0.f;
+    const int per_warp = (K + 7) / 8;            // contiguous k range per warp
+    const int k_begin = warp * per_warp, k_end = min(K, k_begin + per_warp);
+    const float prev = static_cast<float>(out[(size_t)m * N + n]);
+    for (int k0 = k_begin; k0 < k_end; k0 += 8) {
+        float xv[8], wv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int k = k0 + u;
+            xv[u] = k < k_end ? static_cast<float>(x[(size_t)m * K + k]) : 0.f;
+            wv[u] = k < k_end ? __bfloat162float(W[(size_t)k * N + n]) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            acc[u] += xv[u] * wv[u];
+            ss += xv[u] * xv[u];                 // identical in every lane of the warp
+        }
     }
-    red[warp][n] = acc;
+    red[warp][n] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
     if (lane == 0) red[warp][N] = ss;
     __syncthreads();
     if (warp == 0) {
@@ -126,7 +142,6 @@ __global__ void __launch_bounds__(256) action_out_kernel(const XT* __restrict__ 
 #pragma unroll
         for (int w = 0; w < 8; ++w) { a += red[w][n]; s += red[w][N]; }
         float f = rsqrtf(s / K + 1e-6f);
-        float prev = static_cast<float>(out[(size_t)m * N + n]);
         float v = prev + __bfloat162float(bias[n]) + f * a;
         out[(size_t)m * N + n] = static_cast<OT>(v);
         if (mirror) mirror[(size_t)m * N + n] = __float2bfloat16_rn(v);
