@@ -172,6 +172,38 @@ int fvla_vision_patch_embed(const void* images, const void* patch_w, const void*
     return launch_gemm(a, nullptr, 0, S(stream));
 }
 
+// ---- patch embedding without caller-provided scratch -------------------------------------------
+// The patchified image matrix normally lives in scratch the caller hands in. Some callers have
+// nothing to hand in: a control loop that must not call cudaMalloc (it synchronises the device and
+// its latency is unbounded), a C program with no allocator of its own, or Python code whose
+// ScratchPool is already frozen and would raise on a new request. For them the matrix is kept in
+// this fixed device array instead. Every GPU that loads the library holds these bytes until the
+// process exits, hence the modest limit of four camera views.
+#define FVLA_NOALLOC_MAX_VIEWS 4
+static __device__ __align__(256) unsigned char g_patch_scratch[FVLA_NOALLOC_MAX_VIEWS * 256 * 592 * 2];
+
+// In host code `g_patch_scratch` is only a handle for the symbol, not an address the GPU can use;
+// the device address is looked up once per device (with that device current) and cached.
+static void* patch_scratch_device_ptr() {
+    constexpr int kMaxDevices = 64;
+    static void* cached[kMaxDevices] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_error("patch_embed_noalloc: cannot identify the current device");
+        return nullptr;
+    }
+    if (cached[dev] == nullptr) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_patch_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            set_error("patch_embed_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return nullptr;
+        }
+        cached[dev] = ptr;
+    }
+    return cached[dev];
+}
+
 static int norm_linear(const void* x, const void* nw, const void* nb, const void* w, const void* b,
                        void* out, void* x_norm, int M, int N, int K, int act, void* stream) {
     int rc = rownorm(x, 0, nw, nb, x_norm, nullptr, nullptr, M, K, 0, S(stream));
@@ -180,6 +212,23 @@ static int norm_linear(const void* x, const void* nw, const void* nb, const void
     a.A = B(x_norm); a.lda = K; a.B = B(w); a.ldb = N; a.C = out; a.ldc = N; a.bias = B(b);
     a.act = act; a.M = M; a.N = N; a.K = K;
     return launch_gemm(a, nullptr, 0, S(stream));
+}
+
+int fvla_vision_patch_embed_noalloc(const void* images, const void* patch_w, const void* patch_b,
+                                    const void* pos_emb, void* out, int views, void* stream) {
+    FVLA_REQUIRE(views > 0, "patch_embed_noalloc: views=%d", views);
+    if (views > FVLA_NOALLOC_MAX_VIEWS) {
+        set_error("patch_embed_noalloc: %d views exceed the built-in scratch (at most %d views, %zu bytes); "
+                  "use fvla_vision_patch_embed with caller scratch instead",
+                  views, FVLA_NOALLOC_MAX_VIEWS, sizeof(g_patch_scratch));
+        return FVLA_ERR_WORKSPACE;
+    }
+    void* scratch = patch_scratch_device_ptr();
+    if (scratch == nullptr) return FVLA_ERR_LAUNCH;
+    // The patchify kernel rewrites every element it later reads, zero padding included, so the
+    // previous call's contents never need clearing.
+    return fvla_vision_patch_embed(images, patch_w, patch_b, pos_emb, out, views, scratch,
+                                   fvla_patch_embed_workspace_bytes(views), stream);
 }
 
 int fvla_vision_norm_qkv(const void* x, const void* norm_w, const void* norm_b, const void* qkv_w,

@@ -16,6 +16,7 @@ _P, _I, _Z, _F = c_void_p, c_int, c_size_t, c_float
 # name -> argument ctypes (every function returns int except the three queries below)
 SIGNATURES: dict[str, list] = {
     "fvla_vision_patch_embed": [_P, _P, _P, _P, _P, _I, _P, _Z, _P],
+    "fvla_vision_patch_embed_noalloc": [_P, _P, _P, _P, _P, _I, _P],
     "fvla_vision_norm_qkv": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fvla_vision_attention": [_P, _P, _I, _I, _I, _I, _P],
     "fvla_vision_linear_bias_residual": [_P, _P, _P, _P, _P, _I, _I, _I, _P],

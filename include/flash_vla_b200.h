@@ -57,6 +57,18 @@ size_t fvla_patch_embed_workspace_bytes(int views);
 int fvla_vision_patch_embed(const void* images, const void* patch_w, const void* patch_b,
                             const void* pos_emb, void* out, int views, void* ws, size_t ws_bytes,
                             void* stream);
+/* No counterpart in the reference. Same result as fvla_vision_patch_embed, for callers that cannot
+ * supply scratch memory: a control loop that may not call cudaMalloc (it stalls the whole device for
+ * an unbounded time), a host program without an allocator, or code whose scratch pool is already
+ * frozen. The patch matrix is kept in a fixed array inside the library instead (1.2 MB per GPU,
+ * held until the process exits), which limits `views` to 4; more views return FVLA_ERR_WORKSPACE.
+ * This function itself never allocates. The first call on each device looks up the array's device
+ * address (cudaGetSymbolAddress, with that device current): make that first call before starting
+ * any stream capture. All calls on a device share the one array and it keeps the last call's
+ * contents; nothing in it has to start at zero, but two calls whose kernels may overlap on the GPU
+ * (different streams) race on it, so keep them on one stream or order them with events. */
+int fvla_vision_patch_embed_noalloc(const void* images, const void* patch_w, const void* patch_b,
+                                    const void* pos_emb, void* out, int views, void* stream);
 /* wrappers.py:268-276: x_norm = LayerNorm(x); out = x_norm @ W(K,N) + b. */
 int fvla_vision_norm_qkv(const void* x, const void* norm_w, const void* norm_b, const void* qkv_w,
                          const void* qkv_b, void* out, void* x_norm, int M, int N, int K,
