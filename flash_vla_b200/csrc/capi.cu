@@ -51,7 +51,7 @@ static inline bf16* Bm(void* p) { return reinterpret_cast<bf16*>(p); }
 
 static int rownorm(const void* x, int x_is_f32, const void* w, const void* b, void* out, float* f32,
                    void* fbf, int M, int K, int mode, cudaStream_t st) {
-    FVLA_REQUIRE(M > 0 && K > 0 && K % 2 == 0, "rownorm: bad shape M=%d K=%d", M, K);
+    FVLA_REQUIRE(M > 0 && K > 0 && K % 8 == 0 && K <= 8 * 32 * RN_MAX, "rownorm: bad shape M=%d K=%d (K %% 8 == 0, K <= %d)", M, K, 8 * 32 * RN_MAX);
     cudaError_t e;
     if (x_is_f32)
         e = launch_pdl(rownorm_kernel<float>, dim3((M + 3) / 4), dim3(128), 0, st, (const float*)x, B(w), B(b), Bm(out), f32, Bm(fbf), M, K, mode);

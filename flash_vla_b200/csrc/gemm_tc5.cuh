@@ -126,6 +126,7 @@ struct Tc5Args {
     GemmArgs g;                // epilogue description, shapes, C / R / bias / rope pointers
     int tiles_m, tiles_n, k_iters;
     int* status;               // device word: set non-zero when a bounded wait ran out
+    unsigned long long* dbg;   // optional development aid: globaltimer stamps, 8 per CTA
 };
 
 // Epilogue for 8 adjacent columns of one row (a: first / gate accumulator, u: up accumulator).
@@ -133,7 +134,7 @@ struct Tc5Args {
 // (the residual may alias the destination, so loads issued after a store would each wait for it).
 template <bool DUAL>
 __device__ __forceinline__ void epilogue8(const GemmArgs& p, int row, int col, float (&a)[8], const float (&u)[8],
-                                          uint4 rpre) {
+                                          uint4 rpre, bool use_pre) {
     if (DUAL) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) a[i] = gelu_f(a[i]) * u[i];
@@ -157,7 +158,7 @@ __device__ __forceinline__ void epilogue8(const GemmArgs& p, int row, int col, f
             float4 r0 = r[0], r1 = r[1];
             a[0] += r0.x; a[1] += r0.y; a[2] += r0.z; a[3] += r0.w; a[4] += r1.x; a[5] += r1.y; a[6] += r1.z; a[7] += r1.w;
         } else {
-            uint4 r = rpre;
+            uint4 r = use_pre ? rpre : *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.R) + (size_t)rr * p.ldr + col);
             float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y), r2 = unpack_bf16x2(r.z), r3 = unpack_bf16x2(r.w);
             a[0] += r0.x; a[1] += r0.y; a[2] += r1.x; a[3] += r1.y; a[4] += r2.x; a[5] += r2.y; a[6] += r3.x; a[7] += r3.y;
         }
@@ -202,13 +203,16 @@ struct Tc5Cfg {
     static constexpr int ACC_COLS = NB * BN;                    // TMEM columns per accumulator stage
     static constexpr int TMEM_COLS = 2 * ACC_COLS <= 32 ? 32 : (2 * ACC_COLS <= 64 ? 64 : (2 * ACC_COLS <= 128 ? 128 : (2 * ACC_COLS <= 256 ? 256 : 512)));
     static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
-    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BAR_BYTES;
+    static constexpr int EPI_WARPS = 8;                         // two warps per TMEM lane quadrant, half the columns each
+    static constexpr int EPI_STAGE_BYTES = 32 * 80;             // per warp: 32 rows x (64 B + 16 B pad)
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BAR_BYTES + EPI_WARPS * EPI_STAGE_BYTES;
     static_assert(2 * ACC_COLS <= 512, "two accumulator stages must fit in TMEM");
     static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN");
 };
 
 template <int BN, bool DUAL, int STAGES>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                 const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2) {
     using Cfg = Tc5Cfg<BN, DUAL, STAGES>;
@@ -228,10 +232,13 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const GemmArgs& p = args.g;
     const int num_tiles = args.tiles_m * args.tiles_n;
+    unsigned long long* dbg = args.dbg ? args.dbg + (size_t)blockIdx.x * 8 : nullptr;
+    auto stamp = [&](int i) { if (dbg) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); dbg[i] = t; } };
+    if (threadIdx.x == 0) stamp(0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), Cfg::EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -246,6 +253,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
     // Set-up above touched only this CTA's own shared memory and TMEM; from here on the operands
     // written by the previous kernel in the stream are read.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) stamp(1);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -287,6 +295,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait(full_bar(s), ph, abort_flag)) goto mma_done;
                     tc_fence_after();
+                    if (it == 0) stamp(2);
                     const uint32_t sA = smem_base + s * Cfg::STAGE_BYTES;
 #pragma unroll
                     for (int k16 = 0; k16 < BK / 16; ++k16) {
@@ -300,52 +309,109 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                     umma_commit(empty_bar(s));              // slot reusable once these MMAs have read it
                 }
                 umma_commit(accfull_bar(acc));              // accumulator complete
+                if (tcount == 0) stamp(3);
             }
         }
     mma_done:;
     } else {
-        const int quad = warp & 3;                          // TMEM lanes [32*quad, 32*quad+32)
+        // Eight epilogue warps: warp w reads TMEM lanes [32 (w % 4), +32) and owns one half of the
+        // tile's columns. One thread = one output row; results go through a small per-warp staging
+        // area so that global loads and stores touch 64 contiguous bytes per row (8 rows per request)
+        // instead of 16 bytes in each of 32 rows.
+        const int ew = warp - 2, quad = warp & 3, chalf = ew >> 2;
+        constexpr int HALF = BN / 2, CHUNKS = HALF / 32;
+        uint8_t* stg = smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES + ew * Cfg::EPI_STAGE_BYTES;
+        const bool plain = p.rope == nullptr && !p.c_f32;    // bf16 C (and bf16 residual): staged path
+        const int sr = lane >> 2, sp = lane & 3;              // staged access: row sr + 8 i, 16-byte piece sp
         uint32_t tcount = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
             const int acc = tcount & 1;
             const uint32_t acc_ph = (tcount >> 1) & 1u;
-            const int m0 = (tile % args.tiles_m) * BM, n0 = (tile / args.tiles_m) * BN;
+            const int m0 = (tile % args.tiles_m) * BM, n0 = (tile / args.tiles_m) * BN + chalf * HALF;
             const int row = m0 + quad * 32 + lane;
-            // bf16 residual of this thread's whole output row, fetched while the MMAs still run
-            constexpr bool kPreload = !DUAL && BN <= 128;      // wider tiles are only used without a residual
-            uint4 rpre[kPreload ? BN / 8 : 1];
-            if (kPreload && p.R && !p.c_f32 && row < p.M) {
-                const int rr = p.res_mod > 0 ? row % p.res_mod : row;
-                const bf16* rrow = static_cast<const bf16*>(p.R) + (size_t)rr * p.ldr + n0;
+            // operands that do not depend on the accumulator, fetched while the MMAs still run
+            float bias_lane[CHUNKS];
+            uint4 rco[CHUNKS][4];
 #pragma unroll
-                for (int j = 0; j < BN / 8; ++j)
-                    rpre[j] = (n0 + j * 8 < p.N) ? *reinterpret_cast<const uint4*>(rrow + j * 8) : make_uint4(0, 0, 0, 0);
+            for (int c = 0; c < CHUNKS; ++c) {
+                const int col = n0 + c * 32 + lane;
+                bias_lane[c] = (p.bias && col < p.N) ? __bfloat162float(__ldg(p.bias + col)) : 0.f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    rco[c][i] = make_uint4(0, 0, 0, 0);
+                    const int grow = m0 + quad * 32 + sr + 8 * i, gcol = n0 + c * 32 + sp * 8;
+                    if (plain && p.R && grow < p.M && gcol < p.N) {
+                        const int rr = p.res_mod > 0 ? grow % p.res_mod : grow;
+                        rco[c][i] = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.R) + (size_t)rr * p.ldr + gcol);
+                    }
+                }
             }
             if (!mbar_wait(accfull_bar(acc), acc_ph, abort_flag)) break;
             tc_fence_after();
-            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * Cfg::ACC_COLS;
-            // fully unrolled when a residual is preloaded (register array indexed by chunk);
-            // the gated form keeps one chunk live at a time
-#pragma unroll(kPreload ? BN / 32 : 1)
-            for (int c = 0; c < BN; c += 32) {
+            if (tcount == 0 && threadIdx.x == 64) stamp(4);
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * Cfg::ACC_COLS + chalf * HALF;
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c) {
                 float a[32], u[32];
-                tmem_ld32(t_row + c, a);
-                if (DUAL) tmem_ld32(t_row + BN + c, u);
-                if (row < p.M) {
+                tmem_ld32(t_row + c * 32, a);
+                if (DUAL) tmem_ld32(t_row + BN + c * 32, u);
+                if (plain) {
+                    float res[32];
+                    if (p.R) {
+                        // residual arrives coalesced (8 rows x 64 B per request); hand each thread its own row
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(stg + (sr + 8 * i) * 80 + sp * 16) = rco[c][i];
+                        __syncwarp();
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint4 r = *reinterpret_cast<const uint4*>(stg + lane * 80 + j * 16);
+                            const float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y), r2 = unpack_bf16x2(r.z), r3 = unpack_bf16x2(r.w);
+                            res[8 * j] = r0.x; res[8 * j + 1] = r0.y; res[8 * j + 2] = r1.x; res[8 * j + 3] = r1.y;
+                            res[8 * j + 4] = r2.x; res[8 * j + 5] = r2.y; res[8 * j + 6] = r3.x; res[8 * j + 7] = r3.y;
+                        }
+                        __syncwarp();
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float v = DUAL ? gelu_f(a[j]) * u[j] : a[j];
+                        v += __shfl_sync(0xffffffffu, bias_lane[c], j);
+                        if (p.act == 1) v = gelu_f(v);
+                        else if (p.act == 2) v = silu_f(v);
+                        if (p.R) v += res[j];
+                        a[j] = v;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint4*>(stg + lane * 80 + j * 16) =
+                            make_uint4(pack_bf16x2(a[8 * j], a[8 * j + 1]), pack_bf16x2(a[8 * j + 2], a[8 * j + 3]),
+                                       pack_bf16x2(a[8 * j + 4], a[8 * j + 5]), pack_bf16x2(a[8 * j + 6], a[8 * j + 7]));
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int grow = m0 + quad * 32 + sr + 8 * i, gcol = n0 + c * 32 + sp * 8;
+                        if (grow < p.M && gcol < p.N)
+                            *reinterpret_cast<uint4*>(static_cast<bf16*>(p.C) + (size_t)grow * p.ldc + gcol) =
+                                *reinterpret_cast<const uint4*>(stg + (sr + 8 * i) * 80 + sp * 16);
+                    }
+                    __syncwarp();
+                } else if (row < p.M) {
+                    // RoPE scatter or fp32 destination: direct per-row stores
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
-                        const int col = n0 + c + j;
+                        const int col = n0 + c * 32 + j;
                         if (col < p.N) {
                             float a8[8], u8[8];
 #pragma unroll
                             for (int i = 0; i < 8; ++i) { a8[i] = a[j + i]; u8[i] = DUAL ? u[j + i] : 0.f; }
-                            epilogue8<DUAL>(p, row, col, a8, u8, kPreload ? rpre[(c + j) / 8] : make_uint4(0, 0, 0, 0));
+                            uint4 rdirect = make_uint4(0, 0, 0, 0);
+                            epilogue8<DUAL>(p, row, col, a8, u8, rdirect, false);
                         }
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
+            if (tcount == 0 && threadIdx.x == 64) stamp(5);
             if (lane == 0) mbar_arrive(accempty_bar(acc));
         }
     }
@@ -356,6 +422,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
         tc_fence_after();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
+    if (threadIdx.x == 0) stamp(6);
     if (threadIdx.x == 0 && *abort_flag && args.status) atomicExch(args.status, 1);
 }
 
@@ -427,9 +494,10 @@ inline int launch_tc5_cfg(const GemmArgs& g, int* status, cudaStream_t st) {
     a.tiles_n = (g.N + BN - 1) / BN;
     a.k_iters = (g.K + BK - 1) / BK;
     a.status = status;
+    { const char* v = getenv("FVLA_DEBUG_TIMESTAMPS"); a.dbg = v ? reinterpret_cast<unsigned long long*>(strtoull(v, nullptr, 10)) : nullptr; }
     int tiles = a.tiles_m * a.tiles_n;
     int grid = tiles < num_sms() ? tiles : num_sms();
-    cudaError_t e = launch_pdl(kern, dim3(grid), dim3(192), Cfg::SMEM_BYTES, st, a, tmA, tmB, tmB2);
+    cudaError_t e = launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, a, tmA, tmB, tmB2);
     if (e != cudaSuccess) { set_error("tc5_gemm_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("tc5_gemm_kernel");
 }

@@ -11,17 +11,24 @@ namespace fvla {
 // mode 2: the factor rsqrt(mean(x^2) + 1e-6), written as fp32 and/or bf16 (base.py:344), plus
 // the normalised row when `out` is given.
 // The input row is bf16 or fp32 (XT); outputs are always bf16.
+// 8 consecutive elements of a row as floats (one 16-byte load for bf16, two for fp32).
 template <typename XT>
-__device__ __forceinline__ float2 load_pair(const XT* row, int i);
+__device__ __forceinline__ void load8(const XT* p, float (&v)[8]);
 template <>
-__device__ __forceinline__ float2 load_pair<bf16>(const bf16* row, int i) {
-    return unpack_bf16x2(reinterpret_cast<const uint32_t*>(row)[i]);
+__device__ __forceinline__ void load8<bf16>(const bf16* p, float (&v)[8]) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+    v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y; v[4] = f2.x; v[5] = f2.y; v[6] = f3.x; v[7] = f3.y;
 }
 template <>
-__device__ __forceinline__ float2 load_pair<float>(const float* row, int i) {
-    return reinterpret_cast<const float2*>(row)[i];
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
+// One warp per row, K % 8 == 0 and K <= 8 * 32 * RN_MAX. The whole row is fetched in one batch of
+// 16-byte loads and kept in registers, so the row is read once and normalised without a second trip.
+constexpr int RN_MAX = 8;            // 16-byte chunks per lane: rows up to 2048 elements
 template <typename XT>
 __global__ void __launch_bounds__(128) rownorm_kernel(const XT* __restrict__ x, const bf16* __restrict__ w,
                                                       const bf16* __restrict__ b, bf16* __restrict__ out,
@@ -31,16 +38,21 @@ __global__ void __launch_bounds__(128) rownorm_kernel(const XT* __restrict__ x, 
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= M) return;
     const XT* xr = x + (size_t)row * K;
-    const int pairs = K >> 1;
+    const int chunks = K >> 3;
+    float v[RN_MAX][8];
     float s = 0.f, ss = 0.f;
-    for (int i = lane; i < pairs; i += 32) {
-        float2 v = load_pair<XT>(xr, i);
-        s += v.x + v.y;
-        ss += v.x * v.x + v.y * v.y;
+#pragma unroll
+    for (int i = 0; i < RN_MAX; ++i) {
+        const int c = lane + 32 * i;
+        if (c < chunks) {
+            load8<XT>(xr + c * 8, v[i]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { s += v[i][e]; ss += v[i][e] * v[i][e]; }
+        }
     }
     s = warp_sum(s); ss = warp_sum(ss);
     if (mode == 2) {
-        float f = rsqrtf(ss / K + 1e-6f);
+        const float f = rsqrtf(ss / K + 1e-6f);
         if (lane == 0) {
             if (factor_f32) factor_f32[row] = f;
             if (factor_bf16) factor_bf16[row] = __float2bfloat16_rn(f);
@@ -48,22 +60,27 @@ __global__ void __launch_bounds__(128) rownorm_kernel(const XT* __restrict__ x, 
         if (out == nullptr) return;
         mode = 1;                               // also emit the normalised row
     }
-    uint32_t* orow = reinterpret_cast<uint32_t*>(out + (size_t)row * K);
-    if (mode == 1) {
-        float f = rsqrtf(ss / K + 1e-6f);
-        for (int i = lane; i < pairs; i += 32) {
-            float2 v = load_pair<XT>(xr, i);
-            orow[i] = pack_bf16x2(v.x * f, v.y * f);
+    bf16* orow = out + (size_t)row * K;
+    const float mean = mode == 1 ? 0.f : s / K;
+    const float inv = mode == 1 ? rsqrtf(ss / K + 1e-6f) : rsqrtf(ss / K - mean * mean + 1e-5f);
+#pragma unroll
+    for (int i = 0; i < RN_MAX; ++i) {
+        const int c = lane + 32 * i;
+        if (c < chunks) {
+            float y[8];
+            if (mode == 1) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) y[e] = v[i][e] * inv;
+            } else {
+                float wv[8], bv[8];
+                load8<bf16>(w + c * 8, wv);
+                load8<bf16>(b + c * 8, bv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) y[e] = (v[i][e] - mean) * inv * wv[e] + bv[e];
+            }
+            *reinterpret_cast<uint4*>(orow + c * 8) = make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]),
+                                                                 pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
         }
-        return;
-    }
-    const float mean = s / K;
-    const float inv = rsqrtf(ss / K - mean * mean + 1e-5f);
-    const uint32_t* wr = reinterpret_cast<const uint32_t*>(w);
-    const uint32_t* br = reinterpret_cast<const uint32_t*>(b);
-    for (int i = lane; i < pairs; i += 32) {
-        float2 v = load_pair<XT>(xr, i), wv = unpack_bf16x2(wr[i]), bv = unpack_bf16x2(br[i]);
-        orow[i] = pack_bf16x2((v.x - mean) * inv * wv.x + bv.x, (v.y - mean) * inv * wv.y + bv.y);
     }
 }
 
