@@ -136,6 +136,8 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
     // bf16 activations are fetched by TMA straight into the operand layout (rows past M read as
     // zero); fp32 activations are converted by the CTA further down.
     const bool x_by_tma = !p.x_f32 || p.x_shadow != nullptr;
+    if (tid == 32) { tc5::prefetch_tensormap(&tmW); if (EPI == EPI_GEGLU) tc5::prefetch_tensormap(&tmW2); }
+    if (tid == 64 && x_by_tma) tc5::prefetch_tensormap(&tmX);
     if (tid == 0) {
         mbar_init(done_bar, 1);
         mbar_init(in_bar, 1);
@@ -173,7 +175,9 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
         tma_load_2d(sX + warp * 8192, &tmX, bars + warp * 8, k0 + warp * 64, 0);
     // Tell the cluster this CTA is running (barriers initialised); peers wait for that before
     // sending anything into its shared memory.
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    // (the fence after the barrier initialisation already published it cluster-wide, so a relaxed
+    // arrive is enough; a releasing one would also wait for this thread's outstanding requests)
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
     // Epilogue operands that do not depend on the product (RoPE entries, residual values, bias) are
     // fetched now, so that their latency overlaps the weight stream instead of following the MMA.
@@ -295,7 +299,6 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
     const bool done = mbar_wait(done_bar, 0, abort_flag);
     tc5::tc_fence_after();
     FVLA_STAMP(3);
-
     __syncthreads();                                   // sums of squares are complete
     // Stage this CTA's partial tile as [token][n] fp32 over the (now idle) weight region.
     if (warp < 4) {
@@ -398,7 +401,8 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
     // received all of its slices, every outgoing copy of every CTA has completed.
     FVLA_STAMP(6);
     tc5::tc_fence_before();
-    cluster_sync_all();
+    // (execution barrier only: nothing read after it was written by a peer)
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
     if (warp == 0) {
         tc5::tc_fence_after();
         tc5::tmem_dealloc(tmem, 64);
