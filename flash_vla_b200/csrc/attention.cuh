@@ -318,7 +318,8 @@ __global__ void __launch_bounds__(128, 1) decoder_attention_cluster_kernel(const
         if (i_own)
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(in_bar), "r"(SPL * (4 * HD * 4 + 16)) : "memory");
     }
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    // relaxed: the fence above already published the barrier to the cluster
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
     auto load_rows = [&](uint32_t dst, const bf16* src, int row0, int row_lo, int row_hi, int nrows) {
         // rows [row0, row0 + nrows) of `src` into dst; only rows in [row_lo, row_hi) are fetched now
@@ -520,7 +521,8 @@ __global__ void __launch_bounds__(128, 1) decoder_attention_cluster_kernel(const
         }
     }
     // outgoing copies read this CTA's staging area: stay until every owner has everything
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    // (execution barrier only; nothing read after it was written by a peer)
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
     if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 3);
 }
 
