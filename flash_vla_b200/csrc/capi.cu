@@ -66,7 +66,13 @@ static int rownorm(const void* x, int x_is_f32, const void* w, const void* b, vo
 static size_t ws_factor_bytes(int M) { return align256((size_t)M * sizeof(float)); }
 static size_t ws_xnorm_bytes(int M, int K) { return align256((size_t)M * K * sizeof(bf16)); }
 static size_t op_ws_bytes(int M, int N, int K, bool dual) {
-    return ws_factor_bytes(M) + ws_xnorm_bytes(M, K) + plan_gemm_mma(M, N, K, dual).ws_bytes;
+    size_t gemm = plan_gemm_mma(M, N, K, dual).ws_bytes;
+    if (!dual && M > 64) {                      // the tcgen05 kernel may split K through scratch
+        size_t t = tc5::plan_tc5(M, N, K, true).ws_bytes;
+        if (getenv("FVLA_DEBUG_TC5_PLAN")) t = 256 * 64 + (size_t)4 * (M + 127) * (N + 255) * 4;      // room for any forced plan
+        if (t > gemm) gemm = t;
+    }
+    return ws_factor_bytes(M) + ws_xnorm_bytes(M, K) + gemm;
 }
 // Split-K part of an op workspace as (pointer, size); (nullptr, 0) when the caller gave none.
 static void gemm_ws(void* ws, size_t ws_bytes, int M, int K, void** p, size_t* n) {
@@ -113,7 +119,7 @@ static unsigned long long* debug_timestamps() {
 
 // GEMM dispatch: tcgen05 for M > 64, the warp-level kernel (with split-K) for the skinny shapes.
 static int launch_gemm(const GemmArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
-    if (tc5_enabled() && tc5::tc5_supports(a)) return tc5::launch_gemm_tc5(a, device_status_ptr(), st);
+    if (tc5_enabled() && tc5::tc5_supports(a)) return tc5::launch_gemm_tc5(a, device_status_ptr(), st, ws, ws_bytes);
     return launch_gemm_mma(a, ws, ws_bytes, st);
 }
 

@@ -18,6 +18,8 @@
 
 #include <cuda.h>
 
+#include <cstdio>
+
 #include "common.cuh"
 #include "gemm_mma.cuh"
 
@@ -125,6 +127,9 @@ __host__ __device__ constexpr uint32_t instr_desc(int n) {
 struct Tc5Args {
     GemmArgs g;                // epilogue description, shapes, C / R / bias / rope pointers
     int tiles_m, tiles_n, k_iters;
+    int splits, k_per_split;   // K split over `splits` work items per tile (k_per_split 64-wide steps each)
+    float* partial;            // [tile][split][BN/4 column quads][128 rows][4] fp32 partial products (splits > 1)
+    int* counters;             // one self-resetting arrival counter per tile (splits > 1)
     int* status;               // device word: set non-zero when a bounded wait ran out
     unsigned long long* dbg;   // optional development aid: globaltimer stamps, 8 per CTA
 };
@@ -231,7 +236,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const GemmArgs& p = args.g;
-    const int num_tiles = args.tiles_m * args.tiles_n;
+    const int num_tiles = args.tiles_m * args.tiles_n * args.splits;      // work items: (tile, k-split)
     unsigned long long* dbg = args.dbg ? args.dbg + (size_t)blockIdx.x * 8 : nullptr;
     auto stamp = [&](int i) { if (dbg) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); dbg[i] = t; } };
     if (threadIdx.x == 0) stamp(0);
@@ -262,8 +267,10 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
             if (DUAL) prefetch_tensormap(&tmB2);
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-                const int m0 = (tile % args.tiles_m) * BM, n0 = (tile / args.tiles_m) * BN;
-                for (int kt = 0; kt < args.k_iters; ++kt, ++it) {
+                const int t_idx = tile / args.splits, split = tile % args.splits;
+                const int m0 = (t_idx % args.tiles_m) * BM, n0 = (t_idx / args.tiles_m) * BN;
+                const int kt_beg = split * args.k_per_split, kt_end = min(args.k_iters, kt_beg + args.k_per_split);
+                for (int kt = kt_beg; kt < kt_end; ++kt, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) goto producer_done;
@@ -290,7 +297,9 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                 if (!mbar_wait(accempty_bar(acc), acc_ph ^ 1u, abort_flag)) goto mma_done;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_COLS;
-                for (int kt = 0; kt < args.k_iters; ++kt, ++it) {
+                const int split = tile % args.splits;
+                const int kt_beg = split * args.k_per_split, kt_end = min(args.k_iters, kt_beg + args.k_per_split);
+                for (int kt = kt_beg; kt < kt_end; ++kt, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait(full_bar(s), ph, abort_flag)) goto mma_done;
@@ -303,7 +312,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
                         for (int nb = 0; nb < NB; ++nb) {
                             const uint64_t bdesc = smem_desc(sA + Cfg::A_BYTES + nb * Cfg::B_BYTES + k16 * 2048, Cfg::SLAB, 1024);
-                            umma_bf16(d_tmem + nb * BN, adesc, bdesc, idesc, (kt > 0 || k16 > 0) ? 1u : 0u);
+                            umma_bf16(d_tmem + nb * BN, adesc, bdesc, idesc, (kt > kt_beg || k16 > 0) ? 1u : 0u);
                         }
                     }
                     umma_commit(empty_bar(s));              // slot reusable once these MMAs have read it
@@ -327,7 +336,8 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
             const int acc = tcount & 1;
             const uint32_t acc_ph = (tcount >> 1) & 1u;
-            const int m0 = (tile % args.tiles_m) * BM, n0 = (tile / args.tiles_m) * BN + chalf * HALF;
+            const int t_idx = tile / args.splits, split = tile % args.splits;
+            const int m0 = (t_idx % args.tiles_m) * BM, n0 = (t_idx / args.tiles_m) * BN + chalf * HALF;
             const int row = m0 + quad * 32 + lane;
             // operands that do not depend on the accumulator, fetched while the MMAs still run
             float bias_lane[CHUNKS];
@@ -350,11 +360,60 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
             tc_fence_after();
             if (tcount == 0 && threadIdx.x == 64) stamp(4);
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * Cfg::ACC_COLS + chalf * HALF;
+            bool from_partials = false;
+            if (!DUAL && args.splits > 1) {
+                // Publish this item's partial tile, then let the last-arriving item of the tile sum all
+                // of them (in split order, so the result does not depend on arrival order) and finish.
+#pragma unroll
+                for (int c = 0; c < CHUNKS; ++c) {
+                    float a[32];
+                    tmem_ld32(t_row + c * 32, a);
+                    // Partials use a tile-private layout [item][column quad][row][4] so that the 32 rows of a
+                    // warp write (and later read) 512 contiguous bytes per request.
+                    float* dst = args.partial + ((size_t)(t_idx * args.splits + split) * (BN / 4) + (chalf * CHUNKS + c) * 8) * (BM * 4) +
+                                 (quad * 32 + lane) * 4;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        __stcg(reinterpret_cast<float4*>(dst + (j / 4) * (BM * 4)), make_float4(a[j], a[j + 1], a[j + 2], a[j + 3]));
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(accempty_bar(acc));          // the accumulator stage is free again
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * Cfg::EPI_WARPS) : "memory");
+                int* flag = reinterpret_cast<int*>(smem_gen + STAGES * Cfg::STAGE_BYTES + (2 * STAGES + 4) * 8 + 12);
+                if (ew == 0 && lane == 0) {
+                    const int prev = atomicAdd(args.counters + t_idx, 1);
+                    const int last = prev == args.splits - 1;
+                    if (last) args.counters[t_idx] = 0;                  // self-reset: the graph replays this kernel
+                    *flag = last;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * Cfg::EPI_WARPS) : "memory");
+                const int last = *reinterpret_cast<volatile int*>(flag);
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * Cfg::EPI_WARPS) : "memory");   // flag may be rewritten by the next item
+                if (!last) continue;
+                __threadfence();
+                from_partials = true;
+            }
 #pragma unroll
             for (int c = 0; c < CHUNKS; ++c) {
                 float a[32], u[32];
-                tmem_ld32(t_row + c * 32, a);
-                if (DUAL) tmem_ld32(t_row + BN + c * 32, u);
+                if (from_partials) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) a[j] = 0.f;
+                    for (int sp_i = 0; sp_i < args.splits; ++sp_i) {
+                        const float* src = args.partial + ((size_t)(t_idx * args.splits + sp_i) * (BN / 4) + (chalf * CHUNKS + c) * 8) * (BM * 4) +
+                                           (quad * 32 + lane) * 4;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (j / 4) * (BM * 4)));
+                            a[j] += v.x; a[j + 1] += v.y; a[j + 2] += v.z; a[j + 3] += v.w;
+                        }
+                    }
+                } else {
+                    tmem_ld32(t_row + c * 32, a);
+                    if (DUAL) tmem_ld32(t_row + BN + c * 32, u);
+                }
                 if (plain) {
                     float res[32];
                     if (p.R) {
@@ -412,7 +471,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
             tc_fence_before();
             __syncwarp();
             if (tcount == 0 && threadIdx.x == 64) stamp(5);
-            if (lane == 0) mbar_arrive(accempty_bar(acc));
+            if (!from_partials && lane == 0) mbar_arrive(accempty_bar(acc));
         }
     }
 
@@ -471,8 +530,38 @@ inline int num_sms() {
     return sms;
 }
 
+struct Tc5Plan { int bn, splits; size_t ws_bytes; };
+
+// Per-step times (us) of one 64-wide k step at tile width 128 / 192 / 256, as measured on B200: the
+// shared-memory fill through L2 (about 64 B/clk/SM), not the MMA, sets them.
+inline float k_step_us(int bn) { return bn == 128 ? 0.30f : (bn == 192 ? 0.37f : 0.43f); }
+
+// Tile width and K split for a plain (non-gated) GEMM: minimise the estimated time of the slowest SM,
+// (waves of work items) x (k steps per item) x (time per step), plus, for a split, the cost of writing
+// and re-reading the fp32 partials. A split needs caller scratch and is only offered when `ws_ok`.
+inline Tc5Plan plan_tc5(int M, int N, int K, bool ws_ok) {
+    const int tiles_m = (M + BM - 1) / BM, sms = num_sms(), k_iters = (K + BK - 1) / BK;
+    Tc5Plan best{128, 1, 0};
+    float best_t = 1e30f;
+    for (int bn = 128; bn <= 256; bn += 64) {
+        const int tiles = tiles_m * ((N + bn - 1) / bn);
+        for (int s = 1; s <= (ws_ok ? 4 : 1); ++s) {
+            if (s > 1 && k_iters / s < 16) break;
+            const int per = (k_iters + s - 1) / s;
+            const int waves = (tiles * s + sms - 1) / sms;
+            float t = waves * (per * k_step_us(bn) + 4.0f);
+            if (s > 1) t += 3.0f + (float)s * M * N * 8.0f / 4.0e6f;      // partial traffic at about 4 TB/s
+            if (t < best_t) { best_t = t; best = Tc5Plan{bn, s, 0}; }
+        }
+    }
+    if (best.splits > 1)
+        best.ws_bytes = (((size_t)tiles_m * ((N + best.bn - 1) / best.bn) * sizeof(int) + 255) / 256) * 256 +
+                        (size_t)best.splits * tiles_m * ((N + best.bn - 1) / best.bn) * BM * best.bn * sizeof(float);
+    return best;
+}
+
 template <int BN, bool DUAL, int STAGES>
-inline int launch_tc5_cfg(const GemmArgs& g, int* status, cudaStream_t st) {
+inline int launch_tc5_cfg(const GemmArgs& g, int* status, cudaStream_t st, int splits = 1, void* ws = nullptr) {
     using Cfg = Tc5Cfg<BN, DUAL, STAGES>;
     auto kern = tc5_gemm_kernel<BN, DUAL, STAGES>;
     static bool configured = false;
@@ -493,9 +582,17 @@ inline int launch_tc5_cfg(const GemmArgs& g, int* status, cudaStream_t st) {
     a.tiles_m = (g.M + BM - 1) / BM;
     a.tiles_n = (g.N + BN - 1) / BN;
     a.k_iters = (g.K + BK - 1) / BK;
+    a.splits = splits;
+    a.k_per_split = (a.k_iters + splits - 1) / splits;
+    a.partial = nullptr; a.counters = nullptr;
+    if (splits > 1) {
+        const size_t counters = (((size_t)a.tiles_m * a.tiles_n * sizeof(int) + 255) / 256) * 256;
+        a.counters = reinterpret_cast<int*>(ws);
+        a.partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + counters);
+    }
     a.status = status;
     { const char* v = getenv("FVLA_DEBUG_TIMESTAMPS"); a.dbg = v ? reinterpret_cast<unsigned long long*>(strtoull(v, nullptr, 10)) : nullptr; }
-    int tiles = a.tiles_m * a.tiles_n;
+    int tiles = a.tiles_m * a.tiles_n * splits;
     int grid = tiles < num_sms() ? tiles : num_sms();
     cudaError_t e = launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, a, tmA, tmB, tmB2);
     if (e != cudaSuccess) { set_error("tc5_gemm_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
@@ -508,28 +605,23 @@ inline bool tc5_supports(const GemmArgs& g) {
            aligned16(g.A) && aligned16(g.B) && (g.B2 == nullptr || aligned16(g.B2));
 }
 
-// Tile width for a plain GEMM: the one that minimises (waves over the SMs) x (tile width), i.e. the
-// time of the slowest SM. Wider tiles also need less shared-memory fill per MMA. A residual is
-// preloaded per output row and is only supported at width 128.
-inline int pick_bn(const GemmArgs& g) {
-    if (g.R != nullptr) return 128;
-    const int tiles_m = (g.M + BM - 1) / BM, sms = num_sms();
-    int best = 128, best_cost = 1 << 30;
-    for (int bn = 128; bn <= 256; bn += 64) {
-        const int tiles = tiles_m * ((g.N + bn - 1) / bn);
-        const int cost = ((tiles + sms - 1) / sms) * bn;
-        if (cost < best_cost) { best_cost = cost; best = bn; }
-    }
-    return best;
-}
-
-inline int launch_gemm_tc5(GemmArgs g, int* status, cudaStream_t st) {
+inline int launch_gemm_tc5(GemmArgs g, int* status, cudaStream_t st, void* ws = nullptr, size_t ws_bytes = 0) {
     if (g.Kb == 0) g.Kb = g.K;
     if (g.B2 != nullptr) return launch_tc5_cfg<128, true, 4>(g, status, st);
-    switch (pick_bn(g)) {
-        case 256: return launch_tc5_cfg<256, false, 4>(g, status, st);
-        case 192: return launch_tc5_cfg<192, false, 5>(g, status, st);
-        default: return launch_tc5_cfg<128, false, 6>(g, status, st);
+    Tc5Plan pl = plan_tc5(g.M, g.N, g.K, ws != nullptr);
+    if (const char* dbg = getenv("FVLA_DEBUG_TC5_PLAN")) {          // "bn,splits": development aid
+        int bn = 128, sp = 1;
+        if (sscanf(dbg, "%d,%d", &bn, &sp) == 2 && ws != nullptr) {
+            pl.bn = bn; pl.splits = sp;
+            pl.ws_bytes = sp > 1 ? 256 * ((((size_t)((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn)) * 4 + 255) / 256) +
+                                       (size_t)sp * ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn) * BM * bn * 4 : 0;
+        }
+    }
+    if (pl.splits > 1 && (ws_bytes < pl.ws_bytes || g.rope != nullptr || g.c_f32)) pl = plan_tc5(g.M, g.N, g.K, false);
+    switch (pl.bn) {
+        case 256: return launch_tc5_cfg<256, false, 4>(g, status, st, pl.splits, ws);
+        case 192: return launch_tc5_cfg<192, false, 5>(g, status, st, pl.splits, ws);
+        default: return launch_tc5_cfg<128, false, 6>(g, status, st, pl.splits, ws);
     }
 }
 
