@@ -11,6 +11,7 @@
 #include "gemm_mma.cuh"
 #include "gemm_tc5.cuh"
 #include "gemm_skinny.cuh"
+#include "gemm_tc5x2.cuh"
 #include "rowops.cuh"
 
 namespace fvla {
@@ -118,7 +119,23 @@ static unsigned long long* debug_timestamps() {
 }
 
 // GEMM dispatch: tcgen05 for M > 64, the warp-level kernel (with split-K) for the skinny shapes.
+// FVLA_GEMM_PAIR=0 keeps the gated FFN on the one-SM kernel (diagnostic switch).
+static bool pair_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* v = getenv("FVLA_GEMM_PAIR");
+        on = (v != nullptr && v[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
 static int launch_gemm(const GemmArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
+    if (tc5_enabled() && pair_enabled() && a.B2 != nullptr && tc5::tc5_supports(a)) {
+        GemmArgs g = a;
+        if (g.Kb == 0) g.Kb = g.K;
+        int rc = tc5x2::launch_geglu_pair(g, device_status_ptr(), st);
+        if (rc != FVLA_ERR_UNSUPPORTED) return rc;
+    }
     if (tc5_enabled() && tc5::tc5_supports(a)) return tc5::launch_gemm_tc5(a, device_status_ptr(), st, ws, ws_bytes);
     return launch_gemm_mma(a, ws, ws_bytes, st);
 }

@@ -1,0 +1,254 @@
+// Two-SM tcgen05 GEMM for the gated FFN of the prefix encoder: out = gelu(A @ Wg) * (A @ Wu).
+//
+// A pair of CTAs (a cluster of 2) computes a 256-row x 128-column tile of `out` with
+// tcgen05.mma.cta_group::2: one MMA of shape M = 256, N = 256, K = 16 whose first 128 B columns are
+// gate columns held in the leader CTA's shared memory and whose last 128 are the matching up
+// columns held in the peer's. Each CTA therefore stages only its own 128 rows of A (16 KB) and ONE
+// 128-column weight tile (16 KB) per 64-wide k step - 32 KB per 512 tensor-core clocks, which is
+// what the L2 -> SM path can deliver (about 64 B/clk/SM); the one-SM kernel needs 48 KB for the
+// same work and is fill-bound. Each CTA ends up with gate and up accumulators for its own 128 rows
+// in its own TMEM and runs the GeGLU epilogue on them.
+//
+// Synchronisation (all waits bounded, as in the one-SM kernel):
+//   full[s]      in the leader only; the leader's producer expects the bytes of BOTH CTAs, and both
+//                CTAs' TMA loads complete on it (cta_group::2 load with the leader's barrier address)
+//   empty[s]     in both CTAs, released by the leader's tcgen05.commit multicast to both
+//   accfull[a]   in both CTAs, same multicast commit after the last k step of a tile
+//   accempty[a]  in the leader only, 16 arrivals: the 8 epilogue warps of each CTA
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_tc5.cuh"
+
+namespace fvla {
+namespace tc5x2 {
+
+using namespace tc5;
+
+constexpr int STAGES = 6;
+constexpr int STAGE_BYTES = 32768;                 // A 128 x 64 + B 64 x 128, bf16
+constexpr int EPI_WARPS = 8;
+constexpr int EPI_STAGE_BYTES = 32 * 80;
+constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BAR_BYTES + EPI_WARPS * EPI_STAGE_BYTES;
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;      // clears the CTA-rank bit: address in the leader CTA
+
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {      // arrives on `bar` in both CTAs
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// kind::f16, fp32 accumulate, bf16 A (K-major) and B (MN-major), M = 256 over the CTA pair, N = 256.
+__host__ __device__ constexpr uint32_t pair_idesc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(320, 1)
+tc5x2_geglu_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmG,
+                   const __grid_constant__ CUtensorMap tmU) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + s * 8; };
+    auto empty_bar = [&](int s) { return bars + (STAGES + s) * 8; };
+    auto accfull_bar = [&](int a) { return bars + (2 * STAGES + a) * 8; };
+    auto accempty_bar = [&](int a) { return bars + (2 * STAGES + 2 + a) * 8; };
+    const uint32_t tmem_slot = bars + (2 * STAGES + 4) * 8;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const GemmArgs& p = args.g;
+    const int num_tiles = args.tiles_m * args.tiles_n;           // pair tiles: 256 rows x 128 columns
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), 2 * EPI_WARPS); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    // both CTAs' barriers exist before either side signals the other
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    if (warp == 0) {
+        if (lane == 0) {
+            prefetch_tensormap(&tmA);
+            prefetch_tensormap(rank == 0 ? &tmG : &tmU);
+            const CUtensorMap* tmB = rank == 0 ? &tmG : &tmU;
+            uint32_t it = 0;
+            for (int tile = pair; tile < num_tiles; tile += pairs) {
+                const int m0 = (tile % args.tiles_m) * 256 + (int)rank * 128, n0 = (tile / args.tiles_m) * 128;
+                for (int kt = 0; kt < args.k_iters; ++kt, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) goto producer_done;
+                    if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);      // the bytes of both CTAs
+                    const uint32_t sA = smem_base + s * STAGE_BYTES;
+                    const uint32_t leader_full = full_bar(s) & kPeerBitMask;
+                    tma_load_2d_pair(sA, &tmA, leader_full, kt * BK, m0);
+                    tma_load_2d_pair(sA + 16384, tmB, leader_full, n0, kt * BK);
+                    tma_load_2d_pair(sA + 16384 + 8192, tmB, leader_full, n0 + 64, kt * BK);
+                }
+            }
+        }
+    producer_done:;
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = pair_idesc();
+            uint32_t it = 0, tcount = 0;
+            for (int tile = pair; tile < num_tiles; tile += pairs, ++tcount) {
+                const int acc = tcount & 1;
+                const uint32_t acc_ph = (tcount >> 1) & 1u;
+                if (!mbar_wait(accempty_bar(acc), acc_ph ^ 1u, abort_flag)) goto mma_done;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * 256;
+                for (int kt = 0; kt < args.k_iters; ++kt, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(full_bar(s), ph, abort_flag)) goto mma_done;
+                    tc_fence_after();
+                    const uint32_t sA = smem_base + s * STAGE_BYTES;
+#pragma unroll
+                    for (int k16 = 0; k16 < BK / 16; ++k16) {
+                        const uint64_t adesc = smem_desc(sA + k16 * 32, 16, 1024);
+                        const uint64_t bdesc = smem_desc(sA + 16384 + k16 * 2048, 8192, 1024);
+                        umma_bf16_pair(d_tmem, adesc, bdesc, idesc, (kt > 0 || k16 > 0) ? 1u : 0u);
+                    }
+                    umma_commit_pair(empty_bar(s));
+                }
+                umma_commit_pair(accfull_bar(acc));
+            }
+        }
+    mma_done:;
+    } else {
+        const int ew = warp - 2, quad = warp & 3, chalf = ew >> 2;          // 64 output columns per warp
+        uint8_t* stg = smem_gen + STAGES * STAGE_BYTES + BAR_BYTES + ew * EPI_STAGE_BYTES;
+        const int sr = lane >> 2, sp = lane & 3;
+        uint32_t tcount = 0;
+        for (int tile = pair; tile < num_tiles; tile += pairs, ++tcount) {
+            const int acc = tcount & 1;
+            const uint32_t acc_ph = (tcount >> 1) & 1u;
+            const int m0 = (tile % args.tiles_m) * 256 + (int)rank * 128, n0 = (tile / args.tiles_m) * 128 + chalf * 64;
+            if (!mbar_wait(accfull_bar(acc), acc_ph, abort_flag)) break;
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * 256 + chalf * 64;
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                float a[32], u[32];
+                tmem_ld32(t_row + c * 32, a);            // gate columns
+                tmem_ld32(t_row + 128 + c * 32, u);      // up columns
+#pragma unroll
+                for (int j = 0; j < 32; ++j) a[j] = gelu_f(a[j]) * u[j];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    *reinterpret_cast<uint4*>(stg + lane * 80 + j * 16) =
+                        make_uint4(pack_bf16x2(a[8 * j], a[8 * j + 1]), pack_bf16x2(a[8 * j + 2], a[8 * j + 3]),
+                                   pack_bf16x2(a[8 * j + 4], a[8 * j + 5]), pack_bf16x2(a[8 * j + 6], a[8 * j + 7]));
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int grow = m0 + quad * 32 + sr + 8 * i, gcol = n0 + c * 32 + sp * 8;
+                    if (grow < p.M && gcol < p.N)
+                        *reinterpret_cast<uint4*>(static_cast<bf16*>(p.C) + (size_t)grow * p.ldc + gcol) =
+                            *reinterpret_cast<const uint4*>(stg + (sr + 8 * i) * 80 + sp * 16);
+                }
+                __syncwarp();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                uint32_t leader_bar;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(leader_bar) : "r"(accempty_bar(acc)), "r"(0));
+                mbar_arrive_cluster(leader_bar);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    // neither CTA may leave while the other can still signal its barriers or read its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+    if (threadIdx.x == 0 && *abort_flag && args.status) atomicExch(args.status, 4);
+}
+
+// Gated FFN with M > 128 rows, N a multiple of 128: returns FVLA_ERR_UNSUPPORTED otherwise.
+inline int launch_geglu_pair(const GemmArgs& g, int* status, cudaStream_t st) {
+    if (g.B2 == nullptr || g.N % 128 != 0 || g.M <= 128 || g.rope != nullptr || g.c_f32 || g.bias != nullptr || g.R != nullptr ||
+        g.act != 0)
+        return FVLA_ERR_UNSUPPORTED;
+    auto kern = tc5x2_geglu_kernel;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
+        configured = true;
+    }
+    CUtensorMap tmA, tmG, tmU;
+    int rc = make_map(&tmA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, 128);
+    if (rc) return rc;
+    rc = make_map(&tmG, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, 64, BK);
+    if (rc) return rc;
+    rc = make_map(&tmU, g.B2, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, 64, BK);
+    if (rc) return rc;
+    Tc5Args a{};
+    a.g = g;
+    a.tiles_m = (g.M + 255) / 256;
+    a.tiles_n = g.N / 128;
+    a.k_iters = (g.K + BK - 1) / BK;
+    a.splits = 1; a.k_per_split = a.k_iters;
+    a.status = status;
+    const int tiles = a.tiles_m * a.tiles_n;
+    const int max_pairs = num_sms() / 2;
+    const int pairs = tiles < max_pairs ? tiles : max_pairs;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(320, 1, 1);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, tmA, tmG, tmU);
+    if (e != cudaSuccess) { set_error("tc5x2_geglu_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
+    return check_launch("tc5x2_geglu_kernel");
+}
+
+}  // namespace tc5x2
+}  // namespace fvla
