@@ -70,6 +70,8 @@ static size_t op_ws_bytes(int M, int N, int K, bool dual) {
     size_t gemm = plan_gemm_mma(M, N, K, dual).ws_bytes;
     if (!dual && M > 64) {                      // the tcgen05 kernel may split K through scratch
         size_t t = tc5::plan_tc5(M, N, K, true).ws_bytes;
+        size_t t2 = tc5x2::plan_pair_plain(M, N, K, true).ws_bytes;
+        if (t2 > t) t = t2;
         if (getenv("FVLA_DEBUG_TC5_PLAN")) t = 256 * 64 + (size_t)4 * (M + 127) * (N + 255) * 4;      // room for any forced plan
         if (t > gemm) gemm = t;
     }
@@ -135,6 +137,16 @@ static int launch_gemm(const GemmArgs& a, void* ws, size_t ws_bytes, cudaStream_
         if (g.Kb == 0) g.Kb = g.K;
         int rc = tc5x2::launch_geglu_pair(g, device_status_ptr(), st);
         if (rc != FVLA_ERR_UNSUPPORTED) return rc;
+    }
+    if (tc5_enabled() && pair_enabled() && a.B2 == nullptr && tc5::tc5_supports(a)) {
+        // residual projections: take the CTA-pair kernel when its estimate beats the one-SM plan
+        GemmArgs g = a;
+        if (g.Kb == 0) g.Kb = g.K;
+        tc5x2::PairPlan pp = tc5x2::plan_pair_plain(g.M, g.N, g.K, ws != nullptr);
+        if (pp.ok && pp.est_us < tc5::plan_tc5(g.M, g.N, g.K, ws != nullptr).est_us) {
+            int rc = tc5x2::launch_plain_pair(g, ws, ws_bytes, device_status_ptr(), st);
+            if (rc != FVLA_ERR_UNSUPPORTED) return rc;
+        }
     }
     if (tc5_enabled() && tc5::tc5_supports(a)) return tc5::launch_gemm_tc5(a, device_status_ptr(), st, ws, ws_bytes);
     return launch_gemm_mma(a, ws, ws_bytes, st);

@@ -530,7 +530,7 @@ inline int num_sms() {
     return sms;
 }
 
-struct Tc5Plan { int bn, splits; size_t ws_bytes; };
+struct Tc5Plan { int bn, splits; size_t ws_bytes; float est_us; };
 
 // Per-step times (us) of one 64-wide k step at tile width 128 / 192 / 256, as measured on B200: the
 // shared-memory fill through L2 (about 64 B/clk/SM), not the MMA, sets them.
@@ -541,7 +541,7 @@ inline float k_step_us(int bn) { return bn == 128 ? 0.30f : (bn == 192 ? 0.37f :
 // and re-reading the fp32 partials. A split needs caller scratch and is only offered when `ws_ok`.
 inline Tc5Plan plan_tc5(int M, int N, int K, bool ws_ok) {
     const int tiles_m = (M + BM - 1) / BM, sms = num_sms(), k_iters = (K + BK - 1) / BK;
-    Tc5Plan best{128, 1, 0};
+    Tc5Plan best{128, 1, 0, 1e30f};
     float best_t = 1e30f;
     for (int bn = 128; bn <= 256; bn += 64) {
         const int tiles = tiles_m * ((N + bn - 1) / bn);
@@ -551,7 +551,7 @@ inline Tc5Plan plan_tc5(int M, int N, int K, bool ws_ok) {
             const int waves = (tiles * s + sms - 1) / sms;
             float t = waves * (per * k_step_us(bn) + 4.0f);
             if (s > 1) t += 3.0f + (float)s * M * N * 8.0f / 4.0e6f;      // partial traffic at about 4 TB/s
-            if (t < best_t) { best_t = t; best = Tc5Plan{bn, s, 0}; }
+            if (t < best_t) { best_t = t; best = Tc5Plan{bn, s, 0, t}; }
         }
     }
     if (best.splits > 1)

@@ -1,4 +1,5 @@
-// Two-SM tcgen05 GEMM for the gated FFN of the prefix encoder: out = gelu(A @ Wg) * (A @ Wu).
+// Two-SM tcgen05 GEMMs: the gated FFN of the prefix encoder, out = gelu(A @ Wg) * (A @ Wu), and the
+// residual projections out += A @ W (optionally with K split over several work items).
 //
 // A pair of CTAs (a cluster of 2) computes a 256-row x 128-column tile of `out` with
 // tcgen05.mma.cta_group::2: one MMA of shape M = 256, N = 256, K = 16 whose first 128 B columns are
@@ -7,7 +8,8 @@
 // 128-column weight tile (16 KB) per 64-wide k step - 32 KB per 512 tensor-core clocks, which is
 // what the L2 -> SM path can deliver (about 64 B/clk/SM); the one-SM kernel needs 48 KB for the
 // same work and is fill-bound. Each CTA ends up with gate and up accumulators for its own 128 rows
-// in its own TMEM and runs the GeGLU epilogue on them.
+// in its own TMEM and runs the GeGLU epilogue on them. In the plain (residual) form the pair computes a
+// 256 x 256 tile: the leader stages B columns [n0, n0+128), the peer [n0+128, n0+256).
 //
 // Synchronisation (all waits bounded, as in the one-SM kernel):
 //   full[s]      in the leader only; the leader's producer expects the bytes of BOTH CTAs, and both
@@ -59,8 +61,9 @@ __host__ __device__ constexpr uint32_t pair_idesc() {
     return (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
+template <bool DUAL>
 __global__ void __launch_bounds__(320, 1)
-tc5x2_geglu_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmG,
+tc5x2_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmG,
                    const __grid_constant__ CUtensorMap tmU) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -78,7 +81,8 @@ tc5x2_geglu_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, 
     uint32_t rank;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
     const GemmArgs& p = args.g;
-    const int num_tiles = args.tiles_m * args.tiles_n;           // pair tiles: 256 rows x 128 columns
+    constexpr int TILE_N = DUAL ? 128 : 256;                      // output columns of a pair tile
+    const int num_tiles = args.tiles_m * args.tiles_n * args.splits;   // work items: (pair tile, k-split)
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
@@ -102,12 +106,16 @@ tc5x2_geglu_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, 
     if (warp == 0) {
         if (lane == 0) {
             prefetch_tensormap(&tmA);
-            prefetch_tensormap(rank == 0 ? &tmG : &tmU);
-            const CUtensorMap* tmB = rank == 0 ? &tmG : &tmU;
+            const CUtensorMap* tmB = (DUAL && rank == 1) ? &tmU : &tmG;
+            prefetch_tensormap(tmB);
             uint32_t it = 0;
             for (int tile = pair; tile < num_tiles; tile += pairs) {
-                const int m0 = (tile % args.tiles_m) * 256 + (int)rank * 128, n0 = (tile / args.tiles_m) * 128;
-                for (int kt = 0; kt < args.k_iters; ++kt, ++it) {
+                const int t_idx = tile / args.splits, split = tile % args.splits;
+                const int m0 = (t_idx % args.tiles_m) * 256 + (int)rank * 128;
+                // the B columns this CTA stages: gated form, both CTAs the same 128 (gate / up matrix); plain form, its half of 256
+                const int n0 = (t_idx / args.tiles_m) * TILE_N + (DUAL ? 0 : (int)rank * 128);
+                const int kt_beg = split * args.k_per_split, kt_end = min(args.k_iters, kt_beg + args.k_per_split);
+                for (int kt = kt_beg; kt < kt_end; ++kt, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) goto producer_done;
@@ -131,7 +139,9 @@ tc5x2_geglu_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, 
                 if (!mbar_wait(accempty_bar(acc), acc_ph ^ 1u, abort_flag)) goto mma_done;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * 256;
-                for (int kt = 0; kt < args.k_iters; ++kt, ++it) {
+                const int split = tile % args.splits;
+                const int kt_beg = split * args.k_per_split, kt_end = min(args.k_iters, kt_beg + args.k_per_split);
+                for (int kt = kt_beg; kt < kt_end; ++kt, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait(full_bar(s), ph, abort_flag)) goto mma_done;
@@ -141,7 +151,7 @@ tc5x2_geglu_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, 
                     for (int k16 = 0; k16 < BK / 16; ++k16) {
                         const uint64_t adesc = smem_desc(sA + k16 * 32, 16, 1024);
                         const uint64_t bdesc = smem_desc(sA + 16384 + k16 * 2048, 8192, 1024);
-                        umma_bf16_pair(d_tmem, adesc, bdesc, idesc, (kt > 0 || k16 > 0) ? 1u : 0u);
+                        umma_bf16_pair(d_tmem, adesc, bdesc, idesc, (kt > kt_beg || k16 > 0) ? 1u : 0u);
                     }
                     umma_commit_pair(empty_bar(s));
                 }
@@ -150,24 +160,118 @@ tc5x2_geglu_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, 
         }
     mma_done:;
     } else {
-        const int ew = warp - 2, quad = warp & 3, chalf = ew >> 2;          // 64 output columns per warp
+        // 8 epilogue warps per CTA: warp w reads TMEM lanes [32 (w % 4), +32) and owns half of the tile's
+        // output columns (64 in the gated form, 128 in the plain form), 32 at a time.
+        const int ew = warp - 2, quad = warp & 3, chalf = ew >> 2;
+        constexpr int SPAN = TILE_N / 2, CHUNKS = SPAN / 32;
         uint8_t* stg = smem_gen + STAGES * STAGE_BYTES + BAR_BYTES + ew * EPI_STAGE_BYTES;
         const int sr = lane >> 2, sp = lane & 3;
+        auto release_acc = [&](int acc) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                uint32_t leader_bar;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(leader_bar) : "r"(accempty_bar(acc)), "r"(0));
+                mbar_arrive_cluster(leader_bar);
+            }
+        };
         uint32_t tcount = 0;
         for (int tile = pair; tile < num_tiles; tile += pairs, ++tcount) {
             const int acc = tcount & 1;
             const uint32_t acc_ph = (tcount >> 1) & 1u;
-            const int m0 = (tile % args.tiles_m) * 256 + (int)rank * 128, n0 = (tile / args.tiles_m) * 128 + chalf * 64;
+            const int t_idx = tile / args.splits, split = tile % args.splits;
+            const int m0 = (t_idx % args.tiles_m) * 256 + (int)rank * 128, n0 = (t_idx / args.tiles_m) * TILE_N + chalf * SPAN;
+            // the residual of this warp's rows, fetched (coalesced) while the MMAs still run
+            uint4 rco[DUAL ? 1 : CHUNKS][4];
+            if (!DUAL) {
+#pragma unroll
+                for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        rco[DUAL ? 0 : c][i] = make_uint4(0, 0, 0, 0);
+                        const int grow = m0 + quad * 32 + sr + 8 * i, gcol = n0 + c * 32 + sp * 8;
+                        if (p.R && grow < p.M && gcol < p.N)
+                            rco[DUAL ? 0 : c][i] = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.R) + (size_t)grow * p.ldr + gcol);
+                    }
+            }
             if (!mbar_wait(accfull_bar(acc), acc_ph, abort_flag)) break;
             tc_fence_after();
-            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * 256 + chalf * 64;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * 256 + chalf * SPAN;
+            bool from_partials = false;
+            if (!DUAL && args.splits > 1) {
+                // publish this item's partial rows (layout [item][rank][column quad][row][4], coalesced), then the
+                // last-arriving split of this CTA's half tile sums all of them in split order
 #pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                float a[32], u[32];
-                tmem_ld32(t_row + c * 32, a);            // gate columns
-                tmem_ld32(t_row + 128 + c * 32, u);      // up columns
+                for (int c = 0; c < CHUNKS; ++c) {
+                    float a[32];
+                    tmem_ld32(t_row + c * 32, a);
+                    float* dst = args.partial + ((size_t)((t_idx * args.splits + split) * 2 + rank) * 64 + (chalf * CHUNKS + c) * 8) * 512 +
+                                 (quad * 32 + lane) * 4;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) a[j] = gelu_f(a[j]) * u[j];
+                    for (int j = 0; j < 32; j += 4)
+                        __stcg(reinterpret_cast<float4*>(dst + (j / 4) * 512), make_float4(a[j], a[j + 1], a[j + 2], a[j + 3]));
+                }
+                release_acc(acc);
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
+                int* flag = reinterpret_cast<int*>(smem_gen + STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 12);
+                if (ew == 0 && lane == 0) {
+                    const int prev = atomicAdd(args.counters + t_idx * 2 + rank, 1);
+                    const int last = prev == args.splits - 1;
+                    if (last) args.counters[t_idx * 2 + rank] = 0;
+                    *flag = last;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
+                const int last = *reinterpret_cast<volatile int*>(flag);
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
+                if (!last) continue;
+                __threadfence();
+                from_partials = true;
+            }
+#pragma unroll 1
+            for (int c = 0; c < CHUNKS; ++c) {
+                float a[32];
+                if (from_partials) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) a[j] = 0.f;
+                    for (int sp_i = 0; sp_i < args.splits; ++sp_i) {
+                        const float* src = args.partial + ((size_t)((t_idx * args.splits + sp_i) * 2 + rank) * 64 + (chalf * CHUNKS + c) * 8) * 512 +
+                                           (quad * 32 + lane) * 4;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (j / 4) * 512));
+                            a[j] += v.x; a[j + 1] += v.y; a[j + 2] += v.z; a[j + 3] += v.w;
+                        }
+                    }
+                } else {
+                    tmem_ld32(t_row + c * 32, a);
+                }
+                if (DUAL) {
+                    float u[32];
+                    tmem_ld32(t_row + 128 + c * 32, u);      // matching up columns
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) a[j] = gelu_f(a[j]) * u[j];
+                } else if (p.R) {
+                    // hand each thread the residual of its own row (arrived as 8 rows x 64 B per request)
+                    uint4 mine[4];
+#pragma unroll
+                    for (int cc = 0; cc < CHUNKS; ++cc)
+                        if (cc == c) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) mine[i] = rco[DUAL ? 0 : cc][i];
+                        }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(stg + (sr + 8 * i) * 80 + sp * 16) = mine[i];
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 r = *reinterpret_cast<const uint4*>(stg + lane * 80 + j * 16);
+                        const float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y), r2 = unpack_bf16x2(r.z), r3 = unpack_bf16x2(r.w);
+                        a[8 * j] += r0.x; a[8 * j + 1] += r0.y; a[8 * j + 2] += r1.x; a[8 * j + 3] += r1.y;
+                        a[8 * j + 4] += r2.x; a[8 * j + 5] += r2.y; a[8 * j + 6] += r3.x; a[8 * j + 7] += r3.y;
+                    }
+                    __syncwarp();
+                }
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
                     *reinterpret_cast<uint4*>(stg + lane * 80 + j * 16) =
@@ -183,13 +287,7 @@ tc5x2_geglu_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, 
                 }
                 __syncwarp();
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                uint32_t leader_bar;
-                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(leader_bar) : "r"(accempty_bar(acc)), "r"(0));
-                mbar_arrive_cluster(leader_bar);
-            }
+            if (!from_partials) release_acc(acc);
         }
     }
 
@@ -204,12 +302,28 @@ tc5x2_geglu_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, 
     if (threadIdx.x == 0 && *abort_flag && args.status) atomicExch(args.status, 4);
 }
 
-// Gated FFN with M > 128 rows, N a multiple of 128: returns FVLA_ERR_UNSUPPORTED otherwise.
-inline int launch_geglu_pair(const GemmArgs& g, int* status, cudaStream_t st) {
-    if (g.B2 == nullptr || g.N % 128 != 0 || g.M <= 128 || g.rope != nullptr || g.c_f32 || g.bias != nullptr || g.R != nullptr ||
-        g.act != 0)
-        return FVLA_ERR_UNSUPPORTED;
-    auto kern = tc5x2_geglu_kernel;
+struct PairPlan { bool ok; int splits; size_t ws_bytes; float est_us; };
+
+// Plain residual GEMM on CTA pairs: 256 x 256 tiles; K is split so that the work items fill the 74 pairs.
+inline PairPlan plan_pair_plain(int M, int N, int K, bool ws_ok) {
+    PairPlan pl{false, 1, 0, 1e30f};
+    if (M <= 128 || N % 8 || K % 8) return pl;
+    const int tiles = ((M + 255) / 256) * ((N + 255) / 256), pairs = num_sms() / 2, k_iters = (K + BK - 1) / BK;
+    for (int s = 1; s <= (ws_ok ? 6 : 1); ++s) {
+        if (s > 1 && k_iters / s < 8) break;
+        const int per = (k_iters + s - 1) / s;
+        const int waves = (tiles * s + pairs - 1) / pairs;
+        float t = waves * (per * 0.28f + 5.0f);
+        if (s > 1) t += 3.0f + (float)s * M * N * 8.0f / 4.0e6f;
+        if (t < pl.est_us) { pl.est_us = t; pl.splits = s; pl.ok = true; }
+    }
+    if (pl.splits > 1) pl.ws_bytes = (((size_t)tiles * 2 * sizeof(int) + 255) / 256) * 256 + (size_t)tiles * pl.splits * 2 * 128 * 256 * sizeof(float);
+    return pl;
+}
+
+template <bool DUAL>
+inline int launch_pair(const GemmArgs& g, int splits, void* ws, int* status, cudaStream_t st) {
+    auto kern = tc5x2_gemm_kernel<DUAL>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -219,20 +333,25 @@ inline int launch_geglu_pair(const GemmArgs& g, int* status, cudaStream_t st) {
     CUtensorMap tmA, tmG, tmU;
     int rc = make_map(&tmA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, 128);
     if (rc) return rc;
-    rc = make_map(&tmG, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, 64, BK);
+    rc = make_map(&tmG, g.B, (uint64_t)g.N, (uint64_t)g.Kb, (uint64_t)g.ldb, 64, BK);
     if (rc) return rc;
-    rc = make_map(&tmU, g.B2, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, 64, BK);
+    rc = make_map(&tmU, DUAL ? g.B2 : g.B, (uint64_t)g.N, (uint64_t)g.Kb, (uint64_t)g.ldb, 64, BK);
     if (rc) return rc;
     Tc5Args a{};
     a.g = g;
     a.tiles_m = (g.M + 255) / 256;
-    a.tiles_n = g.N / 128;
+    a.tiles_n = DUAL ? g.N / 128 : (g.N + 255) / 256;
     a.k_iters = (g.K + BK - 1) / BK;
-    a.splits = 1; a.k_per_split = a.k_iters;
+    a.splits = splits; a.k_per_split = (a.k_iters + splits - 1) / splits;
+    if (splits > 1) {
+        const size_t counters = (((size_t)a.tiles_m * a.tiles_n * 2 * sizeof(int) + 255) / 256) * 256;
+        a.counters = reinterpret_cast<int*>(ws);
+        a.partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + counters);
+    }
     a.status = status;
-    const int tiles = a.tiles_m * a.tiles_n;
+    const int items = a.tiles_m * a.tiles_n * splits;
     const int max_pairs = num_sms() / 2;
-    const int pairs = tiles < max_pairs ? tiles : max_pairs;
+    const int pairs = items < max_pairs ? items : max_pairs;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     cfg.blockDim = dim3(320, 1, 1);
@@ -246,8 +365,27 @@ inline int launch_geglu_pair(const GemmArgs& g, int* status, cudaStream_t st) {
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, tmA, tmG, tmU);
-    if (e != cudaSuccess) { set_error("tc5x2_geglu_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
-    return check_launch("tc5x2_geglu_kernel");
+    if (e != cudaSuccess) { set_error("tc5x2_gemm_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
+    return check_launch("tc5x2_gemm_kernel");
+}
+
+// Gated FFN with M > 128 rows, N a multiple of 128: returns FVLA_ERR_UNSUPPORTED otherwise.
+inline int launch_geglu_pair(const GemmArgs& g, int* status, cudaStream_t st) {
+    if (g.B2 == nullptr || g.N % 128 != 0 || g.M <= 128 || g.rope != nullptr || g.c_f32 || g.bias != nullptr || g.R != nullptr ||
+        g.act != 0)
+        return FVLA_ERR_UNSUPPORTED;
+    return launch_pair<true>(g, 1, nullptr, status, st);
+}
+
+// out = A @ W (+ bf16 residual), bf16 destination, no bias / activation / RoPE: FVLA_ERR_UNSUPPORTED otherwise.
+inline int launch_plain_pair(const GemmArgs& g, void* ws, size_t ws_bytes, int* status, cudaStream_t st) {
+    if (g.B2 != nullptr || g.rope != nullptr || g.c_f32 || g.bias != nullptr || g.act != 0 || g.res_mod != 0 || g.row_scale != nullptr ||
+        (g.R != nullptr && g.ldr != g.ldc))
+        return FVLA_ERR_UNSUPPORTED;
+    PairPlan pl = plan_pair_plain(g.M, g.N, g.K, ws != nullptr);
+    if (pl.ok && pl.splits > 1 && ws_bytes < pl.ws_bytes) pl = plan_pair_plain(g.M, g.N, g.K, false);
+    if (!pl.ok) return FVLA_ERR_UNSUPPORTED;
+    return launch_pair<false>(g, pl.splits, ws, status, st);
 }
 
 }  // namespace tc5x2
