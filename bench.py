@@ -42,6 +42,10 @@ H100_PUBLISHED_MS = 15.18            # reference README.md:105-108, H100 SXM5, s
 ENC_GATE_FLOPS = 2 * 768 * 2048 * 2 * 16384          # 103.08 GFLOP per launch
 DEC_GATE_BYTES = 2 * 1024 * 4096 * 2 + 51 * 1024 * 2 + 51 * 4096 * 2   # weights + x + out, bytes per launch
 FORWARD_FLOPS = 4.006e12
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised in
+# profiles/tc5x2_gemm_encoder_gate.md and profiles/skinny_gemm_decoder_gate.md
+ENC_GATE_DRAM_BYTES = 152.5e6
+DEC_GATE_DRAM_BYTES = 17.03e6
 
 
 def measured_peaks():
@@ -329,14 +333,16 @@ def run_ours(args):
                 b["decoder_x"], w["decoder_ffn_gate_w"][i], w["decoder_ffn_up_w"][i], b["decoder_hidden"],
                 b["decoder_norm_factor_buf"]), 18, 20)
         tf = ENC_GATE_FLOPS / (t_gate * 1e-3) / 1e12
-        line["roofline"] = {"kernel": "encoder_norm_gated_ffn (RMS norm + gate/up GEMM + GeGLU, M=768 K=2048 N=2x16384)",
+        line["roofline"] = {"kernel": "encoder_norm_gated_ffn (RMS norm kernel + two-SM tcgen05 gate/up GEMM with GeGLU epilogue, M=768 K=2048 N=2x16384)",
                             "bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                            "frac": tf / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"] + " burst",
+                            "frac": tf / peaks["bf16_tflops"], "traffic": ENC_GATE_DRAM_BYTES, "traffic_unit": "bytes per launch",
+                            "peak_source": peaks["source"] + " burst",
                             "ms_per_launch": t_gate}
         gbs = DEC_GATE_BYTES / (t_dec * 1e-3) / 1e9
         line["roofline_decoder"] = {"kernel": "decoder_norm_gated_ffn (M=51 K=1024 N=2x4096, 16.8 MB of weights per launch)",
                                     "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                    "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                                    "frac": gbs / peaks["hbm_gbs"], "traffic": DEC_GATE_DRAM_BYTES, "traffic_unit": "bytes per launch",
+                                    "peak_source": peaks["source"],
                                     "ms_per_launch": t_dec,
                                     "note": "18 layers' weights cycled inside one CUDA graph"}
         if not args.no_cpu_baseline:
