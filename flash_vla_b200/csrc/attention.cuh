@@ -41,6 +41,7 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnArgs p) {
     const uint32_t sQ = smem_u32(smem);
     const uint32_t sKV = sQ + TILE;             // stage s: K at sKV + s*2*TILE, V right after
 
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the next kernel may be scheduled
     asm volatile("griddepcontrol.wait;" ::: "memory");      // no-op unless launched as a dependent
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int q0 = blockIdx.x * BQ;

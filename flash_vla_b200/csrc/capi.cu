@@ -240,12 +240,12 @@ static void* patch_scratch_device_ptr() {
 }
 
 static int norm_linear(const void* x, const void* nw, const void* nb, const void* w, const void* b,
-                       void* out, void* x_norm, int M, int N, int K, int act, void* stream) {
+                       void* out, void* x_norm, int M, int N, int K, int act, void* stream, int trigger_early) {
     int rc = rownorm(x, 0, nw, nb, x_norm, nullptr, nullptr, M, K, 0, S(stream));
     if (rc) return rc;
     GemmArgs a;
     a.A = B(x_norm); a.lda = K; a.B = B(w); a.ldb = N; a.C = out; a.ldc = N; a.bias = B(b);
-    a.act = act; a.M = M; a.N = N; a.K = K;
+    a.act = act; a.M = M; a.N = N; a.K = K; a.trigger_early = trigger_early;
     return launch_gemm(a, nullptr, 0, S(stream));
 }
 
@@ -268,17 +268,17 @@ int fvla_vision_patch_embed_noalloc(const void* images, const void* patch_w, con
 
 int fvla_vision_norm_qkv(const void* x, const void* norm_w, const void* norm_b, const void* qkv_w,
                          const void* qkv_b, void* out, void* x_norm, int M, int N, int K, void* stream) {
-    return norm_linear(x, norm_w, norm_b, qkv_w, qkv_b, out, x_norm, M, N, K, 0, stream);
+    return norm_linear(x, norm_w, norm_b, qkv_w, qkv_b, out, x_norm, M, N, K, 0, stream, 0);
 }
 
 int fvla_vision_norm_ffn_up(const void* x, const void* norm_w, const void* norm_b, const void* weight,
                             const void* bias, void* out, void* x_norm, int M, int N, int K, void* stream) {
-    return norm_linear(x, norm_w, norm_b, weight, bias, out, x_norm, M, N, K, 1, stream);
+    return norm_linear(x, norm_w, norm_b, weight, bias, out, x_norm, M, N, K, 1, stream, 1);      // the down GEMM follows
 }
 
 int fvla_encoder_projector(const void* x, const void* norm_w, const void* norm_b, const void* proj_w,
                            const void* proj_b, void* out, void* x_norm, int M, int N, int K, void* stream) {
-    return norm_linear(x, norm_w, norm_b, proj_w, proj_b, out, x_norm, M, N, K, 0, stream);
+    return norm_linear(x, norm_w, norm_b, proj_w, proj_b, out, x_norm, M, N, K, 0, stream, 0);
 }
 
 int fvla_vision_attention(const void* qkv, void* out, int views, int tokens, int heads, int head_dim,
@@ -298,11 +298,13 @@ int fvla_vision_attention(const void* qkv, void* out, int views, int tokens, int
 }
 
 int fvla_vision_linear_bias_residual(const void* x, const void* weight, const void* bias, const void* res,
-                                     void* out, int M, int N, int K, void* stream) {
+                                     void* out, int M, int N, int K, void* ws, size_t ws_bytes, void* stream) {
     GemmArgs a;
     a.A = B(x); a.lda = K; a.B = B(weight); a.ldb = N; a.C = out; a.ldc = N; a.bias = B(bias);
     a.R = res; a.ldr = N; a.M = M; a.N = N; a.K = K;
-    return launch_gemm(a, nullptr, 0, S(stream));
+    void* gws; size_t gn;
+    gemm_ws(ws, ws_bytes, M, K, &gws, &gn);
+    return launch_gemm(a, gws, gn, S(stream));
 }
 
 int fvla_encoder_norm_qkv_rope(const void* x, const void* weight_qkv, const void* rope, void* Q, void* K,
@@ -315,6 +317,7 @@ int fvla_encoder_norm_qkv_rope(const void* x, const void* weight_qkv, const void
     a.M = M; a.N = (heads + 2) * head_dim; a.K = Kdim;
     a.rope = B(rope); a.q = Bm(Q); a.k = Bm(K); a.v = Bm(V); a.heads = heads; a.head_dim = head_dim;
     a.round_first = 1;
+    a.trigger_early = 1;      // the next kernel (prefix attention / down projection) runs one CTA per SM
     return launch_gemm(a, nullptr, 0, S(stream));
 }
 
@@ -356,6 +359,7 @@ int fvla_encoder_norm_gated_ffn(const void* x, const void* gate_w, const void* u
     GemmArgs a;
     a.A = B(x_norm); a.lda = K; a.B = B(gate_w); a.B2 = B(up_w); a.ldb = N; a.C = out; a.ldc = N;
     a.M = M; a.N = N; a.K = K;
+    a.trigger_early = 1;      // the next kernel (prefix attention / down projection) runs one CTA per SM
     return launch_gemm(a, nullptr, 0, S(stream));
 }
 

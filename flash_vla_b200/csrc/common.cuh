@@ -16,11 +16,14 @@ constexpr float kGeluC0 = 1.5957691216057308f;   // 2 * sqrt(2 / pi)
 constexpr float kGeluC1 = 0.044715f;
 constexpr float kLog2e = 1.4426950408889634f;
 
-// tanh-GELU written as v * sigmoid(C0 * v * (1 + C1 v^2)); same form as the reference
-// kernels (kernels/base.py:77-78), which is algebraically the tanh approximation.
+// tanh-GELU. The reference kernels write it as v * sigmoid(C0 * v * (1 + C1 v^2))
+// (kernels/base.py:77-78); sigmoid(t) = (1 + tanh(t / 2)) / 2, and tanh.approx is one special-function
+// instruction where exp + reciprocal are two (its 2^-11 relative error is below bf16 rounding).
 __device__ __forceinline__ float gelu_f(float v) {
-    float t = kGeluC0 * v * (1.0f + kGeluC1 * v * v);
-    return __fdividef(v, 1.0f + __expf(-t));
+    float t = (0.5f * kGeluC0) * v * (1.0f + kGeluC1 * v * v), th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(t));
+    const float h = 0.5f * v;
+    return fmaf(h, th, h);
 }
 __device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 

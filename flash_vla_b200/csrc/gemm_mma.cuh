@@ -28,6 +28,11 @@ struct GemmArgs {
     int heads = 0, head_dim = 0, round_first = 0;
     // split-K
     int splits = 1, k_per_split = 0; float* partial = nullptr; int* counters = nullptr;
+    // Programmatic dependent launch: 1 = let the next kernel be scheduled once this CTA's last
+    // accumulator is complete (its set-up then overlaps the last epilogue); 0 = only at exit. Set 1
+    // only when the next kernel runs one CTA per SM: a kernel with several small CTAs per SM (row
+    // norm, SigLIP attention) would be packed onto the few SMs that are idle at that moment.
+    int trigger_early = 0;
 };
 
 // Residual values of one (row, col..col+1) pair. Loaded for every fragment BEFORE any store of

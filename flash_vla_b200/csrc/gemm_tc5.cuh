@@ -255,9 +255,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
-    // Set-up above touched only this CTA's own shared memory and TMEM; from here on the operands
-    // written by the previous kernel in the stream are read.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Set-up above touched only this CTA's own shared memory and TMEM.
     if (threadIdx.x == 0) stamp(1);
 
     if (warp == 0) {
@@ -265,6 +263,27 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
             prefetch_tensormap(&tmA);
             prefetch_tensormap(&tmB);
             if (DUAL) prefetch_tensormap(&tmB2);
+            auto load_b = [&](int s, int n0, int kt) {
+                const uint32_t sB = smem_base + s * Cfg::STAGE_BYTES + Cfg::A_BYTES;
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int j = 0; j < BN / 64; ++j)
+                        tma_load_2d(sB + nb * Cfg::B_BYTES + j * Cfg::SLAB, nb == 0 ? &tmB : &tmB2, full_bar(s), n0 + j * 64, kt * BK);
+            };
+            // Weights are never written inside a forward pass, so the B halves of the first stages are
+            // requested before waiting for the previous kernel; the A halves (its output) follow the wait.
+            uint32_t early = 0;
+            if ((int)blockIdx.x < num_tiles) {
+                const int t_idx = blockIdx.x / args.splits, split = blockIdx.x % args.splits;
+                const int n0 = (t_idx / args.tiles_m) * BN;
+                const int kt_beg = split * args.k_per_split, kt_end = min(args.k_iters, kt_beg + args.k_per_split);
+                for (int kt = kt_beg; kt < kt_end && early < (uint32_t)STAGES; ++kt, ++early) {
+                    mbar_expect_tx(full_bar(early), Cfg::STAGE_BYTES);
+                    load_b(early, n0, kt);
+                }
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
                 const int t_idx = tile / args.splits, split = tile % args.splits;
@@ -273,21 +292,21 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                 for (int kt = kt_beg; kt < kt_end; ++kt, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
-                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) goto producer_done;
-                    mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
-                    const uint32_t sA = smem_base + s * Cfg::STAGE_BYTES;
-                    tma_load_2d(sA, &tmA, full_bar(s), kt * BK, m0);
-#pragma unroll
-                    for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                        for (int j = 0; j < BN / 64; ++j)
-                            tma_load_2d(sA + Cfg::A_BYTES + nb * Cfg::B_BYTES + j * Cfg::SLAB, nb == 0 ? &tmB : &tmB2,
-                                        full_bar(s), n0 + j * 64, kt * BK);
+                    const bool fresh = it >= early;               // stages below `early` already hold their B request
+                    if (fresh) {
+                        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) goto producer_done;
+                        mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
+                    }
+                    tma_load_2d(smem_base + s * Cfg::STAGE_BYTES, &tmA, full_bar(s), kt * BK, m0);
+                    if (fresh) load_b(s, n0, kt);
                 }
             }
         }
     producer_done:;
+        __syncwarp();
+        if (p.trigger_early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // every thread of the CTA signals at the end of its role
     } else if (warp == 1) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc(BN);
             uint32_t it = 0, tcount = 0;
@@ -322,11 +341,14 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
             }
         }
     mma_done:;
+        __syncwarp();
+        if (p.trigger_early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     } else {
         // Eight epilogue warps: warp w reads TMEM lanes [32 (w % 4), +32) and owns one half of the
         // tile's columns. One thread = one output row; results go through a small per-warp staging
         // area so that global loads and stores touch 64 contiguous bytes per row (8 rows per request)
         // instead of 16 bytes in each of 32 rows.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         const int ew = warp - 2, quad = warp & 3, chalf = ew >> 2;
         constexpr int HALF = BN / 2, CHUNKS = HALF / 32;
         uint8_t* stg = smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES + ew * Cfg::EPI_STAGE_BYTES;
@@ -357,6 +379,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                 }
             }
             if (!mbar_wait(accfull_bar(acc), acc_ph, abort_flag)) break;
+            if (tile + (int)gridDim.x >= num_tiles) { if (p.trigger_early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }      // last accumulator complete
             tc_fence_after();
             if (tcount == 0 && threadIdx.x == 64) stamp(4);
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * Cfg::ACC_COLS + chalf * HALF;
@@ -430,15 +453,19 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                         }
                         __syncwarp();
                     }
+                    // the activation is chosen once per chunk, outside the element loop: inside it the compiler
+                    // evaluates every branch for every element and selects
+                    auto finish = [&](auto act) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float v = DUAL ? gelu_f(a[j]) * u[j] : a[j];
-                        v += __shfl_sync(0xffffffffu, bias_lane[c], j);
-                        if (p.act == 1) v = gelu_f(v);
-                        else if (p.act == 2) v = silu_f(v);
-                        if (p.R) v += res[j];
-                        a[j] = v;
-                    }
+                        for (int j = 0; j < 32; ++j) {
+                            float v = (DUAL ? gelu_f(a[j]) * u[j] : a[j]) + __shfl_sync(0xffffffffu, bias_lane[c], j);
+                            v = act(v);
+                            a[j] = p.R ? v + res[j] : v;
+                        }
+                    };
+                    if (p.act == 1) finish([](float v) { return gelu_f(v); });
+                    else if (p.act == 2) finish([](float v) { return silu_f(v); });
+                    else finish([](float v) { return v; });
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
                         *reinterpret_cast<uint4*>(stg + lane * 80 + j * 16) =

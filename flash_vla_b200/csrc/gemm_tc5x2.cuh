@@ -101,35 +101,59 @@ tc5x2_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, c
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
-    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0) {
             prefetch_tensormap(&tmA);
             const CUtensorMap* tmB = (DUAL && rank == 1) ? &tmU : &tmG;
             prefetch_tensormap(tmB);
+            // the B columns this CTA stages: gated form, both CTAs the same 128 (gate / up matrix); plain form, its half of 256
+            auto b_col = [&](int t_idx) { return (t_idx / args.tiles_m) * TILE_N + (DUAL ? 0 : (int)rank * 128); };
+            // Weights are never written inside a forward pass: the B halves of the first stages are requested
+            // before waiting for the previous kernel, the A halves (its output) after.
+            uint32_t early = 0;
+            if (pair < num_tiles) {
+                const int t_idx = pair / args.splits, split = pair % args.splits;
+                const int n0 = b_col(t_idx);
+                const int kt_beg = split * args.k_per_split, kt_end = min(args.k_iters, kt_beg + args.k_per_split);
+                for (int kt = kt_beg; kt < kt_end && early < (uint32_t)STAGES; ++kt, ++early) {
+                    if (rank == 0) mbar_expect_tx(full_bar(early), 2 * STAGE_BYTES);
+                    const uint32_t sB = smem_base + early * STAGE_BYTES + 16384;
+                    const uint32_t leader_full = full_bar(early) & kPeerBitMask;
+                    tma_load_2d_pair(sB, tmB, leader_full, n0, kt * BK);
+                    tma_load_2d_pair(sB + 8192, tmB, leader_full, n0 + 64, kt * BK);
+                }
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             uint32_t it = 0;
             for (int tile = pair; tile < num_tiles; tile += pairs) {
                 const int t_idx = tile / args.splits, split = tile % args.splits;
                 const int m0 = (t_idx % args.tiles_m) * 256 + (int)rank * 128;
-                // the B columns this CTA stages: gated form, both CTAs the same 128 (gate / up matrix); plain form, its half of 256
-                const int n0 = (t_idx / args.tiles_m) * TILE_N + (DUAL ? 0 : (int)rank * 128);
+                const int n0 = b_col(t_idx);
                 const int kt_beg = split * args.k_per_split, kt_end = min(args.k_iters, kt_beg + args.k_per_split);
                 for (int kt = kt_beg; kt < kt_end; ++kt, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
-                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) goto producer_done;
-                    if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);      // the bytes of both CTAs
+                    const bool fresh = it >= early;               // stages below `early` already hold their B request
+                    if (fresh) {
+                        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) goto producer_done;
+                        if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);      // the bytes of both CTAs
+                    }
                     const uint32_t sA = smem_base + s * STAGE_BYTES;
                     const uint32_t leader_full = full_bar(s) & kPeerBitMask;
                     tma_load_2d_pair(sA, &tmA, leader_full, kt * BK, m0);
-                    tma_load_2d_pair(sA + 16384, tmB, leader_full, n0, kt * BK);
-                    tma_load_2d_pair(sA + 16384 + 8192, tmB, leader_full, n0 + 64, kt * BK);
+                    if (fresh) {
+                        tma_load_2d_pair(sA + 16384, tmB, leader_full, n0, kt * BK);
+                        tma_load_2d_pair(sA + 16384 + 8192, tmB, leader_full, n0 + 64, kt * BK);
+                    }
                 }
             }
         }
     producer_done:;
+        __syncwarp();
+        if (p.trigger_early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // every thread of the CTA signals at the end of its role
     } else if (warp == 1) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         if (lane == 0 && rank == 0) {
             constexpr uint32_t idesc = pair_idesc();
             uint32_t it = 0, tcount = 0;
@@ -159,9 +183,12 @@ tc5x2_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, c
             }
         }
     mma_done:;
+        __syncwarp();
+        if (p.trigger_early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     } else {
         // 8 epilogue warps per CTA: warp w reads TMEM lanes [32 (w % 4), +32) and owns half of the tile's
         // output columns (64 in the gated form, 128 in the plain form), 32 at a time.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         const int ew = warp - 2, quad = warp & 3, chalf = ew >> 2;
         constexpr int SPAN = TILE_N / 2, CHUNKS = SPAN / 32;
         uint8_t* stg = smem_gen + STAGES * STAGE_BYTES + BAR_BYTES + ew * EPI_STAGE_BYTES;
@@ -195,6 +222,7 @@ tc5x2_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, c
                     }
             }
             if (!mbar_wait(accfull_bar(acc), acc_ph, abort_flag)) break;
+            if (tile + (int)pairs >= num_tiles) { if (p.trigger_early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }      // last accumulator complete
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * 256 + chalf * SPAN;
             bool from_partials = false;

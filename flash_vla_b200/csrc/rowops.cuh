@@ -34,6 +34,7 @@ __global__ void __launch_bounds__(128) rownorm_kernel(const XT* __restrict__ x, 
                                                       const bf16* __restrict__ b, bf16* __restrict__ out,
                                                       float* __restrict__ factor_f32,
                                                       bf16* __restrict__ factor_bf16, int M, int K, int mode) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the next kernel may be scheduled
     asm volatile("griddepcontrol.wait;" ::: "memory");      // no-op unless launched as a dependent
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= M) return;

@@ -19,7 +19,7 @@ SIGNATURES: dict[str, list] = {
     "fvla_vision_patch_embed_noalloc": [_P, _P, _P, _P, _P, _I, _P],
     "fvla_vision_norm_qkv": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fvla_vision_attention": [_P, _P, _I, _I, _I, _I, _P],
-    "fvla_vision_linear_bias_residual": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "fvla_vision_linear_bias_residual": [_P, _P, _P, _P, _P, _I, _I, _I, _P, _Z, _P],
     "fvla_vision_norm_ffn_up": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fvla_encoder_projector": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fvla_encoder_norm_qkv_rope": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],

@@ -164,19 +164,20 @@ def vision_attention(QKV, out):
     return out
 
 
-def _linear_bias_residual(x, weight, bias, res, out):
+def _linear_bias_residual(role, x, weight, bias, res, out):
     K, N = weight.shape
     M = x.numel() // K
     if res.numel() != M * N or out.numel() != M * N:
         raise ValueError("linear_bias_residual: res/out have the wrong size")
+    ws, nb = _ws(role, _lib.load().fvla_gemm_workspace_bytes(M, N, K, 0), x.device)
     _lib.call("fvla_vision_linear_bias_residual", _chk("x", x), _chk("weight", weight),
-              _chk("bias", bias, (N,)), _chk("res", res), _chk("out", out), M, N, K, _stream())
+              _chk("bias", bias, (N,)), _chk("res", res), _chk("out", out), M, N, K, ws, nb, _stream())
     return out
 
 
 def vision_out_proj_residual(x, weight, bias, res, out):
     """out = x @ weight + bias + res; res and out may be one buffer (wrappers.py:279-288)."""
-    return _linear_bias_residual(x, weight, bias, res, out)
+    return _linear_bias_residual("vis_o_ws", x, weight, bias, res, out)
 
 
 def vision_norm_ffn_up(x, norm_w, norm_b, weight, bias, out, x_norm):
@@ -188,7 +189,7 @@ def vision_norm_ffn_up(x, norm_w, norm_b, weight, bias, out, x_norm):
 
 def vision_ffn_down_residual(x, weight, bias, res, out):
     """out = hidden @ weight + bias + res (wrappers.py:301-306)."""
-    return _linear_bias_residual(x, weight, bias, res, out)
+    return _linear_bias_residual("vis_down_ws", x, weight, bias, res, out)
 
 
 # -------------------------------------------------------------------------- encoder

@@ -76,9 +76,12 @@ int fvla_vision_norm_qkv(const void* x, const void* norm_w, const void* norm_b, 
 /* kernels/attention.py:20-26: packed (views,256,3,heads,head_dim) -> (views,256,heads*head_dim). */
 int fvla_vision_attention(const void* qkv, void* out, int views, int tokens, int heads,
                           int head_dim, void* stream);
-/* wrappers.py:279-288 and :301-306: out = x(M,K) @ W(K,N) + b + res; res may alias out. */
+/* wrappers.py:279-288 and :301-306: out = x(M,K) @ W(K,N) + b + res; res may alias out.
+ * `ws` (fvla_gemm_workspace_bytes(M, N, K, 0), zero-initialised once) lets the kernel split K when the
+ * output has too few tiles to fill the GPU; NULL is allowed and disables the split. */
 int fvla_vision_linear_bias_residual(const void* x, const void* weight, const void* bias,
-                                     const void* res, void* out, int M, int N, int K, void* stream);
+                                     const void* res, void* out, int M, int N, int K, void* ws,
+                                     size_t ws_bytes, void* stream);
 /* wrappers.py:291-298: x_norm = LayerNorm(x); out = gelu_tanh(x_norm @ W + b). */
 int fvla_vision_norm_ffn_up(const void* x, const void* norm_w, const void* norm_b,
                             const void* weight, const void* bias, void* out, void* x_norm, int M,
