@@ -260,12 +260,14 @@ inline int launch_attention(const AttnArgs& a, dim3 grid, cudaStream_t st) {
 // ---------------------------------------------------------------------------------------------
 // Decoder attention in one launch: keys split over the 8 CTAs of a thread-block cluster, partial
 // results merged through distributed shared memory (no partial buffers in global memory, no
-// second kernel). Grid = (ceil(queries / 32), 8), cluster (1, 8). In each CTA warp w handles
-// query rows 16 * (w & 1) .. + 16 of the 32-row block against key block (w >> 1) of the CTA's
-// <= 128 keys, so every warp does exactly one 16 x 64 score tile and one P V product. The two key
-// halves are merged in shared memory, the normalised 32 x 256 partial and its log-sum-exp are
-// staged, and rank r receives rows 4r .. 4r+3 from all 8 ranks by bulk copy, combines them with
-// log-sum-exp weights in rank order and writes bf16.
+// second kernel). Grid = (ceil(queries / 32), 8), cluster (1, 8), 8 warps per CTA. Warp w works on
+// query rows 16 (w & 1) .. + 16 of the 32-row block, key block (w >> 1) & 1 of the CTA's <= 128 keys
+// and half (w >> 2) of the head dimension: it sums Q K^T over its 128 of the 256 dimensions, swaps
+// that partial 16 x 64 score tile with the warp holding the other half (both then own the full
+// scores and run the same softmax) and multiplies P with its 128 columns of V. The two key blocks are
+// merged in shared memory, the normalised 32 x 256 partial and its log-sum-exp are staged, and rank
+// r receives rows 4r .. 4r+3 from all 8 ranks by bulk copy, combines them with log-sum-exp weights
+// in rank order and writes bf16.
 // ---------------------------------------------------------------------------------------------
 struct DecAttnArgs {
     const bf16* q; const bf16* k; const bf16* v; bf16* out;
@@ -274,18 +276,23 @@ struct DecAttnArgs {
     int mask_rows, mask_key_le;
     int prefix_keys;            // keys [0, prefix_keys) were not written by the preceding kernel
     int* status;
+    unsigned long long* dbg;    // optional development aid: 8 globaltimer stamps per CTA
 };
 
 namespace decattn {
-constexpr int HD = 256, BQ = 32, SPL = 8, PITCH = HD * 2 + 16, CH = HD / 8;
+constexpr int HD = 256, BQ = 32, SPL = 8, PITCH = HD * 2 + 16, CH = HD / 8, THREADS = 256;
+constexpr int OP = HD + 8;                          // fp32 row pitch of the merge / staging buffers: rows 8 banks apart
+constexpr int SLICE = 4 * OP * 4;                   // bytes of the 4 staged rows one owner receives from one rank
 constexpr int Q_BYTES = BQ * PITCH, KV_BYTES = 128 * PITCH;
-constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + KV_BYTES, OFF_RED = OFF_V + KV_BYTES;   // RED: [src 8][4 rows][256] fp32
-constexpr int OFF_LSE_IN = OFF_RED + SPL * 4 * HD * 4;                                   // [src 8][4] fp32
-constexpr int OFF_BAR = OFF_LSE_IN + SPL * 4 * 4;
+constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + KV_BYTES, OFF_RED = OFF_V + KV_BYTES;   // RED: [src 8][4 rows][OP] fp32
+constexpr int OFF_LSE_IN = OFF_RED + SPL * SLICE;                                        // [src 8][4] fp32
+constexpr int OFF_SX = OFF_LSE_IN + SPL * 4 * 4;                                         // score swap: [warp 8][32][lane 32] fp32
+constexpr int OFF_BAR = OFF_SX + 8 * 32 * 32 * 4;
 constexpr int SMEM = OFF_BAR + 64;
 // staging areas alias K (half-merge buffer) and V (final partial) once the MMAs are done
-constexpr int OFF_HALF = OFF_K;                    // [32 rows][256] fp32 + m[32] + l[32]
-constexpr int OFF_STAGE = OFF_V;                   // [32 rows][256] fp32 + lse[32]
+constexpr int OFF_HALF = OFF_K;                    // [32 rows][OP] fp32 + m[32] + l[32]
+constexpr int OFF_STAGE = OFF_V;                   // [32 rows][OP] fp32 + lse[32]
+static_assert(BQ * OP * 4 + 256 <= KV_BYTES, "merge buffers must fit in the K / V tiles they alias");
 }  // namespace decattn
 
 __device__ __forceinline__ uint32_t dsm_map(uint32_t local_addr, uint32_t rank) {
@@ -294,7 +301,7 @@ __device__ __forceinline__ uint32_t dsm_map(uint32_t local_addr, uint32_t rank) 
     return r;
 }
 
-__global__ void __launch_bounds__(128, 1) decoder_attention_cluster_kernel(const DecAttnArgs p) {
+__global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster_kernel(const DecAttnArgs p) {
     using namespace decattn;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
@@ -303,6 +310,9 @@ __global__ void __launch_bounds__(128, 1) decoder_attention_cluster_kernel(const
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_BAR + 16);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    unsigned long long* dbg = p.dbg ? p.dbg + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8 : nullptr;
+    auto stamp = [&](int i) { if (dbg && tid == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); dbg[i] = t; } };
+    stamp(0);
     uint32_t rank;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
     const int q0 = blockIdx.x * BQ;
@@ -317,31 +327,26 @@ __global__ void __launch_bounds__(128, 1) decoder_attention_cluster_kernel(const
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         if (i_own)
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(in_bar), "r"(SPL * (4 * HD * 4 + 16)) : "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(in_bar), "r"(SPL * (SLICE + 16)) : "memory");
     }
     // relaxed: the fence above already published the barrier to the cluster
     asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
     auto load_rows = [&](uint32_t dst, const bf16* src, int row0, int row_lo, int row_hi, int nrows) {
         // rows [row0, row0 + nrows) of `src` into dst; only rows in [row_lo, row_hi) are fetched now
-        for (int idx = tid; idx < nrows * CH; idx += 128) {
+        for (int idx = tid; idx < nrows * CH; idx += THREADS) {
             int r = idx / CH, c = idx % CH;
             int g = row0 + r;
             if (g >= row_lo && g < row_hi) cp_async16(dst + r * PITCH + c * 16, src + (size_t)g * HD + c * 8, 16);
         }
     };
-    // Prefix keys were written long before the preceding kernel: fetch them while it finishes.
+    // Prefix keys were written long before the preceding kernel: fetch them while it finishes. Rows
+    // past the end (keys of the ragged last split, queries of the last block) must read as zero.
     const int pre_end = min(key_end, p.prefix_keys);
     load_rows(sK, p.k, key_beg, key_beg, pre_end, 128);
     load_rows(sV, p.v, key_beg, key_beg, pre_end, 128);
     cp_async_commit();
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    load_rows(sK, p.k, key_beg, max(key_beg, pre_end), key_end, 128);
-    load_rows(sV, p.v, key_beg, max(key_beg, pre_end), key_end, 128);
-    load_rows(sQ, p.q, q0, q0, p.nq, BQ);
-    // rows past the end (keys of the ragged last split, queries of the last block) must read as zero
-    for (int idx = tid; idx < 128 * CH; idx += 128) {
+    for (int idx = tid; idx < 128 * CH; idx += THREADS) {
         int r = idx / CH, c = idx % CH;
         if (key_beg + r >= key_end) {
             *reinterpret_cast<uint4*>(smem + OFF_K + r * PITCH + c * 16) = make_uint4(0, 0, 0, 0);
@@ -349,21 +354,29 @@ __global__ void __launch_bounds__(128, 1) decoder_attention_cluster_kernel(const
         }
         if (r < BQ && q0 + r >= p.nq) *reinterpret_cast<uint4*>(smem + r * PITCH + c * 16) = make_uint4(0, 0, 0, 0);
     }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    stamp(1);
+    load_rows(sQ, p.q, q0, q0, p.nq, BQ);
+    load_rows(sK, p.k, key_beg, max(key_beg, pre_end), key_end, 128);
+    load_rows(sV, p.v, key_beg, max(key_beg, pre_end), key_end, 128);
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
+    stamp(2);
 
-    const int rg = warp & 1, half = warp >> 1;
+    const int rg = warp & 1, kh = (warp >> 1) & 1, dh = warp >> 2;
     const int row_lo = q0 + rg * 16 + (lane >> 2);
-    float o[HD / 8][4];
+    float o[HD / 16][4];                               // this warp's 128 output columns
     float m_run[2], l_run[2];
     {
-        const uint32_t sKb = sK + half * 64 * PITCH, sVb = sV + half * 64 * PITCH;
+        const uint32_t sKb = sK + kh * 64 * PITCH, sVb = sV + kh * 64 * PITCH;
         float s[8][4];
 #pragma unroll
         for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
+        for (int k8 = 0; k8 < HD / 32; ++k8) {
+            const int kk = dh * (HD / 32) + k8;
             uint32_t a[4];
             ldmatrix_x4(a, sQ + (rg * 16 + (lane & 15)) * PITCH + (kk * 2 + (lane >> 4)) * 16);
 #pragma unroll
@@ -375,7 +388,23 @@ __global__ void __launch_bounds__(128, 1) decoder_attention_cluster_kernel(const
                 mma_bf16_16816(s[2 * nj + 1], a, b[2], b[3]);
             }
         }
-        const int kbase = key_beg + half * 64;
+        // Swap partial scores with the warp that summed the other half of the head dimension (same rows,
+        // same keys, hence the same fragment layout: element j of lane l pairs with element j of lane l).
+        {
+            float* sx = reinterpret_cast<float*>(smem + OFF_SX);
+            float* mine = sx + warp * 1024;
+            const float* theirs = sx + (warp ^ 4) * 1024;
+#pragma unroll
+            for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mine[(ni * 4 + e) * 32 + lane] = s[ni][e];
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");
+#pragma unroll
+            for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[ni][e] += theirs[(ni * 4 + e) * 32 + lane];
+        }
+        const int kbase = key_beg + kh * 64;
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int ni = 0; ni < 8; ++ni)
@@ -411,7 +440,7 @@ __global__ void __launch_bounds__(128, 1) decoder_attention_cluster_kernel(const
             l_run[h] = psum[h];
         }
 #pragma unroll
-        for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+        for (int i = 0; i < HD / 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
             uint32_t a[4];
@@ -420,30 +449,32 @@ __global__ void __launch_bounds__(128, 1) decoder_attention_cluster_kernel(const
             a[2] = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
             a[3] = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-            for (int dj = 0; dj < HD / 16; ++dj) {
+            for (int dl = 0; dl < HD / 32; ++dl) {
+                const int dj = dh * (HD / 32) + dl;
                 uint32_t b[4];
                 int key = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
                 ldmatrix_x4_trans(b, sVb + key * PITCH + (dj * 2 + (lane >> 4)) * 16);
-                mma_bf16_16816(o[2 * dj], a, b[0], b[1]);
-                mma_bf16_16816(o[2 * dj + 1], a, b[2], b[3]);
+                mma_bf16_16816(o[2 * dl], a, b[0], b[1]);
+                mma_bf16_16816(o[2 * dl + 1], a, b[2], b[3]);
             }
         }
     }
     __syncthreads();                                   // K and V are dead from here on
+    stamp(3);
 
-    float* half_o = reinterpret_cast<float*>(smem + OFF_HALF);            // [32][256]
-    float* half_ml = half_o + BQ * HD;                                      // m[32], l[32]
-    float* stage_o = reinterpret_cast<float*>(smem + OFF_STAGE);          // [32][256]
-    float* stage_lse = stage_o + BQ * HD;                                   // [32]
+    float* half_o = reinterpret_cast<float*>(smem + OFF_HALF);            // [32][OP]
+    float* half_ml = half_o + BQ * OP;                                      // m[32], l[32]
+    float* stage_o = reinterpret_cast<float*>(smem + OFF_STAGE);          // [32][OP]
+    float* stage_lse = stage_o + BQ * OP;                                   // [32]
     const int r_in_blk = rg * 16 + (lane >> 2);
-    if (half == 1) {
+    const int c_base = dh * (HD / 2) + (lane & 3) * 2;                      // column of o[i][0]: c_base + 8 i
+    if (kh == 1) {
 #pragma unroll
-        for (int i = 0; i < HD / 8; ++i)
+        for (int i = 0; i < HD / 16; ++i)
 #pragma unroll
             for (int h = 0; h < 2; ++h)
-                *reinterpret_cast<float2*>(half_o + (r_in_blk + h * 8) * HD + i * 8 + (lane & 3) * 2) =
-                    make_float2(o[i][2 * h], o[i][2 * h + 1]);
-        if ((lane & 3) == 0) {
+                *reinterpret_cast<float2*>(half_o + (r_in_blk + h * 8) * OP + c_base + i * 8) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+        if (dh == 0 && (lane & 3) == 0) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 half_ml[r_in_blk + h * 8] = m_run[h];
@@ -452,7 +483,7 @@ __global__ void __launch_bounds__(128, 1) decoder_attention_cluster_kernel(const
         }
     }
     __syncthreads();
-    if (half == 0) {
+    if (kh == 0) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int r = r_in_blk + h * 8;
@@ -463,27 +494,28 @@ __global__ void __launch_bounds__(128, 1) decoder_attention_cluster_kernel(const
             const float l = l_run[h] * a0 + l1 * a1;
             const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
-            for (int i = 0; i < HD / 8; ++i) {
-                const int c = i * 8 + (lane & 3) * 2;
-                const float2 o1 = *reinterpret_cast<const float2*>(half_o + r * HD + c);
-                *reinterpret_cast<float2*>(stage_o + r * HD + c) =
+            for (int i = 0; i < HD / 16; ++i) {
+                const int c = c_base + i * 8;
+                const float2 o1 = *reinterpret_cast<const float2*>(half_o + r * OP + c);
+                *reinterpret_cast<float2*>(stage_o + r * OP + c) =
                     make_float2((o[i][2 * h] * a0 + o1.x * a1) * inv, (o[i][2 * h + 1] * a0 + o1.y * a1) * inv);
             }
-            if ((lane & 3) == 0) stage_lse[r] = l > 0.f ? mn + log2f(l) : -INFINITY;
+            if (dh == 0 && (lane & 3) == 0) stage_lse[r] = l > 0.f ? mn + log2f(l) : -INFINITY;
         }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
+    stamp(4);
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");     // peers' barriers are initialised
     if (tid == 0) {
         for (int r = 0; r < owners; ++r) {
             const uint32_t bar_r = dsm_map(in_bar, (uint32_t)r);
             asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                         ::"r"(dsm_map(sbase + OFF_RED + rank * (4 * HD * 4), (uint32_t)r)),
-                           "r"(sbase + OFF_STAGE + r * (4 * HD * 4)), "r"(4 * HD * 4), "r"(bar_r) : "memory");
+                         ::"r"(dsm_map(sbase + OFF_RED + rank * SLICE, (uint32_t)r)),
+                           "r"(sbase + OFF_STAGE + r * SLICE), "r"(SLICE), "r"(bar_r) : "memory");
             asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                          ::"r"(dsm_map(sbase + OFF_LSE_IN + rank * 16, (uint32_t)r)),
-                           "r"(sbase + OFF_STAGE + BQ * HD * 4 + r * 16), "r"(16), "r"(bar_r) : "memory");
+                           "r"(sbase + OFF_STAGE + BQ * OP * 4 + r * 16), "r"(16), "r"(bar_r) : "memory");
         }
     }
     if (i_own) {
@@ -495,35 +527,35 @@ __global__ void __launch_bounds__(128, 1) decoder_attention_cluster_kernel(const
             if (done) { ok = true; break; }
         }
         if (!ok) *abort_flag = 1;
+        stamp(5);
         const float* red = reinterpret_cast<const float*>(smem + OFF_RED);
         const float* lse_in = reinterpret_cast<const float*>(smem + OFF_LSE_IN);
-        const int r4 = tid >> 5, c8 = (tid & 31) * 8;
+        const int r4 = tid >> 6, c4 = (tid & 63) * 4;
         const int row = q0 + (int)rank * 4 + r4;
         if (ok && row < p.nq) {
             float mx = -INFINITY;
 #pragma unroll
             for (int s = 0; s < SPL; ++s) mx = fmaxf(mx, lse_in[s * 4 + r4]);
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
             float wsum = 0.f;
 #pragma unroll
             for (int s = 0; s < SPL; ++s) {
                 const float l = lse_in[s * 4 + r4];
                 const float w = l == -INFINITY ? 0.f : exp2f(l - mx);
                 wsum += w;
-                const float4 v0 = *reinterpret_cast<const float4*>(red + (s * 4 + r4) * HD + c8);
-                const float4 v1 = *reinterpret_cast<const float4*>(red + (s * 4 + r4) * HD + c8 + 4);
+                const float4 v0 = *reinterpret_cast<const float4*>(red + (s * 4 + r4) * OP + c4);
                 acc[0] += w * v0.x; acc[1] += w * v0.y; acc[2] += w * v0.z; acc[3] += w * v0.w;
-                acc[4] += w * v1.x; acc[5] += w * v1.y; acc[6] += w * v1.z; acc[7] += w * v1.w;
             }
             const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
-            *reinterpret_cast<uint4*>(p.out + (size_t)row * HD + c8) =
-                make_uint4(pack_bf16x2(acc[0] * inv, acc[1] * inv), pack_bf16x2(acc[2] * inv, acc[3] * inv),
-                           pack_bf16x2(acc[4] * inv, acc[5] * inv), pack_bf16x2(acc[6] * inv, acc[7] * inv));
+            *reinterpret_cast<uint2*>(p.out + (size_t)row * HD + c4) =
+                make_uint2(pack_bf16x2(acc[0] * inv, acc[1] * inv), pack_bf16x2(acc[2] * inv, acc[3] * inv));
         }
     }
     // outgoing copies read this CTA's staging area: stay until every owner has everything
     // (execution barrier only; nothing read after it was written by a peer)
+    stamp(6);
     asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+    stamp(7);
     if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 3);
 }
 
@@ -537,7 +569,7 @@ inline int launch_decoder_attention_cluster(const DecAttnArgs& a, bool pdl, cuda
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((a.nq + decattn::BQ - 1) / decattn::BQ, decattn::SPL, 1);
-    cfg.blockDim = dim3(128, 1, 1);
+    cfg.blockDim = dim3(decattn::THREADS, 1, 1);
     cfg.dynamicSmemBytes = decattn::SMEM;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];

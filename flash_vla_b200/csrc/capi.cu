@@ -117,7 +117,14 @@ static bool tc5_enabled() {
 // globaltimer stamps there (development aid; unset in normal use).
 static unsigned long long* debug_timestamps() {
     const char* v = getenv("FVLA_DEBUG_TIMESTAMPS");
-    return v ? reinterpret_cast<unsigned long long*>(strtoull(v, nullptr, 10)) : nullptr;
+    if (!v) return nullptr;
+    // FVLA_DEBUG_TIMESTAMPS_SLOTS=n gives successive launches their own 2048-entry slot (n slots, cyclic)
+    static int slots = -1, next = 0;
+    if (slots < 0) { const char* s = getenv("FVLA_DEBUG_TIMESTAMPS_SLOTS"); slots = s ? atoi(s) : 1; if (slots < 1) slots = 1; }
+    unsigned long long* base = reinterpret_cast<unsigned long long*>(strtoull(v, nullptr, 10));
+    unsigned long long* p = base + (size_t)(next % slots) * 2048;
+    ++next;
+    return p;
 }
 
 // GEMM dispatch: tcgen05 for M > 64, the warp-level kernel (with split-K) for the skinny shapes.
@@ -455,7 +462,7 @@ int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* ou
         d.nq = queries; d.nk = keys; d.keys_per_split = ((keys + 7) / 8 + 7) / 8 * 8;
         d.scale_log2 = kLog2e / sqrtf((float)head_dim);
         d.mask_rows = heads; d.mask_key_le = encoder_seq_len; d.prefix_keys = encoder_seq_len;
-        d.status = device_status_ptr();
+        d.status = device_status_ptr(); d.dbg = debug_timestamps();
         return launch_decoder_attention_cluster(d, pdl_enabled(), S(stream));
     }
     const int splits = (keys + 127) / 128;
@@ -509,6 +516,22 @@ int fvla_decoder_action_out_proj(const void* x, int x_is_f32, const void* weight
         e = launch_pdl(action_out_kernel<bf16, bf16>, dim3(M), dim3(256), 0, st, B(x), B(weight), B(bias), Bm(out), Bm(mirror), Bm(norm_factor), K);
     if (e != cudaSuccess) { set_error("action_out_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("action_out_kernel");
+}
+
+int fvla_l2_prefetch(const void* const* ptrs, const size_t* bytes, int count, void* stream) {
+    FVLA_REQUIRE(count > 0 && count <= 8 && ptrs != nullptr && bytes != nullptr, "l2_prefetch: 1..8 ranges, got %d", count);
+    PrefetchArgs a;
+    a.count = count;
+    for (int i = 0; i < count; ++i) {
+        FVLA_REQUIRE(ptrs[i] != nullptr && aligned16(ptrs[i]), "l2_prefetch: range %d is null or not 16-byte aligned", i);
+        a.ptr[i] = static_cast<const uint8_t*>(ptrs[i]);
+        a.bytes[i] = bytes[i];
+    }
+    int mode = 0, grid = 148, threads = 32; unsigned long long chunk = 8192;
+    if (const char* v = getenv("FVLA_DEBUG_PREFETCH")) sscanf(v, "%d,%d,%d,%llu", &mode, &grid, &threads, &chunk);
+    a.mode = mode; a.chunk = chunk;
+    l2_prefetch_kernel<<<grid, threads, 0, S(stream)>>>(a);
+    return check_launch("l2_prefetch_kernel");
 }
 
 }  // extern "C"

@@ -143,7 +143,7 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
         mbar_init(in_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        if (i_own) mbar_expect_tx(in_bar, (uint32_t)S * (uint32_t)TS * (512u + (p.need_factor ? 4u : 0u)));
+        if (i_own) mbar_expect_tx(in_bar, (uint32_t)(S - 1) * (uint32_t)TS * (512u + (p.need_factor ? 4u : 0u)));      // S - 1 peers send
     }
     // One lane per k-block sets up that block's barrier and requests its weights: all of this
     // CTA's share of W is in flight within a few hundred cycles of kernel start.
@@ -300,20 +300,17 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
     tc5::tc_fence_after();
     FVLA_STAMP(3);
     __syncthreads();                                   // sums of squares are complete
-    // Stage this CTA's partial tile as [token][n] fp32 over the (now idle) weight region.
-    if (warp < 4) {
-        float lo[32], hi[32];
-        tc5::tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16), lo);
-        tc5::tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + 32, hi);
+    // Stage this CTA's partial tile as [token][n] fp32 over the (now idle) weight region. All 16 warps
+    // take part: warp w reads TMEM lanes 32 (w & 3) .. + 32 (its n) and token columns 16 (w >> 2) .. + 16.
+    {
+        const int q = warp & 3, g = warp >> 2;
+        float part[16];
+        tc5::tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + g * 16, part);
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
-            stage[t * TN + tid] = done ? lo[t] : 0.f;
-            stage[(32 + t) * TN + tid] = done ? hi[t] : 0.f;
-        }
-    } else if (p.need_factor && tid >= 128 && tid < 128 + TOK) {
-        const int t = tid - 128;
-        stage[TOK * TN + t] = t < p.M ? ssq_local[t * 2] + (KB == 8 ? ssq_local[t * 2 + 1] : 0.f) : 0.f;
+        for (int t = 0; t < 16; ++t) stage[(g * 16 + t) * TN + q * 32 + lane] = done ? part[t] : 0.f;
     }
+    if (p.need_factor && tid < TOK)
+        stage[TOK * TN + tid] = tid < p.M ? ssq_local[tid * 2] + (KB == 8 ? ssq_local[tid * 2 + 1] : 0.f) : 0.f;
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // staging writes -> visible to the bulk copies
     tc5::tc_fence_before();
     __syncthreads();
@@ -321,6 +318,7 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
     if (tid == 0) {
         // one bulk copy per owner: its slice of tokens goes to slot [src = my rank] of its RED buffer
         for (int r = 0; r < owners; ++r) {
+            if (r == (int)rank) continue;                    // the owner reads its own slice where it was staged
             bulk_copy_to_cta(map_to_cta(base + off_red + (uint32_t)(rank * TS) * 512u, (uint32_t)r),
                              base + (uint32_t)(r * TS) * 512u, (uint32_t)TS * 512u, map_to_cta(in_bar, (uint32_t)r));
             if (p.need_factor)
@@ -341,15 +339,17 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
             const int tl = item / QPT, c4 = (item % QPT) * 4;
             const int token = (int)rank * TS + tl;
             if (item >= items || token >= p.M) continue;
+            // partial of source rank s for this token: received in RED, or (own rank) still in the staging area
+            auto part_row = [&](int s) { return s == (int)rank ? stage + ((int)rank * TS + tl) * TN : red + (s * TS + tl) * TN; };
             float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int s = 0; s < S; ++s) {
-                const float4 v = *reinterpret_cast<const float4*>(red + (s * TS + tl) * TN + c4);
+                const float4 v = *reinterpret_cast<const float4*>(part_row(s) + c4);
                 sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
             }
             float factor = 1.f;
             if (p.need_factor) {
                 float ss = 0.f;
-                for (int s = 0; s < S; ++s) ss += ssq_in[s * TS + tl];
+                for (int s = 0; s < S; ++s) ss += s == (int)rank ? stage[TOK * TN + (int)rank * TS + tl] : ssq_in[s * TS + tl];
                 factor = rsqrtf(ss * (1.0f / (float)p.K) + 1e-6f);
                 if (p.factor_out && tile == 0 && c4 == 0) p.factor_out[token] = __float2bfloat16_rn(factor);
             }
@@ -372,7 +372,7 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
                 // columns 0..63 of the tile are gate columns, 64..127 the matching up columns
                 float4 up = make_float4(0.f, 0.f, 0.f, 0.f);
                 for (int s = 0; s < S; ++s) {
-                    const float4 v = *reinterpret_cast<const float4*>(red + (s * TS + tl) * TN + 64 + c4);
+                    const float4 v = *reinterpret_cast<const float4*>(part_row(s) + 64 + c4);
                     up.x += v.x; up.y += v.y; up.z += v.z; up.w += v.w;
                 }
                 const float f2 = factor;

@@ -89,6 +89,46 @@ def sync_shadow(t: torch.Tensor) -> None:
             return
 
 
+# Side stream on which `prefetch_l2` runs, per device, and whether work on it still has to be joined.
+_PREFETCH: dict = {"streams": {}, "pending": None}
+
+
+def prefetch_l2(*tensors: torch.Tensor) -> None:
+    """Start pulling `tensors` (up to 8, contiguous) into L2 on a side stream, ordered after the work
+    already enqueued on the current stream. The decoder calls this one layer ahead of its weight reads.
+    Legal during stream capture (the side stream joins the capture); `join_prefetch` must follow."""
+    import ctypes
+    if not tensors:
+        return
+    main = torch.cuda.current_stream()
+    dev = tensors[0].device
+    side = _PREFETCH["streams"].get(dev.index)
+    if side is None:
+        side = _PREFETCH["streams"][dev.index] = torch.cuda.Stream(device=dev)
+    fork = torch.cuda.Event()
+    fork.record(main)
+    side.wait_event(fork)
+    n = len(tensors)
+    ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in tensors])
+    sizes = (ctypes.c_size_t * n)(*[t.numel() * t.element_size() for t in tensors])
+    for t in tensors:
+        if not t.is_contiguous():
+            raise ValueError("prefetch_l2: tensors must be contiguous")
+    _lib.call("fvla_l2_prefetch", ptrs, sizes, n, side.cuda_stream)
+    _PREFETCH["pending"] = side
+
+
+def join_prefetch() -> None:
+    """Make the current stream wait for the side-stream prefetches issued so far."""
+    side = _PREFETCH["pending"]
+    if side is None:
+        return
+    done = torch.cuda.Event()
+    done.record(side)
+    torch.cuda.current_stream().wait_event(done)
+    _PREFETCH["pending"] = None
+
+
 def scratch(role: str, shape, dtype, device) -> torch.Tensor:
     """Graph-safe temporary from the pool that is active at call time."""
     return _POOL.get(role, shape, dtype, device)
@@ -368,4 +408,5 @@ DECODER_WRAPPERS = {f.__name__: f for f in (
     decoder_norm_gated_ffn, decoder_action_out_proj)}
 
 # `sync_shadow` rides in the table so that orchestration code can reach it through `ops`.
-ALL_WRAPPERS = {**VISION_WRAPPERS, **ENCODER_WRAPPERS, **DECODER_WRAPPERS, "sync_shadow": sync_shadow}
+ALL_WRAPPERS = {**VISION_WRAPPERS, **ENCODER_WRAPPERS, **DECODER_WRAPPERS, "sync_shadow": sync_shadow,
+                "prefetch_l2": prefetch_l2, "join_prefetch": join_prefetch}

@@ -8,6 +8,8 @@ all on the B200 side of the drop-in boundary:
     `ops.encoder_attention`) into preallocated buffers instead of being torch calls.
   * When the buffer plan holds `diffusion_noise_f32`, the Euler updates accumulate in it and
     the bf16 `diffusion_noise` is refreshed once at the end of the decoder.
+  * When the table offers `prefetch_l2`, the decoder asks for the next layer's weights and prefix K/V
+    one layer ahead (a hint on a side stream; results do not depend on it).
 """
 from __future__ import annotations
 
@@ -60,7 +62,18 @@ def transformer_encoder(ops, weights, buffers, encoder_seq_len):
         ops.encoder_ffn_down_residual(b["encoder_hidden"], w["encoder_ffn_down_w"][layer], x)
 
 
-def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LAYERS, noise=None):
+_DECODER_LAYER_WEIGHTS = ("decoder_attn_qkv_w", "decoder_attn_o_w", "decoder_ffn_gate_w", "decoder_ffn_up_w",
+                          "decoder_ffn_down_w")
+
+
+def _prefetch_decoder_layer(ops, weights, buffers, layer):
+    if hasattr(ops, "prefetch_l2"):
+        ops.prefetch_l2(*[weights[name][layer] for name in _DECODER_LAYER_WEIGHTS],
+                        buffers["encoder_K"][layer], buffers["encoder_V"][layer])
+
+
+def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LAYERS, noise=None,
+                 prefetch_next_step=False):
     """One flow-matching Euler step over `noise` (default: the plan's master copy)."""
     w, b, S = weights, buffers, encoder_seq_len
     if noise is None:
@@ -76,6 +89,10 @@ def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LA
     q = b["decoder_q_buf"]
     for layer in range(layers):
         k_cache, v_cache = b["encoder_K"][layer], b["encoder_V"][layer]
+        if layer + 1 < layers:
+            _prefetch_decoder_layer(ops, w, b, layer + 1)
+        elif prefetch_next_step:
+            _prefetch_decoder_layer(ops, w, b, 0)
         ops.decoder_norm_qkv_rope(x, w["decoder_attn_qkv_w"][layer], b["decoder_rope_weights"], q,
                                   k_cache[S:], v_cache[S:], nf)
         ops.decoder_attention(q, k_cache, v_cache, b["decoder_attn_buf"], q, S)
@@ -85,6 +102,8 @@ def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LA
         ops.decoder_ffn_down_residual(b["decoder_hidden"], w["decoder_ffn_down_w"][layer], x)
     ops.decoder_action_out_proj(x[1:], w["decoder_action_fused_out_proj_w"],
                                 w["decoder_action_fused_out_proj_b"], noise, nf)
+    if not prefetch_next_step and hasattr(ops, "join_prefetch"):
+        ops.join_prefetch()                  # the side stream rejoins before the caller goes on
 
 
 def transformer_decoder(ops, weights, buffers, encoder_seq_len, steps=DIFFUSION_STEPS,
@@ -96,8 +115,10 @@ def transformer_decoder(ops, weights, buffers, encoder_seq_len, steps=DIFFUSION_
     master = b.get("diffusion_noise_f32")
     if master is not None:
         master.copy_(b["diffusion_noise"])
+    _prefetch_decoder_layer(ops, weights, b, 0)
     for step in range(steps):
-        decoder_step(ops, weights, b, encoder_seq_len, step, layers, noise=master)
+        decoder_step(ops, weights, b, encoder_seq_len, step, layers, noise=master,
+                     prefetch_next_step=step + 1 < steps)
     if master is not None:
         b["diffusion_noise"].copy_(master)
 

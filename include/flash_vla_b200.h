@@ -140,6 +140,12 @@ int fvla_decoder_action_out_proj(const void* x, int x_is_f32, const void* weight
                                  int out_is_f32, void* mirror, void* norm_factor, int M, int N,
                                  int K, void* stream);
 
+/* No counterpart in the reference. Enqueues a small kernel that pulls `count` (1..8) byte ranges
+ * (16-byte aligned starts) from HBM into L2. The decoder GEMMs read every weight once per Euler step,
+ * always cold; a host that runs this on a second stream one layer ahead of them turns that read into
+ * an L2 hit. Purely a hint: no data is modified and no result depends on it. */
+int fvla_l2_prefetch(const void* const* ptrs, const size_t* bytes, int count, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
