@@ -31,7 +31,10 @@ struct AttnArgs {
     int splits, keys_per_split;
 };
 
-template <int HD>   // padded head dim, multiple of 16
+// HD: padded head dim, multiple of 16. STAGES: K/V tiles in shared memory; 2 overlaps the next
+// tile's load with this tile's math inside the CTA, 1 halves the footprint so that two CTAs share an SM
+// and overlap each other instead.
+template <int HD, int STAGES>
 __global__ void __launch_bounds__(128) attention_kernel(const AttnArgs p) {
     constexpr int BQ = 64, BKV = 64;
     constexpr int PITCH = HD * 2 + 16;          // bytes; +16 keeps ldmatrix rows on distinct banks
@@ -78,14 +81,24 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnArgs p) {
     const int row_lo = q0 + warp * 16 + (lane >> 2);      // this thread's two rows: row_lo, row_lo + 8
 
     for (int jb = 0; jb < nblocks; ++jb) {
-        const int stage = jb & 1;
-        if (jb + 1 < nblocks) {
-            const int kb = key_beg + (jb + 1) * BKV;
-            load_rows(sKV + (stage ^ 1) * 2 * TILE, K, p.k_stride, kb, key_end);
-            load_rows(sKV + (stage ^ 1) * 2 * TILE + TILE, V, p.v_stride, kb, key_end);
+        const int stage = STAGES == 2 ? (jb & 1) : 0;
+        if (STAGES == 2) {
+            if (jb + 1 < nblocks) {
+                const int kb = key_beg + (jb + 1) * BKV;
+                load_rows(sKV + (stage ^ 1) * 2 * TILE, K, p.k_stride, kb, key_end);
+                load_rows(sKV + (stage ^ 1) * 2 * TILE + TILE, V, p.v_stride, kb, key_end);
+            }
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            if (jb > 0) {                    // the barrier closing the previous iteration freed the tile
+                const int kb = key_beg + jb * BKV;
+                load_rows(sKV, K, p.k_stride, kb, key_end);
+                load_rows(sKV + TILE, V, p.v_stride, kb, key_end);
+                cp_async_commit();
+            }
+            cp_async_wait<0>();
         }
-        cp_async_commit();
-        cp_async_wait<1>();
         __syncthreads();
         const uint32_t sK = sKV + stage * 2 * TILE, sV = sK + TILE;
 
@@ -218,6 +231,7 @@ __global__ void __launch_bounds__(128) attention_combine_kernel(const float* __r
                                                                 const float* __restrict__ part_lse,
                                                                 bf16* __restrict__ out, int nq,
                                                                 int nq_pad, int hd, int splits) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");      // no-op unless launched as a dependent
     const int row = blockIdx.x * 2 + (threadIdx.x >> 6);
     const int t = threadIdx.x & 63;
     if (row >= nq) return;
@@ -241,10 +255,10 @@ __global__ void __launch_bounds__(128) attention_combine_kernel(const float* __r
     }
 }
 
-template <int HD>
+template <int HD, int STAGES = 2>
 inline int launch_attention(const AttnArgs& a, dim3 grid, cudaStream_t st) {
-    constexpr int smem = 5 * 64 * (HD * 2 + 16);
-    auto kern = attention_kernel<HD>;
+    constexpr int smem = (1 + 2 * STAGES) * 64 * (HD * 2 + 16);
+    auto kern = attention_kernel<HD, STAGES>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

@@ -328,8 +328,14 @@ int fvla_encoder_norm_qkv_rope(const void* x, const void* weight_qkv, const void
     return launch_gemm(a, nullptr, 0, S(stream));
 }
 
+size_t fvla_encoder_attention_workspace_bytes(int queries, int keys) {
+    if (queries <= 0 || keys <= 0) return 0;
+    const size_t qpad = (size_t)(queries + 63) / 64 * 64;
+    return 2 * (align256(qpad * sizeof(float)) + align256(qpad * 256 * sizeof(float)));
+}
+
 int fvla_encoder_attention(const void* Q, const void* K, const void* V, void* out, int queries, int keys,
-                           int head_dim, float scale, void* stream) {
+                           int head_dim, float scale, void* ws, size_t ws_bytes, void* stream) {
     FVLA_REQUIRE(queries > 0 && keys > 0, "encoder_attention: bad shape");
     if (head_dim != 256) { set_error("encoder_attention: head_dim %d not built (256 only)", head_dim); return FVLA_ERR_UNSUPPORTED; }
     AttnArgs a{};
@@ -337,7 +343,25 @@ int fvla_encoder_attention(const void* Q, const void* K, const void* V, void* ou
     a.q_stride = a.k_stride = a.v_stride = a.o_stride = head_dim;
     a.batch_inner = 1; a.nq = queries; a.nk = keys; a.hd = head_dim; a.nq_pad = queries;
     a.scale_log2 = scale * kLog2e; a.splits = 1; a.keys_per_split = keys;
-    return launch_attention<256>(a, dim3((queries + 63) / 64, 1, 1), S(stream));
+    const int q_tiles = (queries + 63) / 64;
+    // With scratch, the keys are split in two: twice the CTAs, each with a one-tile K/V buffer so that two
+    // share an SM; a second kernel merges the halves. Worth it when one wave of CTAs leaves SMs idle.
+    if (ws != nullptr && ws_bytes >= fvla_encoder_attention_workspace_bytes(queries, keys) && keys > 128 && q_tiles < 2 * tc5::num_sms()) {
+        const size_t qpad = (size_t)q_tiles * 64;
+        a.splits = 2;
+        a.keys_per_split = ((keys + 1) / 2 + 63) / 64 * 64;
+        a.nq_pad = (int)qpad;
+        a.part_lse = (float*)ws;
+        a.part_o = (float*)((uint8_t*)ws + 2 * align256(qpad * sizeof(float)));
+        a.out = nullptr;
+        int rc = launch_attention<256, 1>(a, dim3(q_tiles, 1, 2), S(stream));
+        if (rc) return rc;
+        cudaError_t e = launch_pdl(attention_combine_kernel, dim3((queries + 1) / 2), dim3(128), 0, S(stream),
+                                   (const float*)a.part_o, (const float*)a.part_lse, Bm(out), queries, (int)qpad, head_dim, 2);
+        if (e != cudaSuccess) { set_error("attention_combine_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
+        return check_launch("attention_combine_kernel");
+    }
+    return launch_attention<256>(a, dim3(q_tiles, 1, 1), S(stream));
 }
 
 int fvla_linear_residual(const void* x, const void* weight, void* out, int out_is_f32, void* out_shadow, int M,

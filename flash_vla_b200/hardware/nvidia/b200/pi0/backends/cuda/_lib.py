@@ -23,7 +23,7 @@ SIGNATURES: dict[str, list] = {
     "fvla_vision_norm_ffn_up": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fvla_encoder_projector": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fvla_encoder_norm_qkv_rope": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
-    "fvla_encoder_attention": [_P, _P, _P, _P, _I, _I, _I, _F, _P],
+    "fvla_encoder_attention": [_P, _P, _P, _P, _I, _I, _I, _F, _P, _Z, _P],
     "fvla_linear_residual": [_P, _P, _P, _I, _P, _I, _I, _I, _P, _Z, _P],
     "fvla_encoder_norm_gated_ffn": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fvla_decoder_small_proj": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _Z, _P],
@@ -40,6 +40,7 @@ QUERIES: dict[str, tuple] = {
     "fvla_device_status": ([_P], c_int),
     "fvla_gemm_workspace_bytes": ([_I, _I, _I, _I], c_size_t),
     "fvla_decoder_attention_workspace_bytes": ([_I, _I], c_size_t),
+    "fvla_encoder_attention_workspace_bytes": ([_I, _I], c_size_t),
     "fvla_patch_embed_workspace_bytes": ([_I], c_size_t),
 }
 

@@ -257,8 +257,9 @@ def encoder_attention(Q, K, V, scale, out):
     keys = K.shape[0]
     if out.numel() != queries * hd:
         raise ValueError("encoder_attention: out has the wrong size")
+    ws, nb = _ws("enc_attn_ws", _lib.load().fvla_encoder_attention_workspace_bytes(queries, keys), Q.device)
     _lib.call("fvla_encoder_attention", _chk("Q", Q), _chk("K", K, (keys, hd)), _chk("V", V, (keys, hd)),
-              _chk("out", out), queries, keys, hd, float(scale), _stream())
+              _chk("out", out), queries, keys, hd, float(scale), ws, nb, _stream())
     return out
 
 

@@ -98,9 +98,12 @@ int fvla_encoder_projector(const void* x, const void* norm_w, const void* norm_b
 int fvla_encoder_norm_qkv_rope(const void* x, const void* weight_qkv, const void* rope, void* Q,
                                void* K, void* V, void* x_norm, int M, int Kdim, int heads,
                                int head_dim, void* stream);
-/* kernels/attention.py:29-34: unmasked multi-query attention, Q flat (tokens*heads, hd). */
+/* kernels/attention.py:29-34: unmasked multi-query attention, Q flat (tokens*heads, hd). With `ws`
+ * (fvla_encoder_attention_workspace_bytes; contents need no initialisation) the keys are split over
+ * twice as many CTAs and a second kernel merges the halves; NULL keeps the single-kernel form. */
+size_t fvla_encoder_attention_workspace_bytes(int queries, int keys);
 int fvla_encoder_attention(const void* Q, const void* K, const void* V, void* out, int queries,
-                           int keys, int head_dim, float scale, void* stream);
+                           int keys, int head_dim, float scale, void* ws, size_t ws_bytes, void* stream);
 /* wrappers.py:366-371, :383-392 (encoder) and :176-189 (decoder): out += x(M,K) @ W(K,N). out is
  * bf16, or an fp32 residual stream when out_is_f32 != 0. out_shadow (may be NULL; M <= 64 only) is a
  * bf16 tensor of out's shape that receives the rounded new value, for a later GEMM to read. */
