@@ -1,0 +1,332 @@
+// tcgen05 flash attention for the prefix encoder: unmasked multi-query attention over flat queries
+// (token x head rows, one shared K/V head), head dimension 256.
+//
+// One CTA owns 128 query rows (= the 128 TMEM lanes) and walks the keys in blocks of 128:
+//   * warp 0 (one lane) is the TMA producer: the Q tile once, then K and V blocks, each into its own
+//     single buffer (K is free again as soon as S = Q K^T has been issued, V once P V has);
+//   * warp 1 (one lane) issues the MMAs: S_j = Q K_j^T (16 x m128 n128 k16) into one of two TMEM score
+//     buffers, always one block ahead of O += P_j V_j (8 x m128 n256 k16) into a TMEM accumulator;
+//   * warps 2-5 are the softmax: thread = query row. They read S_j from TMEM, keep a running maximum,
+//     write P_j = exp2(S_j - m) as bf16 into the K-major operand layout in shared memory and track the
+//     row sum. The accumulator is rescaled only when the maximum has grown by more than 2^8 since the
+//     value P is expressed against (rare after the first block), so P V seldom waits for a correction.
+// All operands are used where TMA puts them (128-byte swizzle): Q and K are K-major, V is the
+// MN-major B operand exactly as the weights of the GEMM kernels.
+#pragma once
+
+#include "common.cuh"
+#include "gemm_tc5.cuh"
+
+namespace fvla {
+namespace attn5 {
+
+using tc5::mbar_init;
+using tc5::mbar_expect_tx;
+using tc5::mbar_wait;
+using tc5::tma_load_2d;
+using tc5::smem_desc;
+
+constexpr int HD = 256, BQ = 128, BKEY = 128, THREADS = 192;
+constexpr int Q_BYTES = BQ * HD * 2, K_BYTES = BKEY * HD * 2, V_BYTES = BKEY * HD * 2, P_BYTES = BQ * BKEY * 2;
+constexpr int OFF_Q = 0, OFF_K = OFF_Q + Q_BYTES, OFF_V = OFF_K + K_BYTES, OFF_P = OFF_V + V_BYTES;
+constexpr int OFF_BAR = OFF_P + P_BYTES;
+constexpr int SMEM = 1024 + OFF_BAR + 192;
+constexpr uint32_t S_COLS = 128, O_COL = 256;         // TMEM: S buffers at columns 0 and 128, O at 256..511
+constexpr float RESCALE_THRESHOLD = 8.0f;              // log2 units
+
+struct Args {
+    bf16* out;
+    int nq, nk;
+    float scale_log2;
+    int* status;
+};
+
+// S = Q K^T: both operands K-major.
+__host__ __device__ constexpr uint32_t idesc_qk() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (0u << 16) | ((uint32_t)(BKEY >> 3) << 17) |
+           ((uint32_t)(BQ >> 4) << 24);
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// 128 consecutive TMEM columns of this thread's lane: four 32-column loads issued back to back, one wait.
+__device__ __forceinline__ void ld_row128(uint32_t taddr, float (&v)[128]) {
+    uint32_t r[128];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[c * 32 + 0]), "=r"(r[c * 32 + 1]), "=r"(r[c * 32 + 2]), "=r"(r[c * 32 + 3]), "=r"(r[c * 32 + 4]), "=r"(r[c * 32 + 5]),
+              "=r"(r[c * 32 + 6]), "=r"(r[c * 32 + 7]), "=r"(r[c * 32 + 8]), "=r"(r[c * 32 + 9]), "=r"(r[c * 32 + 10]), "=r"(r[c * 32 + 11]),
+              "=r"(r[c * 32 + 12]), "=r"(r[c * 32 + 13]), "=r"(r[c * 32 + 14]), "=r"(r[c * 32 + 15]), "=r"(r[c * 32 + 16]), "=r"(r[c * 32 + 17]),
+              "=r"(r[c * 32 + 18]), "=r"(r[c * 32 + 19]), "=r"(r[c * 32 + 20]), "=r"(r[c * 32 + 21]), "=r"(r[c * 32 + 22]), "=r"(r[c * 32 + 23]),
+              "=r"(r[c * 32 + 24]), "=r"(r[c * 32 + 25]), "=r"(r[c * 32 + 26]), "=r"(r[c * 32 + 27]), "=r"(r[c * 32 + 28]), "=r"(r[c * 32 + 29]),
+              "=r"(r[c * 32 + 30]), "=r"(r[c * 32 + 31])
+            : "r"(taddr + c * 32) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 128; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void mbar_arrive_local(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t sQ = base + OFF_Q, sK = base + OFF_K, sV = base + OFF_V, sP = base + OFF_P;
+    const uint32_t bars = base + OFF_BAR;
+    const uint32_t q_full = bars, k_full = bars + 8, k_empty = bars + 16, v_full = bars + 24, v_empty = bars + 32;
+    const uint32_t p_full = bars + 40, p_empty = bars + 48, o_done = bars + 56;
+    auto s_full = [&](int b) { return bars + 64 + b * 8; };
+    auto s_empty = [&](int b) { return bars + 80 + b * 8; };
+    const uint32_t tmem_slot = bars + 96;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen + OFF_BAR + 96);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + OFF_BAR + 104);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q0 = blockIdx.x * BQ;
+    const int nblk = (p.nk + BKEY - 1) / BKEY;
+
+    if (tid == 0) {
+        for (int i = 0; i < 12; ++i) mbar_init(bars + i * 8, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tc5::tmem_alloc(tmem_slot, 512);
+        tc5::tmem_relinquish();
+    }
+    tc5::tc_fence_before();
+    __syncthreads();
+    tc5::tc_fence_after();
+    const uint32_t tmem = *tmem_slot_ptr;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");       // Q, K and V come from the preceding kernel
+
+    if (warp == 0) {
+        // two independent streams: lane 0 feeds Q and the K blocks, lane 1 the V blocks, so that the next K
+        // block is requested as soon as S = Q K^T has been issued, whatever the state of P V
+        if (lane == 0) {
+            tc5::prefetch_tensormap(&tmQ);
+            tc5::prefetch_tensormap(&tmK);
+            mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+            for (int a = 0; a < 4; ++a) tma_load_2d(sQ + a * 16384, &tmQ, q_full, a * 64, q0);
+            for (int j = 0; j < nblk; ++j) {
+                if (!mbar_wait(k_empty, (uint32_t)(j & 1) ^ 1u, abort_flag)) break;
+                mbar_expect_tx(k_full, K_BYTES);
+#pragma unroll
+                for (int a = 0; a < 4; ++a) tma_load_2d(sK + a * 16384, &tmK, k_full, a * 64, j * BKEY);
+            }
+        } else if (lane == 1) {
+            tc5::prefetch_tensormap(&tmV);
+            for (int j = 0; j < nblk; ++j) {
+                if (!mbar_wait(v_empty, (uint32_t)(j & 1) ^ 1u, abort_flag)) break;
+                mbar_expect_tx(v_full, V_BYTES);
+#pragma unroll
+                for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+                    for (int a = 0; a < 4; ++a)
+                        tma_load_2d(sV + kb * 32768 + a * 8192, &tmV, v_full, a * 64, j * BKEY + kb * 64);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t id_qk = idesc_qk();
+            constexpr uint32_t id_pv = tc5::instr_desc(256);
+            bool ok = mbar_wait(q_full, 0, abort_flag);
+            tc5::tc_fence_after();
+            auto issue_qk = [&](int j) -> bool {
+                const int b = j & 1;
+                if (!mbar_wait(k_full, (uint32_t)(j & 1), abort_flag)) return false;
+                if (!mbar_wait(s_empty(b), (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag)) return false;
+                tc5::tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint64_t adesc = smem_desc(sQ + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
+                    const uint64_t bdesc = smem_desc(sK + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
+                    tc5::umma_bf16(tmem + b * S_COLS, adesc, bdesc, id_qk, kk > 0 ? 1u : 0u);
+                }
+                tc5::umma_commit(k_empty);
+                tc5::umma_commit(s_full(b));
+                return true;
+            };
+            if (ok && nblk > 0) ok = issue_qk(0);
+            for (int j = 0; j < nblk && ok; ++j) {
+                if (j + 1 < nblk) { ok = issue_qk(j + 1); if (!ok) break; }
+                if (!mbar_wait(p_full, (uint32_t)(j & 1), abort_flag)) break;
+                if (!mbar_wait(v_full, (uint32_t)(j & 1), abort_flag)) break;
+                tc5::tc_fence_after();
+#pragma unroll
+                for (int k16 = 0; k16 < BKEY / 16; ++k16) {
+                    const uint64_t adesc = smem_desc(sP + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024);
+                    const uint64_t bdesc = smem_desc(sV + (k16 >> 2) * 32768 + (k16 & 3) * 2048, 8192, 1024);
+                    tc5::umma_bf16(tmem + O_COL, adesc, bdesc, id_pv, (j > 0 || k16 > 0) ? 1u : 0u);
+                }
+                tc5::umma_commit(v_empty);
+                tc5::umma_commit(p_empty);
+                tc5::umma_commit(o_done);
+            }
+        }
+    } else {
+        // softmax / correction / epilogue: one thread per query row. Every thread runs every iteration and
+        // every named barrier even after a wait has given up (`ok` false), so nobody is left behind.
+        const int quad = warp & 3;                           // TMEM lane group this warp may access
+        const int row = quad * 32 + lane;
+        const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
+        bool ok = true;
+        float m_used = 0.f, l = 0.f;
+        for (int j = 0; j < nblk; ++j) {
+            const int b = j & 1;
+            ok = ok && mbar_wait(s_full(b), (uint32_t)((j >> 1) & 1), abort_flag);
+            __syncwarp();                                    // the TMEM accesses below are warp-collective
+            tc5::tc_fence_after();
+            const uint32_t t_s = tmem + t_lane + b * S_COLS;
+            // the whole 128-key score row of this thread, read once (four loads in flight, one wait)
+            float v[BKEY];
+            ld_row128(t_s, v);
+            const bool ragged = (j + 1) * BKEY > p.nk;      // only the last block can hold keys past the end
+            float mx = -INFINITY;
+            if (!ragged) {
+#pragma unroll
+                for (int i = 0; i < BKEY; ++i) mx = fmaxf(mx, v[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < BKEY; ++i)
+                    if (j * BKEY + i < p.nk) mx = fmaxf(mx, v[i]);
+            }
+            mx *= p.scale_log2;                              // the scale is positive
+            if (j == 0) {
+                m_used = mx == -INFINITY ? 0.f : mx;
+            } else {
+                const bool grow = mx > m_used + RESCALE_THRESHOLD;
+                if (__any_sync(0xffffffffu, grow)) {
+                    // the accumulator must be quiet while it is rescaled: P_{j-1} V_{j-1} has to be complete
+                    ok = ok && mbar_wait(o_done, (uint32_t)((j - 1) & 1), abort_flag);
+                    __syncwarp();
+                    tc5::tc_fence_after();
+                    const float alpha = grow ? fast_exp2(m_used - mx) : 1.0f;
+#pragma unroll 1
+                    for (int c = 0; c < HD / 32; ++c) {
+                        float o[32];
+                        tc5::tmem_ld32(tmem + t_lane + O_COL + c * 32, o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] *= alpha;
+                        tmem_st32(tmem + t_lane + O_COL + c * 32, o);
+                    }
+                    l *= alpha;
+                    if (grow) m_used = mx;
+                    tc5::tc_fence_before();
+                }
+            }
+            // P = 2^(scale * S - m): one fused multiply-add and one special-function op per key
+            float psum = 0.f;
+            if (!ragged) {
+#pragma unroll
+                for (int i = 0; i < BKEY; ++i) { v[i] = fast_exp2(fmaf(v[i], p.scale_log2, -m_used)); psum += v[i]; }
+            } else {
+#pragma unroll
+                for (int i = 0; i < BKEY; ++i) { v[i] = j * BKEY + i < p.nk ? fast_exp2(fmaf(v[i], p.scale_log2, -m_used)) : 0.f; psum += v[i]; }
+            }
+            ok = ok && mbar_wait(p_empty, (uint32_t)(j & 1) ^ 1u, abort_flag);      // P_{j-1} has been consumed
+            __syncwarp();
+            // 8 keys = 16 bytes = one piece of this row's 128 bytes in atom (keys / 64), 128-byte swizzle
+#pragma unroll
+            for (int piece = 0; piece < BKEY / 8; ++piece) {
+                uint8_t* prow = gen + OFF_P + (piece >> 3) * 16384 + row * 128;
+                *reinterpret_cast<uint4*>(prow + (((piece & 7) ^ (row & 7)) << 4)) =
+                    make_uint4(pack_bf16x2(v[8 * piece], v[8 * piece + 1]), pack_bf16x2(v[8 * piece + 2], v[8 * piece + 3]),
+                               pack_bf16x2(v[8 * piece + 4], v[8 * piece + 5]), pack_bf16x2(v[8 * piece + 6], v[8 * piece + 7]));
+            }
+            l += psum;
+            tc5::tc_fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P stores -> visible to the MMA
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (warp == 2 && lane == 0) {
+                mbar_arrive_local(p_full);
+                mbar_arrive_local(s_empty(b));
+            }
+        }
+        if (nblk > 0) ok = ok && mbar_wait(o_done, (uint32_t)((nblk - 1) & 1), abort_flag);
+        __syncwarp();
+        tc5::tc_fence_after();
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        const int grow = q0 + row;
+        const bool store = ok && grow < p.nq;              // the TMEM loads are warp-collective: only the stores are predicated
+        bf16* dst = p.out + (size_t)(store ? grow : 0) * HD;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+            float o[32];
+            tc5::tmem_ld32(tmem + t_lane + O_COL + c * 32, o);
+            if (store) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) =
+                        make_uint4(pack_bf16x2(o[8 * q] * inv, o[8 * q + 1] * inv), pack_bf16x2(o[8 * q + 2] * inv, o[8 * q + 3] * inv),
+                                   pack_bf16x2(o[8 * q + 4] * inv, o[8 * q + 5] * inv), pack_bf16x2(o[8 * q + 6] * inv, o[8 * q + 7] * inv));
+            }
+            __syncwarp();
+        }
+    }
+
+    tc5::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc5::tc_fence_after();
+        tc5::tmem_dealloc(tmem, 512);
+    }
+    if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 4);
+}
+
+inline int launch_attention_tc5(const void* Q, const void* K, const void* V, void* out, int nq, int nk, float scale_log2,
+                                int* status, cudaStream_t st) {
+    auto kern = attention_tc5_kernel;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
+        configured = true;
+    }
+    CUtensorMap tmQ, tmK, tmV;
+    int rc = tc5::make_map(&tmQ, Q, HD, (uint64_t)nq, HD, 64, BQ);
+    if (rc) return rc;
+    rc = tc5::make_map(&tmK, K, HD, (uint64_t)nk, HD, 64, BKEY);
+    if (rc) return rc;
+    rc = tc5::make_map(&tmV, V, HD, (uint64_t)nk, HD, 64, 64);
+    if (rc) return rc;
+    Args a{static_cast<bf16*>(out), nq, nk, scale_log2, status};
+    cudaError_t e = launch_pdl(kern, dim3((nq + BQ - 1) / BQ), dim3(THREADS), SMEM, st, a, tmQ, tmK, tmV);
+    if (e != cudaSuccess) { set_error("attention_tc5_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
+    return check_launch("attention_tc5_kernel");
+}
+
+}  // namespace attn5
+}  // namespace fvla

@@ -7,6 +7,7 @@
 #include <cstring>
 
 #include "attention.cuh"
+#include "attention_tc5.cuh"
 #include "common.cuh"
 #include "gemm_mma.cuh"
 #include "gemm_tc5.cuh"
@@ -343,6 +344,11 @@ int fvla_encoder_attention(const void* Q, const void* K, const void* V, void* ou
     a.q_stride = a.k_stride = a.v_stride = a.o_stride = head_dim;
     a.batch_inner = 1; a.nq = queries; a.nk = keys; a.hd = head_dim; a.nq_pad = queries;
     a.scale_log2 = scale * kLog2e; a.splits = 1; a.keys_per_split = keys;
+    // tcgen05 kernel (FVLA_ATTN=mma keeps the warp-level kernels: diagnostic switch)
+    static int attn_tc5 = -1;
+    if (attn_tc5 < 0) { const char* v = getenv("FVLA_ATTN"); attn_tc5 = (v != nullptr && strcmp(v, "mma") == 0) ? 0 : 1; }
+    if (attn_tc5 && tc5_enabled() && aligned16(Q) && aligned16(K) && aligned16(V))
+        return attn5::launch_attention_tc5(Q, K, V, out, queries, keys, scale * kLog2e, device_status_ptr(), S(stream));
     const int q_tiles = (queries + 63) / 64;
     // With scratch, the keys are split in two: twice the CTAs, each with a one-tile K/V buffer so that two
     // share an SM; a second kernel merges the halves. Worth it when one wave of CTAs leaves SMs idle.
