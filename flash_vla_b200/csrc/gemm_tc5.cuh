@@ -229,7 +229,9 @@ struct Tc5Cfg {
     static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN");
 };
 
-template <int BN, bool DUAL, int STAGES>
+// ROPE: the staged (coalesced) epilogue also handles the RoPE + Q/K/V scatter form; without it that form
+// takes the per-row path. A template switch so that the other instantiations do not carry its registers.
+template <int BN, bool DUAL, int STAGES, bool ROPE = false>
 __global__ void __launch_bounds__(320, 1)
 tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                 const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2) {
@@ -365,7 +367,10 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
         const int ew = warp - 2, quad = warp & 3, chalf = ew >> 2;
         constexpr int HALF = BN / 2, CHUNKS = HALF / 32;
         uint8_t* stg = smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES + ew * Cfg::EPI_STAGE_BYTES;
-        const bool plain = p.rope == nullptr && !p.c_f32;    // bf16 C (and bf16 residual): staged path
+        // staged path: bf16 destination(s); the preloaded operand is the bf16 residual or, for the RoPE +
+        // scatter epilogue, the cos/sin entries of the chunk (one or the other)
+        const bool plain = !p.c_f32 && (ROPE ? !(p.R != nullptr || p.bias != nullptr || p.act != 0) : p.rope == nullptr);
+        const int rope_qd = p.heads * p.head_dim;            // RoPE epilogue: columns [0, qd) are Q, then K, then V
         const int sr = lane >> 2, sp = lane & 3;              // staged access: row sr + 8 i, 16-byte piece sp
         uint32_t tcount = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
@@ -385,7 +390,10 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                 for (int i = 0; i < 4; ++i) {
                     rco[c][i] = make_uint4(0, 0, 0, 0);
                     const int grow = m0 + quad * 32 + sr + 8 * i, gcol = n0 + c * 32 + sp * 8;
-                    if (plain && p.R && grow < p.M && gcol < p.N) {
+                    if (ROPE && plain && p.rope) {
+                        if (grow < p.M && gcol < rope_qd + p.head_dim)
+                            rco[c][i] = __ldg(reinterpret_cast<const uint4*>(p.rope + (size_t)grow * p.head_dim + (gcol % p.head_dim)));
+                    } else if (plain && p.R && grow < p.M && gcol < p.N) {
                         const int rr = p.res_mod > 0 ? grow % p.res_mod : grow;
                         rco[c][i] = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.R) + (size_t)rr * p.ldr + gcol);
                     }
@@ -452,7 +460,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                 }
                 if (plain) {
                     float res[32];
-                    if (p.R) {
+                    if (p.R || (ROPE && p.rope)) {
                         // residual arrives coalesced (8 rows x 64 B per request); hand each thread its own row
 #pragma unroll
                         for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(stg + (sr + 8 * i) * 80 + sp * 16) = rco[c][i];
@@ -476,7 +484,24 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                             a[j] = p.R ? v + res[j] : v;
                         }
                     };
-                    if (p.act == 1) finish([](float v) { return gelu_f(v); });
+                    const int col0 = n0 + c * 32;                  // first column of this chunk
+                    bf16* out_base = static_cast<bf16*>(p.C);
+                    int out_ld = p.ldc, out_col = col0;
+                    if (ROPE && p.rope) {
+                        // res[] holds this row's 16 (cos, sin) pairs for the chunk's 16 column pairs
+                        if (col0 < rope_qd + p.head_dim) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                float x0 = a[2 * i], x1 = a[2 * i + 1];
+                                if (p.round_first) { x0 = round_bf16(x0); x1 = round_bf16(x1); }
+                                a[2 * i] = x0 * res[2 * i] - x1 * res[2 * i + 1];
+                                a[2 * i + 1] = x1 * res[2 * i] + x0 * res[2 * i + 1];
+                            }
+                        }
+                        if (col0 < rope_qd) { out_base = p.q; out_ld = rope_qd; }
+                        else if (col0 < rope_qd + p.head_dim) { out_base = p.k; out_ld = p.head_dim; out_col = col0 - rope_qd; }
+                        else { out_base = p.v; out_ld = p.head_dim; out_col = col0 - rope_qd - p.head_dim; }
+                    } else if (p.act == 1) finish([](float v) { return gelu_f(v); });
                     else if (p.act == 2) finish([](float v) { return silu_f(v); });
                     else finish([](float v) { return v; });
 #pragma unroll
@@ -489,7 +514,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                     for (int i = 0; i < 4; ++i) {
                         const int grow = m0 + quad * 32 + sr + 8 * i, gcol = n0 + c * 32 + sp * 8;
                         if (grow < p.M && gcol < p.N)
-                            *reinterpret_cast<uint4*>(static_cast<bf16*>(p.C) + (size_t)grow * p.ldc + gcol) =
+                            *reinterpret_cast<uint4*>(out_base + (size_t)grow * out_ld + out_col + sp * 8) =
                                 *reinterpret_cast<const uint4*>(stg + (sr + 8 * i) * 80 + sp * 16);
                     }
                     __syncwarp();
@@ -600,10 +625,10 @@ inline Tc5Plan plan_tc5(int M, int N, int K, bool ws_ok) {
     return best;
 }
 
-template <int BN, bool DUAL, int STAGES>
+template <int BN, bool DUAL, int STAGES, bool ROPE = false>
 inline int launch_tc5_cfg(const GemmArgs& g, int* status, cudaStream_t st, int splits = 1, void* ws = nullptr) {
     using Cfg = Tc5Cfg<BN, DUAL, STAGES>;
-    auto kern = tc5_gemm_kernel<BN, DUAL, STAGES>;
+    auto kern = tc5_gemm_kernel<BN, DUAL, STAGES, ROPE>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
@@ -648,6 +673,7 @@ inline bool tc5_supports(const GemmArgs& g) {
 inline int launch_gemm_tc5(GemmArgs g, int* status, cudaStream_t st, void* ws = nullptr, size_t ws_bytes = 0) {
     if (g.Kb == 0) g.Kb = g.K;
     if (g.B2 != nullptr) return launch_tc5_cfg<128, true, 4>(g, status, st);
+    if (g.rope != nullptr) return launch_tc5_cfg<128, false, 6, true>(g, status, st);
     Tc5Plan pl = plan_tc5(g.M, g.N, g.K, ws != nullptr);
     if (const char* dbg = getenv("FVLA_DEBUG_TC5_PLAN")) {          // "bn,splits": development aid
         int bn = 128, sp = 1;
