@@ -360,11 +360,12 @@ SWEEP = {   # name: (M, K, N, gated, residual, layers cycled)
     "dec_down": (51, 4096, 1024, False, True, 18),
     "enc_gate": (768, 2048, 16384, True, False, 6),
     "enc_down": (768, 16384, 2048, False, True, 6),
+    "enc_attn": (768 * 8, 256, 768, False, False, 6),     # prefix attention: flat queries, head dim, keys
 }
 
 
 def run_sweep(args):
-    """Isolated GEMM roofline sweep (the four decoder / encoder FFN GEMMs): bf16 weights ~ N(0, 0.02),
+    """Isolated kernel roofline sweep (the four decoder / encoder FFN GEMMs and the prefix attention): bf16 weights ~ N(0, 0.02),
     activations ~ N(0, 1), fp32 accumulate, distinct weight copies cycled inside one CUDA graph so every
     launch streams its weights cold. One JSON line with HBM GB/s and TFLOP/s against the measured peaks."""
     if not torch.cuda.is_available():
@@ -380,6 +381,17 @@ def run_sweep(args):
         for name in names:
             M, K, N, gated, residual, layers = SWEEP[name]
             layers = min(layers, args.sweep_layers) if args.sweep_layers else layers
+            if name == "enc_attn":
+                q = [torch.randn(M, K, device="cuda", generator=g).to(bf16) for _ in range(layers)]
+                kv = [torch.randn(2, N, K, device="cuda", generator=g).to(bf16) for _ in range(layers)]
+                o = torch.zeros(M, K, device="cuda", dtype=bf16)
+                ms = time_isolated_op(lambda i: ops.encoder_attention(q[i], kv[i][0], kv[i][1], K ** -0.5, o), layers, args.sweep_reps)
+                flops, nbytes = 4.0 * M * N * K, 2 * (2 * M * K + 2 * N * K)
+                rows[name] = {"queries": M, "keys": N, "head_dim": K, "ms_per_launch": ms, "tflops": flops / ms / 1e9,
+                              "gbs": nbytes / ms / 1e6, "algorithmic_bytes": nbytes, "flops": flops,
+                              "frac_of_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                              "frac_of_bf16": flops / ms / 1e9 / peaks["bf16_tflops"]}
+                continue
             w = [(torch.randn(K, N, device="cuda", generator=g) * 0.02).to(bf16) for _ in range(layers * (2 if gated else 1))]
             x32 = torch.randn(M, K, device="cuda", generator=g)
             x = x32 if (name == "dec_gate") else x32.to(bf16)          # the decoder's residual stream is fp32

@@ -123,7 +123,8 @@ __global__ void __launch_bounds__(256) small_k_proj_kernel(const XT* __restrict_
 // The Euler update: out[m, :] += bias + rsqrt(mean(x[m]^2) + 1e-6) * (x[m, :] @ W), W (K, 32).
 // One CTA per row; the sum of squares rides along with the dot products so x is read once.
 // `out` is fp32 or bf16; when `mirror` is given the new value is also written there as bf16.
-// Each warp walks its share of K eight rows at a time so that eight loads are in flight.
+// Thread t owns k rows (t / 4) + 64 i and the 8 output columns 8 (t % 4) .. + 8: every W access is a
+// 16-byte load, and a batch of eight of them (plus the matching x values) is in flight per thread.
 template <typename XT, typename OT>
 __global__ void __launch_bounds__(256) action_out_kernel(const XT* __restrict__ x, const bf16* __restrict__ W,
                                                          const bf16* __restrict__ bias, OT* __restrict__ out,
@@ -133,29 +134,45 @@ __global__ void __launch_bounds__(256) action_out_kernel(const XT* __restrict__ 
     __shared__ float red[8][N + 1];
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int n = lane;                          // each warp covers all 32 outputs for its k slice
+    const int kg = tid >> 2, quad = tid & 3;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, ss = 0.f;
-    const int per_warp = (K + 7) / 8;            // contiguous k range per warp
-    const int k_begin = warp * per_warp, k_end = min(K, k_begin + per_warp);
-    const float prev = static_cast<float>(out[(size_t)m * N + n]);
-    for (int k0 = k_begin; k0 < k_end; k0 += 8) {
-        float xv[8], wv[8];
+    const float prev = lane < N && warp == 0 ? static_cast<float>(out[(size_t)m * N + lane]) : 0.f;
+    for (int k0 = 0; k0 < K; k0 += 512) {
+        uint4 wv[8];
+        float xv[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            const int k = k0 + u;
-            xv[u] = k < k_end ? static_cast<float>(x[(size_t)m * K + k]) : 0.f;
-            wv[u] = k < k_end ? __bfloat162float(W[(size_t)k * N + n]) : 0.f;
+            const int k = k0 + u * 64 + kg;
+            wv[u] = make_uint4(0, 0, 0, 0);
+            xv[u] = 0.f;
+            if (k < K) {
+                wv[u] = __ldg(reinterpret_cast<const uint4*>(W + (size_t)k * N + quad * 8));
+                xv[u] = static_cast<float>(x[(size_t)m * K + k]);
+            }
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            acc[u] += xv[u] * wv[u];
-            ss += xv[u] * xv[u];                 // identical in every lane of the warp
+            const float2 w0 = unpack_bf16x2(wv[u].x), w1 = unpack_bf16x2(wv[u].y), w2 = unpack_bf16x2(wv[u].z), w3 = unpack_bf16x2(wv[u].w);
+            acc[0] += xv[u] * w0.x; acc[1] += xv[u] * w0.y; acc[2] += xv[u] * w1.x; acc[3] += xv[u] * w1.y;
+            acc[4] += xv[u] * w2.x; acc[5] += xv[u] * w2.y; acc[6] += xv[u] * w3.x; acc[7] += xv[u] * w3.y;
+            ss += xv[u] * xv[u];                 // the four lanes of a k group hold the same x: counted once below
         }
     }
-    red[warp][n] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
-    if (lane == 0) red[warp][N] = ss;
+    // lanes of a warp: 8 k groups x 4 column quads; fold the k groups
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    }
+    if (lane < 4) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) red[warp][lane * 8 + j] = acc[j];
+        if (lane == 0) red[warp][N] = ss;
+    }
     __syncthreads();
     if (warp == 0) {
+        const int n = lane;
         float a = 0.f, s = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) { a += red[w][n]; s += red[w][N]; }
