@@ -328,5 +328,219 @@ inline int launch_attention_tc5(const void* Q, const void* K, const void* V, voi
     return check_launch("attention_tc5_kernel");
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// SigLIP attention on tcgen05: one CTA per (view, head, half of the 256 query tokens). The whole key
+// range (256 tokens) is one S tile, so there is no loop and no rescale: S = Q K^T (5 x m128 n256 k16:
+// head dim 72 padded to 80), softmax by two threads per row (128 keys each, maxima and sums swapped
+// through shared memory), O = P V (16 x m128 n80 k16). Q, K and V are read by TMA straight from the
+// packed QKV activation ([views * tokens, 3 * heads * 72], head slices of 144 bytes); the 64-wide boxes
+// that cover dims 64..127 of a slice pick up 56 columns that belong to the next slice: dims 72..79 of
+// the Q tile are zeroed in shared memory before the MMA (so the matching K columns do not matter), and
+// output columns 72..79 are simply not stored.
+// ---------------------------------------------------------------------------------------------
+namespace vis {
+constexpr int TOK = 256, HDIM = 72, THREADS = 320;
+constexpr int OFF_Q = 0;                       // 2 atoms x [128 rows x 128 B]
+constexpr int OFF_K = 32768;                   // 2 atoms x [256 rows x 128 B]
+constexpr int OFF_V = 98304;                   // [key block 4][dim atom 2][64 rows x 128 B]
+constexpr int OFF_P = 163840;                  // 4 atoms x [128 rows x 128 B]
+constexpr int OFF_BAR = 229376;
+constexpr int SMEM = 1024 + OFF_BAR + 128;
+constexpr uint32_t O_COL = 256;                // TMEM: S at columns 0..255, O at 256..335
+
+__host__ __device__ constexpr uint32_t idesc_qk() {      // m128 n256, both operands K-major
+    return (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (0u << 16) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+__host__ __device__ constexpr uint32_t idesc_pv() {      // m128 n80, A K-major, B MN-major
+    return (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) | ((uint32_t)(80 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+struct Args {
+    bf16* out;
+    int heads;
+    float scale_log2;
+    int* status;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+vision_attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                            const __grid_constant__ CUtensorMap tmV) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t sQ = base + OFF_Q, sK = base + OFF_K, sV = base + OFF_V, sP = base + OFF_P;
+    const uint32_t bars = base + OFF_BAR;
+    const uint32_t qk_full = bars, v_full = bars + 8, q_fixed = bars + 16, s_full = bars + 24, p_full = bars + 32, o_full = bars + 40;
+    const uint32_t tmem_slot = bars + 48;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen + OFF_BAR + 48);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + OFF_BAR + 56);
+    float* xch = reinterpret_cast<float*>(gen + OFF_Q);      // [2 groups][128 rows] maxima, then sums: Q is dead by then
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int qh = blockIdx.x, head = blockIdx.y, view = blockIdx.z;
+    const int width = p.heads * HDIM;
+
+    if (tid == 0) {
+        mbar_init(qk_full, 1); mbar_init(v_full, 1); mbar_init(q_fixed, 128);
+        mbar_init(s_full, 1); mbar_init(p_full, 1); mbar_init(o_full, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tc5::tmem_alloc(tmem_slot, 512);
+        tc5::tmem_relinquish();
+    }
+    tc5::tc_fence_before();
+    __syncthreads();
+    tc5::tc_fence_after();
+    const uint32_t tmem = *tmem_slot_ptr;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");       // the QKV activation comes from the preceding kernel
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tc5::prefetch_tensormap(&tmQ);
+            tc5::prefetch_tensormap(&tmK);
+            tc5::prefetch_tensormap(&tmV);
+            mbar_expect_tx(qk_full, 32768 + 65536);
+#pragma unroll
+            for (int a = 0; a < 2; ++a) {
+                tma_load_2d(sQ + a * 16384, &tmQ, qk_full, head * HDIM + a * 64, view * TOK + qh * 128);
+                tma_load_2d(sK + a * 32768, &tmK, qk_full, width + head * HDIM + a * 64, view * TOK);
+            }
+            mbar_expect_tx(v_full, 65536);
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+                for (int a = 0; a < 2; ++a)
+                    tma_load_2d(sV + kb * 16384 + a * 8192, &tmV, v_full, 2 * width + head * HDIM + a * 64, view * TOK + kb * 64);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = mbar_wait(qk_full, 0, abort_flag) && mbar_wait(q_fixed, 0, abort_flag);
+            if (ok) {
+                tc5::tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 5; ++kk) {
+                    const uint64_t adesc = smem_desc(sQ + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
+                    const uint64_t bdesc = smem_desc(sK + (kk >> 2) * 32768 + (kk & 3) * 32, 16, 1024);
+                    tc5::umma_bf16(tmem, adesc, bdesc, idesc_qk(), kk > 0 ? 1u : 0u);
+                }
+                tc5::umma_commit(s_full);
+                ok = mbar_wait(p_full, 0, abort_flag) && mbar_wait(v_full, 0, abort_flag);
+            }
+            if (ok) {
+                tc5::tc_fence_after();
+#pragma unroll
+                for (int k16 = 0; k16 < TOK / 16; ++k16) {
+                    const uint64_t adesc = smem_desc(sP + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024);
+                    const uint64_t bdesc = smem_desc(sV + (k16 >> 2) * 16384 + (k16 & 3) * 2048, 8192, 1024);
+                    tc5::umma_bf16(tmem + O_COL, adesc, bdesc, idesc_pv(), k16 > 0 ? 1u : 0u);
+                }
+                tc5::umma_commit(o_full);
+            }
+        }
+    } else {
+        // softmax / epilogue: group g (warps 2-5, 6-9) takes keys [128 g, +128) of row = 32 (warp & 3) + lane
+        const int g = (warp - 2) >> 2, quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
+        bool ok = true;
+        if (g == 0) {
+            // dims 72..79 of the Q tile hold the next slice's data: zero them (16-byte piece 1 of atom 1)
+            ok = mbar_wait(qk_full, 0, abort_flag);
+            *reinterpret_cast<uint4*>(gen + OFF_Q + 16384 + row * 128 + ((1 ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive_local(q_fixed);
+        }
+        ok = mbar_wait(s_full, 0, abort_flag) && ok;
+        __syncwarp();
+        tc5::tc_fence_after();
+        float v[128];
+        ld_row128(tmem + t_lane + g * 128, v);
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 128; ++i) mx = fmaxf(mx, v[i]);
+        xch[g * 128 + row] = mx;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const float m = fmaxf(xch[row], xch[128 + row]) * p.scale_log2;      // the scale is positive
+        asm volatile("bar.sync 1, 256;" ::: "memory");                           // maxima read before the sums overwrite them
+        float psum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 128; ++i) { v[i] = fast_exp2(fmaf(v[i], p.scale_log2, -m)); psum += v[i]; }
+#pragma unroll
+        for (int piece = 0; piece < 16; ++piece) {
+            uint8_t* prow = gen + OFF_P + (2 * g + (piece >> 3)) * 16384 + row * 128;
+            *reinterpret_cast<uint4*>(prow + (((piece & 7) ^ (row & 7)) << 4)) =
+                make_uint4(pack_bf16x2(v[8 * piece], v[8 * piece + 1]), pack_bf16x2(v[8 * piece + 2], v[8 * piece + 3]),
+                           pack_bf16x2(v[8 * piece + 4], v[8 * piece + 5]), pack_bf16x2(v[8 * piece + 6], v[8 * piece + 7]));
+        }
+        xch[g * 128 + row] = psum;
+        tc5::tc_fence_before();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P stores -> visible to the MMA
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (warp == 2 && lane == 0) mbar_arrive_local(p_full);
+        const float l = xch[row] + xch[128 + row];
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        ok = mbar_wait(o_full, 0, abort_flag) && ok;
+        __syncwarp();
+        tc5::tc_fence_after();
+        // group 0 stores dims 0..39, group 1 dims 40..71 (TMEM columns 32..63 and 64..79 are read in both)
+        float a[32], b[16];
+        tc5::tmem_ld32(tmem + t_lane + O_COL + (g == 0 ? 0 : 32), a);
+        tc5::tmem_ld16(tmem + t_lane + O_COL + (g == 0 ? 32 : 64), b);
+        if (ok) {
+            bf16* dst = p.out + ((size_t)(view * TOK + qh * 128 + row)) * width + head * HDIM;
+            auto pack8 = [&](const float* s) {
+                return make_uint4(pack_bf16x2(s[0] * inv, s[1] * inv), pack_bf16x2(s[2] * inv, s[3] * inv),
+                                  pack_bf16x2(s[4] * inv, s[5] * inv), pack_bf16x2(s[6] * inv, s[7] * inv));
+            };
+            if (g == 0) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + q * 8) = pack8(a + q * 8);
+                *reinterpret_cast<uint4*>(dst + 32) = pack8(b);
+            } else {
+                // a = dims 32..63, b = dims 64..79
+#pragma unroll
+                for (int q = 1; q < 4; ++q) *reinterpret_cast<uint4*>(dst + 32 + q * 8) = pack8(a + q * 8);
+                *reinterpret_cast<uint4*>(dst + 64) = pack8(b);
+            }
+        }
+    }
+
+    tc5::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc5::tc_fence_after();
+        tc5::tmem_dealloc(tmem, 512);
+    }
+    if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 5);
+}
+
+// qkv: [views * 256, 3 * heads * 72] bf16; out: [views * 256, heads * 72] bf16.
+inline int launch_vision_attention_tc5(const void* qkv, void* out, int views, int heads, int* status, cudaStream_t st) {
+    auto kern = vision_attention_tc5_kernel;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
+        configured = true;
+    }
+    const uint64_t cols = (uint64_t)3 * heads * HDIM, rows = (uint64_t)views * TOK;
+    CUtensorMap tmQ, tmK, tmV;
+    int rc = tc5::make_map(&tmQ, qkv, cols, rows, cols, 64, 128);
+    if (rc) return rc;
+    rc = tc5::make_map(&tmK, qkv, cols, rows, cols, 64, 256);
+    if (rc) return rc;
+    rc = tc5::make_map(&tmV, qkv, cols, rows, cols, 64, 64);
+    if (rc) return rc;
+    Args a{static_cast<bf16*>(out), heads, kLog2e / sqrtf((float)HDIM), status};
+    cudaError_t e = launch_pdl(kern, dim3(2, heads, views), dim3(THREADS), SMEM, st, a, tmQ, tmK, tmV);
+    if (e != cudaSuccess) { set_error("vision_attention_tc5_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
+    return check_launch("vision_attention_tc5_kernel");
+}
+}  // namespace vis
+
 }  // namespace attn5
 }  // namespace fvla

@@ -294,6 +294,11 @@ int fvla_vision_attention(const void* qkv, void* out, int views, int tokens, int
     FVLA_REQUIRE(views > 0 && tokens > 0 && heads > 0, "vision_attention: bad shape");
     if (head_dim != 72) { set_error("vision_attention: head_dim %d not built (72 only)", head_dim); return FVLA_ERR_UNSUPPORTED; }
     const int width = heads * head_dim;
+    // tcgen05 kernel for the model's shape (FVLA_ATTN=mma / FVLA_GEMM=mma keep the warp-level kernel)
+    static int attn_tc5 = -1;
+    if (attn_tc5 < 0) { const char* v = getenv("FVLA_ATTN"); attn_tc5 = (v != nullptr && strcmp(v, "mma") == 0) ? 0 : 1; }
+    if (attn_tc5 && tc5_enabled() && tokens == attn5::vis::TOK && aligned16(qkv) && aligned16(out))
+        return attn5::vis::launch_vision_attention_tc5(qkv, out, views, heads, device_status_ptr(), S(stream));
     AttnArgs a{};
     a.q = B(qkv); a.k = B(qkv) + width; a.v = B(qkv) + 2 * width; a.out = Bm(out);
     a.q_stride = a.k_stride = a.v_stride = 3 * width; a.o_stride = width;
