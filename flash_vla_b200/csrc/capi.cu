@@ -175,6 +175,7 @@ int fvla_device_status(void* stream) {
     if (ptr == nullptr) { set_error("device_status: no CUDA device"); return FVLA_ERR_LAUNCH; }
     int value = 0;
     cudaError_t e = cudaMemcpyAsync(&value, ptr, sizeof(int), cudaMemcpyDeviceToHost, S(stream));
+    if (e == cudaSuccess) e = cudaMemsetAsync(ptr, 0, sizeof(int), S(stream));      // read and clear
     if (e == cudaSuccess) e = cudaStreamSynchronize(S(stream));
     if (e != cudaSuccess) { set_error("device_status: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return value;
@@ -567,6 +568,14 @@ int fvla_l2_prefetch(const void* const* ptrs, const size_t* bytes, int count, vo
     a.mode = mode; a.chunk = chunk;
     l2_prefetch_kernel<<<grid, threads, 0, S(stream)>>>(a);
     return check_launch("l2_prefetch_kernel");
+}
+
+int fvla_embed_rows(const void* table, const long long* ids, void* out, int rows, int dim, long long vocab, void* stream) {
+    FVLA_REQUIRE(rows > 0 && dim > 0 && dim % 8 == 0 && vocab > 0, "embed_rows: bad shape rows=%d dim=%d (dim %% 8 == 0)", rows, dim);
+    FVLA_REQUIRE(table != nullptr && ids != nullptr && out != nullptr && aligned16(table) && aligned16(out), "embed_rows: null or misaligned pointer");
+    cudaError_t e = launch_pdl(embed_rows_kernel, dim3(rows), dim3(128), 0, S(stream), B(table), ids, Bm(out), dim, vocab, device_status_ptr());
+    if (e != cudaSuccess) { set_error("embed_rows_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
+    return check_launch("embed_rows_kernel");
 }
 
 }  // extern "C"

@@ -203,4 +203,19 @@ __global__ void __launch_bounds__(256) l2_prefetch_kernel(const PrefetchArgs a) 
     }
 }
 
+// out[r, :] = table[ids[r], :] for bf16 rows of `dim` elements (dim % 8 == 0): the prompt embedding
+// lookup. One CTA per row, 16-byte copies. An id outside [0, vocab) yields a zero row and sets the device
+// status word, so a bad prompt is reported instead of reading out of bounds.
+__global__ void __launch_bounds__(128) embed_rows_kernel(const bf16* __restrict__ table, const long long* __restrict__ ids,
+                                                         bf16* __restrict__ out, int dim, long long vocab, int* status) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int r = blockIdx.x;
+    const long long id = ids[r];
+    const bool ok = id >= 0 && id < vocab;
+    if (!ok && threadIdx.x == 0 && status) atomicExch(status, 7);
+    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)(ok ? id : 0) * dim);
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)r * dim);
+    for (int c = threadIdx.x; c < dim / 8; c += blockDim.x) dst[c] = ok ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
+}
+
 }  // namespace fvla

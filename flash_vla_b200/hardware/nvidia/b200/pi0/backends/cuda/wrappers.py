@@ -129,6 +129,20 @@ def join_prefetch() -> None:
     _PREFETCH["pending"] = None
 
 
+def embed_prompt(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = table[ids[r]]: the prompt embedding lookup (a plain row gather, no scaling). Not in the
+    reference table, which only accepts precomputed `language_embeds` (engine.py:43, :60)."""
+    vocab, dim = table.shape
+    rows = ids.numel()
+    if ids.dtype != torch.int64 or not ids.is_cuda or not ids.is_contiguous():
+        raise ValueError("embed_prompt: ids must be a contiguous int64 CUDA tensor")
+    if tuple(out.shape) != (rows, dim):
+        raise ValueError(f"embed_prompt: out has shape {tuple(out.shape)}, expected {(rows, dim)}")
+    if rows:
+        _lib.call("fvla_embed_rows", _chk("table", table), ids.data_ptr(), _chk("out", out), rows, dim, vocab, _stream())
+    return out
+
+
 def scratch(role: str, shape, dtype, device) -> torch.Tensor:
     """Graph-safe temporary from the pool that is active at call time."""
     return _POOL.get(role, shape, dtype, device)
@@ -410,4 +424,4 @@ DECODER_WRAPPERS = {f.__name__: f for f in (
 
 # `sync_shadow` rides in the table so that orchestration code can reach it through `ops`.
 ALL_WRAPPERS = {**VISION_WRAPPERS, **ENCODER_WRAPPERS, **DECODER_WRAPPERS, "sync_shadow": sync_shadow,
-                "prefetch_l2": prefetch_l2, "join_prefetch": join_prefetch}
+                "prefetch_l2": prefetch_l2, "join_prefetch": join_prefetch, "embed_prompt": embed_prompt}

@@ -83,6 +83,25 @@ class Pi0Inference:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
 
+    def set_prompt(self, ids, embedding_table):
+        """Replace the prompt: language_embeds[r] = embedding_table[ids[r]] (row gather on the device).
+
+        The prompt length is fixed at construction (it sets the static buffer plan and the captured graph):
+        `ids` must hold exactly `prompt_len` token ids. The gather writes into the static tensor the graph
+        reads, so the next `forward` uses the new prompt. An extension: the reference takes only
+        precomputed `language_embeds` (engine.py:43, :60).
+        """
+        ids = torch.as_tensor(ids, dtype=torch.int64).reshape(-1)
+        if ids.numel() != self.prompt_len:
+            raise ValueError(f"set_prompt: {ids.numel()} ids for an engine built with prompt_len={self.prompt_len}")
+        if self.prompt_len == 0:
+            return
+        target = self.weights["language_embeds"]
+        table = embedding_table.to(device=target.device, dtype=torch.bfloat16)
+        if table.ndim != 2 or table.shape[1] != target.shape[1]:
+            raise ValueError(f"set_prompt: embedding table must be (vocab, {target.shape[1]})")
+        self.ops.embed_prompt(table.contiguous(), ids.to(target.device), target)
+
     def __del__(self):
         try:
             wrappers.unregister_bf16_shadow(self.buffers["decoder_x"])

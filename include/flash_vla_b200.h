@@ -41,8 +41,9 @@ int fvla_abi_version(void);
 /* Number of kernel launches this library has enqueued in this process so far (captured launches
  * count once, at capture time). Lets a caller report how much of a pass ran in these kernels. */
 unsigned long long fvla_launch_count(void);
-/* Health word of the current device: 0, or 1 once a kernel gave up on one of its bounded waits
- * (its output is then invalid). Negative: error code. This one call synchronises `stream`. */
+/* Health word of the current device: 0, or a small positive code once a kernel gave up on one of its
+ * bounded waits (1..6: which kernel; its output is then invalid) or met a bad token id (7). Reading
+ * clears the word. Negative: error code. This one call synchronises `stream`. */
 int fvla_device_status(void* stream);
 
 /* Scratch needed by a GEMM-shaped op of the given logical size. `dual` = 1 for gated FFNs. */
@@ -148,6 +149,12 @@ int fvla_decoder_action_out_proj(const void* x, int x_is_f32, const void* weight
  * always cold; a host that runs this on a second stream one layer ahead of them turns that read into
  * an L2 hit. Purely a hint: no data is modified and no result depends on it. */
 int fvla_l2_prefetch(const void* const* ptrs, const size_t* bytes, int count, void* stream);
+
+/* No counterpart in the reference, which accepts only precomputed `language_embeds` (engine.py:43, :60):
+ * out[r, :] = table[ids[r], :], bf16 rows of `dim` elements (dim % 8 == 0), ids int64 on the device. An id
+ * outside [0, vocab) gives a zero row and makes fvla_device_status report 7. */
+int fvla_embed_rows(const void* table, const long long* ids, void* out, int rows, int dim,
+                    long long vocab, void* stream);
 
 #ifdef __cplusplus
 }

@@ -48,7 +48,7 @@ def test_op_table_contract():
         "decoder_ffn_down_residual", "decoder_norm_gated_ffn", "decoder_action_out_proj"}
     assert reference_names <= set(cuda.ALL_WRAPPERS)
     assert set(cuda.ALL_WRAPPERS) - reference_names == {"vision_attention", "encoder_attention", "sync_shadow",
-                                                              "prefetch_l2", "join_prefetch"}
+                                                              "prefetch_l2", "join_prefetch", "embed_prompt"}
     assert set(DEFAULT_FUSED_OPS) == {"decoder_norm_gated_ffn", "decoder_action_out_proj", "decoder_attention"}
     fused, unfused = op_table(True), op_table(False)
     assert fused.decoder_attention is cuda.FUSED_WRAPPERS["decoder_attention"]

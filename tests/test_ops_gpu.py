@@ -302,3 +302,33 @@ def test_prefetch_l2_is_a_pure_hint(ops):
     with pytest.raises(FvlaError):
         ops[1].prefetch_l2(*[ts[0]] * 9)
     ops[1].join_prefetch()
+
+
+@pytest.mark.parametrize("rows", [1, 48, 49])
+def test_embed_prompt_is_a_row_gather(ops, rows):
+    """Prompt embedding lookup against the oracle's gather, ids at both ends of the vocabulary included."""
+    g = torch.Generator().manual_seed(5)
+    vocab, dim = 4096, 2048
+    table = rnd(g, vocab, dim, scale=0.02)
+    ids = torch.randint(0, vocab, (rows,), generator=g)
+    ids[0], ids[-1] = vocab - 1, 0
+    want = O.embed_prompt(table, ids)
+    out = torch.zeros(rows, dim, dtype=bf16, device="cuda")
+    ops[1].embed_prompt(table.cuda(), ids.cuda(), out)
+    assert torch.equal(out.cpu(), want.to(bf16))
+
+
+def test_embed_prompt_reports_a_bad_id(ops):
+    """An id outside the vocabulary gives a zero row and is reported through the device status word."""
+    from flash_vla_b200.hardware.nvidia.b200.pi0.backends.cuda import _lib
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(6)
+    table = rnd(g, 100, 64).cuda()
+    ids = torch.tensor([3, 100, 7, -1], dtype=torch.int64).cuda()
+    out = torch.full((4, 64), 9.0, dtype=bf16, device="cuda")
+    assert lib.fvla_device_status(None) == 0
+    ops[1].embed_prompt(table, ids, out)
+    assert lib.fvla_device_status(None) == 7          # reading clears it
+    assert lib.fvla_device_status(None) == 0
+    assert torch.equal(out[0], table[3]) and torch.equal(out[2], table[7])
+    assert (out[1] == 0).all() and (out[3] == 0).all()

@@ -74,10 +74,17 @@ def test_full_forward(full_checkpoint, prompt_len):
     gold = torch.load(GOLDEN / f"forward_p{prompt_len}.pt")
     ck = dict(full_checkpoint)
     if prompt_len:
-        ck["language_embeds"] = prompt_embeds(prompt_len)[1]
+        rows = prompt_embeds(prompt_len)[1]
+        ck["language_embeds"] = torch.zeros_like(rows)           # the prompt arrives through set_prompt below
     images, state, noise = bench_inputs()
     engine = Pi0Inference(ck, num_views=3, chunk_size=50)
     assert engine.encoder_seq_len == 768 + prompt_len
+    if prompt_len:
+        # a small table holding the prompt's rows in shuffled order; the ids undo the shuffle
+        perm = torch.randperm(prompt_len, generator=torch.Generator().manual_seed(9))
+        engine.set_prompt(torch.argsort(perm), rows[perm])
+        with pytest.raises(ValueError):
+            engine.set_prompt(torch.arange(prompt_len + 1), rows)
     out = engine.forward(images, state, noise).clone()
     out2 = engine.forward(images, state, noise).clone()
     torch.cuda.synchronize()
