@@ -220,7 +220,7 @@ struct Tc5Cfg {
     static constexpr int STAGE_BYTES = A_BYTES + NB * B_BYTES;
     static constexpr int ACC_COLS = NB * BN;                    // TMEM columns per accumulator stage
     static constexpr int TMEM_COLS = 2 * ACC_COLS <= 32 ? 32 : (2 * ACC_COLS <= 64 ? 64 : (2 * ACC_COLS <= 128 ? 128 : (2 * ACC_COLS <= 256 ? 256 : 512)));
-    static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+    static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16 + 16;     // pipeline barriers, TMEM slot / flags, cluster split-K barriers
     static constexpr int EPI_WARPS = 8;                         // two warps per TMEM lane quadrant, half the columns each
     static constexpr int EPI_STAGE_BYTES = 32 * 80;             // per warp: 32 rows x (64 B + 16 B pad)
     static constexpr int THREADS = 64 + 32 * EPI_WARPS;
@@ -231,7 +231,11 @@ struct Tc5Cfg {
 
 // ROPE: the staged (coalesced) epilogue also handles the RoPE + Q/K/V scatter form; without it that form
 // takes the per-row path. A template switch so that the other instantiations do not carry its registers.
-template <int BN, bool DUAL, int STAGES, bool ROPE = false>
+// CLUSTER: split-K inside a thread-block cluster. The `splits` CTAs of a tile are cluster mates; the ones
+// with split > 0 stage their fp32 partial tile in their own (by then idle) pipeline shared memory and push
+// it with one bulk copy into the idle pipeline memory of the split-0 CTA, which adds the partials in
+// split order and runs the epilogue. No global scratch, no semaphore; needs one work item per CTA.
+template <int BN, bool DUAL, int STAGES, bool ROPE = false, bool CLUSTER = false>
 __global__ void __launch_bounds__(320, 1)
 tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                 const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2) {
@@ -259,6 +263,8 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), Cfg::EPI_WARPS); }
+        mbar_init(bars + (2 * STAGES + 4) * 8 + 16, 1);          // cluster split-K: "the leader's pipeline memory is free"
+        mbar_init(bars + (2 * STAGES + 4) * 8 + 24, 1);          // cluster split-K: "the peers' partial tiles have arrived"
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -270,6 +276,9 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    // cluster split-K: tell the cluster mates that this CTA's barriers exist (the fence after their
+    // initialisation already published them; the matching wait sits where the first remote access is)
+    if (CLUSTER) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     // Set-up above touched only this CTA's own shared memory and TMEM.
     if (threadIdx.x == 0) stamp(1);
 
@@ -364,6 +373,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
         // area so that global loads and stores touch 64 contiguous bytes per row (8 rows per request)
         // instead of 16 bytes in each of 32 rows.
         asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (CLUSTER) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         const int ew = warp - 2, quad = warp & 3, chalf = ew >> 2;
         constexpr int HALF = BN / 2, CHUNKS = HALF / 32;
         uint8_t* stg = smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES + ew * Cfg::EPI_STAGE_BYTES;
@@ -405,7 +415,50 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
             if (tcount == 0 && threadIdx.x == 64) stamp(4);
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * Cfg::ACC_COLS + chalf * HALF;
             bool from_partials = false;
-            if (!DUAL && args.splits > 1) {
+            bool from_cluster = false;
+            if (CLUSTER && args.splits > 1) {
+                const uint32_t free_bar = bars + (2 * STAGES + 4) * 8 + 16, red_bar = bars + (2 * STAGES + 4) * 8 + 24;
+                constexpr uint32_t TILE_BYTES = BM * BN * 4;
+                if (split > 0) {
+                    // stage the partial tile as [column quad][row][4] in this CTA's idle pipeline memory, then push it
+#pragma unroll
+                    for (int c = 0; c < CHUNKS; ++c) {
+                        float a[32];
+                        tmem_ld32(t_row + c * 32, a);
+                        float* dst = reinterpret_cast<float*>(smem_gen) + ((chalf * CHUNKS + c) * 8) * (BM * 4) + (quad * 32 + lane) * 4;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4*>(dst + (j / 4) * (BM * 4)) = make_float4(a[j], a[j + 1], a[j + 2], a[j + 3]);
+                    }
+                    tc_fence_before();
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // staged tile -> visible to the bulk copy
+                    asm volatile("bar.sync 1, %0;" ::"n"(32 * Cfg::EPI_WARPS) : "memory");
+                    if (ew == 0 && lane == 0) {
+                        mbar_arrive(accempty_bar(acc));
+                        if (mbar_wait(free_bar, 0, abort_flag)) {      // the leader's pipeline memory is idle
+                            uint32_t dst0, rbar;
+                            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst0) : "r"(smem_base + (uint32_t)(split - 1) * TILE_BYTES), "r"(0));
+                            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(red_bar), "r"(0));
+#pragma unroll
+                            for (uint32_t off = 0; off < TILE_BYTES; off += 16384)
+                                asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                             ::"r"(dst0 + off), "r"(smem_base + off), "r"(16384), "r"(rbar) : "memory");
+                        }
+                    }
+                    continue;
+                }
+                if (ew == 0 && lane == 0) {
+                    mbar_expect_tx(red_bar, (uint32_t)(args.splits - 1) * TILE_BYTES);
+                    for (int sp_i = 1; sp_i < args.splits; ++sp_i) {
+                        uint32_t fb;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(fb) : "r"(free_bar), "r"(sp_i));
+                        asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(fb) : "memory");
+                    }
+                }
+                mbar_wait(red_bar, 0, abort_flag);      // a wait that gives up sets the abort flag; the sums are then garbage and reported
+                from_cluster = true;
+            }
+            if (!CLUSTER && !DUAL && args.splits > 1) {
                 // Publish this item's partial tile, then let the last-arriving item of the tile sum all
                 // of them (in split order, so the result does not depend on arrival order) and finish.
 #pragma unroll
@@ -457,6 +510,18 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                 } else {
                     tmem_ld32(t_row + c * 32, a);
                     if (DUAL) tmem_ld32(t_row + BN + c * 32, u);
+                }
+                if (CLUSTER && from_cluster) {
+                    // split 0 is this CTA's own accumulator; the others arrived in split order
+                    for (int sp_i = 1; sp_i < args.splits; ++sp_i) {
+                        const float* src = reinterpret_cast<const float*>(smem_gen + (size_t)(sp_i - 1) * (BM * BN * 4)) +
+                                           ((chalf * CHUNKS + c) * 8) * (BM * 4) + (quad * 32 + lane) * 4;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 v = *reinterpret_cast<const float4*>(src + (j / 4) * (BM * 4));
+                            a[j] += v.x; a[j + 1] += v.y; a[j + 2] += v.z; a[j + 3] += v.w;
+                        }
+                    }
                 }
                 if (plain) {
                     float res[32];
@@ -540,6 +605,11 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
         }
     }
 
+    if (CLUSTER) {
+        // nobody leaves while a bulk copy may still read its shared memory or signal its barriers
+        if (warp < 2) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");      // pairs with the arrive after set-up
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -625,10 +695,10 @@ inline Tc5Plan plan_tc5(int M, int N, int K, bool ws_ok) {
     return best;
 }
 
-template <int BN, bool DUAL, int STAGES, bool ROPE = false>
+template <int BN, bool DUAL, int STAGES, bool ROPE = false, bool CLUSTER = false>
 inline int launch_tc5_cfg(const GemmArgs& g, int* status, cudaStream_t st, int splits = 1, void* ws = nullptr) {
     using Cfg = Tc5Cfg<BN, DUAL, STAGES>;
-    auto kern = tc5_gemm_kernel<BN, DUAL, STAGES, ROPE>;
+    auto kern = tc5_gemm_kernel<BN, DUAL, STAGES, ROPE, CLUSTER>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
@@ -650,7 +720,7 @@ inline int launch_tc5_cfg(const GemmArgs& g, int* status, cudaStream_t st, int s
     a.splits = splits;
     a.k_per_split = (a.k_iters + splits - 1) / splits;
     a.partial = nullptr; a.counters = nullptr;
-    if (splits > 1) {
+    if (splits > 1 && !CLUSTER) {
         const size_t counters = (((size_t)a.tiles_m * a.tiles_n * sizeof(int) + 255) / 256) * 256;
         a.counters = reinterpret_cast<int*>(ws);
         a.partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + counters);
@@ -659,7 +729,22 @@ inline int launch_tc5_cfg(const GemmArgs& g, int* status, cudaStream_t st, int s
     { const char* v = getenv("FVLA_DEBUG_TIMESTAMPS"); a.dbg = v ? reinterpret_cast<unsigned long long*>(strtoull(v, nullptr, 10)) : nullptr; }
     int tiles = a.tiles_m * a.tiles_n * splits;
     int grid = tiles < num_sms() ? tiles : num_sms();
-    cudaError_t e = launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, a, tmA, tmB, tmB2);
+    cudaError_t e;
+    if (CLUSTER) {
+        // one work item per CTA, the splits of a tile adjacent in the grid = one cluster
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(tiles); cfg.blockDim = dim3(Cfg::THREADS); cfg.dynamicSmemBytes = Cfg::SMEM_BYTES; cfg.stream = st;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled() ? 2 : 1;
+        e = cudaLaunchKernelEx(&cfg, kern, a, tmA, tmB, tmB2);
+    } else {
+        e = launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, a, tmA, tmB, tmB2);
+    }
     if (e != cudaSuccess) { set_error("tc5_gemm_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("tc5_gemm_kernel");
 }
@@ -682,6 +767,19 @@ inline int launch_gemm_tc5(GemmArgs g, int* status, cudaStream_t st, void* ws = 
             pl.ws_bytes = sp > 1 ? 256 * ((((size_t)((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn)) * 4 + 255) / 256) +
                                        (size_t)sp * ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn) * BM * bn * 4 : 0;
         }
+    }
+    // Split-K reduced inside clusters (128-wide tiles, one work item per CTA, no scratch): taken when its
+    // estimate (mainloop + epilogue + one 64 KB push per extra split) beats the plan above.
+    if (g.rope == nullptr && !g.c_f32 && !getenv("FVLA_DEBUG_TC5_PLAN")) {
+        const int tiles = ((g.M + BM - 1) / BM) * ((g.N + 127) / 128), k_iters = (g.K + BK - 1) / BK;
+        int best_s = 0;
+        float best_t = pl.est_us;
+        for (int sp = 2; sp <= 4; ++sp) {
+            if (tiles * sp > num_sms() || k_iters / sp < 8) break;
+            const float t = ((k_iters + sp - 1) / sp) * k_step_us(128) + 4.0f + 2.5f + (sp - 1) * 2.1f;
+            if (t < best_t) { best_t = t; best_s = sp; }
+        }
+        if (best_s) return launch_tc5_cfg<128, false, 6, false, true>(g, status, st, best_s, nullptr);
     }
     if (pl.splits > 1 && (ws_bytes < pl.ws_bytes || g.rope != nullptr || g.c_f32)) pl = plan_tc5(g.M, g.N, g.K, false);
     switch (pl.bn) {
