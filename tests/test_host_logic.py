@@ -171,3 +171,16 @@ def test_header_argument_counts_match_ctypes_table():
         args = m.group(1).strip()
         count = 0 if args in ("", "void") else args.count(",") + 1
         assert count == len(argtypes), f"{name}: header has {count} parameters, ctypes table {len(argtypes)}"
+
+
+def test_graft_entry_build_passes():
+    """The entry point the build check runs: compiles (or finds the up-to-date library), verifies that every
+    declared symbol is exported and that the op table holds the reference's 19 call sites plus the extensions."""
+    import importlib
+    import sys
+    from pathlib import Path
+    root = str(Path(__file__).resolve().parents[1])
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    entry = importlib.import_module("__graft_entry__")
+    entry.build()
