@@ -215,11 +215,12 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def workload_config(n_gpus: int):
+def workload_config(n_gpus: int, episodes: int = 1):
     return {"workload": "Pi0 full forward: 3 views 224x224x3, empty prompt (prefix 768), chunk 50, 10 Euler steps, "
-                        "27 SigLIP + 18 prefix + 18 decoder layers, batch 1, one CUDA graph",
+                        "27 SigLIP + 18 prefix + 18 decoder layers, batch 1, one CUDA graph" +
+                        ("" if episodes == 1 else f"; {episodes} independent episodes per GPU on concurrent streams inside the graph"),
             "weights": "random_checkpoint N(0, 0.02) bf16, 2.709 G params",
-            "replicas": n_gpus, "episodes_per_gpu": 1, "parallelism": f"replicas x{n_gpus} (no collective)",
+            "replicas": n_gpus, "episodes_per_gpu": episodes, "parallelism": f"replicas x{n_gpus} (no collective)",
             "l2": "each step streams 5.4 GB of weights, far more than the 126 MB L2; no explicit flush"}
 
 
@@ -268,11 +269,16 @@ def run_ours(args):
     lib = _lib.load()
     ck = random_checkpoint(prompt_len=0, wscale=0.02, seed=0, device="cuda")
     launches_before = lib.fvla_launch_count()
-    engine = Pi0Inference(ck, num_views=3, chunk_size=50)
-    per_forward = (lib.fvla_launch_count() - launches_before) // 4       # 3 warm-up passes + 1 captured
+    E = max(1, args.episodes)
+    engine = Pi0Inference(ck, num_views=3, chunk_size=50, episodes=E)
+    per_forward = (lib.fvla_launch_count() - launches_before) // (4 * E)       # 3 warm-up passes + 1 captured, E episodes each
     del ck
-    images, state, noise = [t.to(torch.bfloat16).pin_memory() for t in bench_inputs(seed=rank)]
-    host_out = torch.empty(50, 32, dtype=torch.bfloat16).pin_memory()
+    if E == 1:
+        images, state, noise = [t.to(torch.bfloat16).pin_memory() for t in bench_inputs(seed=rank)]
+    else:       # one input set per episode, seeds rank * E + e
+        sets = [bench_inputs(seed=rank * E + e) for e in range(E)]
+        images, state, noise = [torch.stack([s[i] for s in sets]).to(torch.bfloat16).pin_memory() for i in range(3)]
+    host_out = torch.empty((50, 32) if E == 1 else (E, 50, 32), dtype=torch.bfloat16).pin_memory()
     stream = torch.cuda.current_stream()
 
     K, W = args.steps, max(3, args.warmup)
@@ -308,22 +314,22 @@ def run_ours(args):
 
     peaks = measured_peaks()
     line = {
-        "metric": "pi0_forwards_per_s", "value": job_throughput(args.gpus, K, ms_total), "unit": "forwards/s",
+        "metric": "pi0_forwards_per_s", "value": job_throughput(args.gpus * E, K, ms_total), "unit": "forwards/s",
         "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": ms_total / K, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args.gpus),
-        "e2e": {"value": job_throughput(args.gpus, K, ms_e2e), "unit": "forwards/s", "ms_per_forward": ms_e2e / K,
+        "config": workload_config(args.gpus, E),
+        "e2e": {"value": job_throughput(args.gpus * E, K, ms_e2e), "unit": "forwards/s", "ms_per_forward": ms_e2e / K / E,
                 "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (images, state, noise)),
                 "d2h_bytes_per_step": host_out.numel() * host_out.element_size()},
-        "gpu_launches": int(per_forward * K), "gpu_launches_per_forward": int(per_forward),
+        "gpu_launches": int(per_forward * K * E), "gpu_launches_per_forward": int(per_forward),
         "clocks": clock_summary,
         "published_h100_ms_per_forward": H100_PUBLISHED_MS,
     }
-    if args.gpus == 1:
+    if args.gpus == 1 and E == 1:
         # the published figure is ms/forward on one H100; express it in this line's unit
         line["vs_baseline"] = line["value"] / (1000.0 / H100_PUBLISHED_MS)
 
-    if rank == 0 and args.gpus == 1:
+    if rank == 0 and args.gpus == 1 and E == 1:
         w, b = engine.weights, engine.buffers
         with wrappers.use_pool(engine.pool):
             t_gate = time_isolated_op(lambda i: engine.ops.encoder_norm_gated_ffn(
@@ -437,6 +443,8 @@ def main():
     p.add_argument("--steps", type=int, default=30)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    p.add_argument("--episodes", type=int, default=1,
+                   help="independent episodes per GPU inside the graph (throughput profile; the default 1 is the headline workload)")
     p.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle leg (faster iteration)")
     p.add_argument("--sweep", action="store_true", help="isolated GEMM roofline sweep instead of the forward pass")
     p.add_argument("--sweep-only", choices=list(SWEEP), default=None)

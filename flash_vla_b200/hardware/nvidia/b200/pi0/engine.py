@@ -5,6 +5,12 @@ times to populate the scratch pool, freezes the pool and captures vision + prefi
 all decoder steps into a single graph on a side stream. `forward` copies the three inputs into
 their static buffers and replays. Public surface and life cycle follow the reference engine
 (`.../h100/pi0/engine.py:26-86`).
+
+`episodes=E > 1` is the throughput profile: E independent episodes share the weights, each has its own
+static buffers and scratch pool, and the captured graph forks into E streams, one pass each, and joins
+again. The decoder's kernels are latency-bound at batch 1 and leave SMs idle; running episodes side by
+side fills them. Every episode runs exactly the kernels of the single-episode engine, so its result is
+bit-identical to that engine's.
 """
 from __future__ import annotations
 
@@ -29,12 +35,20 @@ class Pi0Inference:
 
     def __init__(self, checkpoint, num_views: int, chunk_size: int, steps: int = 10,
                  layers: int = 18, fused: bool = True, device: str = "cuda", plan=None,
-                 capture: bool = True):
+                 capture: bool = True, episodes: int = 1):
         if not torch.cuda.is_available():
             raise RuntimeError("Pi0Inference needs a CUDA device; the B200 target has no CPU path")
+        if episodes < 1:
+            raise ValueError("episodes must be >= 1")
         self.num_views, self.chunk_size = num_views, chunk_size
         self.steps, self.layers, self.fused = steps, layers, fused
+        self.episodes = episodes
         self.ops = op_table(fused, plan=plan)
+        if episodes > 1:
+            # the weight prefetch hint owns one side stream per device; concurrent episodes would contend for it
+            for name in ("prefetch_l2", "join_prefetch"):
+                if hasattr(self.ops, name):
+                    delattr(self.ops, name)
         self.prompt_len = int(checkpoint["language_embeds"].shape[0])
 
         expected = weight_shapes(self.prompt_len)
@@ -47,32 +61,55 @@ class Pi0Inference:
             if tuple(value.shape) != tuple(shape):
                 raise ValueError(f"checkpoint[{name!r}] has shape {tuple(value.shape)}, expected {shape}")
             self.weights[name] = value.to(device=device, dtype=torch.bfloat16).contiguous()
-        self.buffers, self.encoder_seq_len = allocate_static_buffers(
-            num_views, chunk_size, self.prompt_len, device)
-
-        wrappers.register_bf16_shadow(self.buffers["decoder_x"], self.buffers["decoder_x_bf16"])
-        self.pool = ScratchPool()
+        self.episode_buffers, self.pools = [], []
+        for _ in range(episodes):
+            buffers, self.encoder_seq_len = allocate_static_buffers(num_views, chunk_size, self.prompt_len, device)
+            wrappers.register_bf16_shadow(buffers["decoder_x"], buffers["decoder_x_bf16"])
+            self.episode_buffers.append(buffers)
+            self.pools.append(ScratchPool())
+        if episodes > 1:
+            # inputs and the result of all episodes live in three batched tensors, so `forward` stays three copies
+            for name in ("observation_images_normalized", "observation_state_normalized", "diffusion_noise"):
+                batched = torch.zeros((episodes,) + tuple(self.episode_buffers[0][name].shape), dtype=torch.bfloat16, device=device)
+                for e, b in enumerate(self.episode_buffers):
+                    b[name] = batched[e]
+                setattr(self, "_batched_" + name, batched)
+            self.streams = [torch.cuda.Stream(device=device) for _ in range(episodes)]
+        self.buffers, self.pool = self.episode_buffers[0], self.pools[0]
         self.graph = None
         if capture:
             self._capture()
 
-    def _run(self):
-        """One full pass, in place on the static buffers."""
-        b = self.buffers
+    def _run_episode(self, e: int):
+        b = self.episode_buffers[e]
         if self.prompt_len:
             b["encoder_x"][self.num_views * 256:].copy_(self.weights["language_embeds"])
-        with wrappers.use_pool(self.pool):
+        with wrappers.use_pool(self.pools[e]):
             pipeline.vision_encoder(self.ops, self.weights, b, self.num_views)
             pipeline.transformer_encoder(self.ops, self.weights, b, self.encoder_seq_len)
             pipeline.transformer_decoder(self.ops, self.weights, b, self.encoder_seq_len,
                                          steps=self.steps, layers=self.layers)
+
+    def _run(self):
+        """One full pass per episode, in place on the static buffers; episodes run on streams of their own."""
+        if self.episodes == 1:
+            self._run_episode(0)
+            return
+        current = torch.cuda.current_stream()
+        for e, stream in enumerate(self.streams):
+            stream.wait_stream(current)
+            with torch.cuda.stream(stream):
+                self._run_episode(e)
+        for stream in self.streams:
+            current.wait_stream(stream)
 
     def _capture(self):
         """Warm up (which fills the scratch pool), freeze the pool, capture one pass."""
         for _ in range(3):
             self._run()
         torch.cuda.synchronize()
-        self.pool.freeze()
+        for pool in self.pools:
+            pool.freeze()
         self.graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -104,7 +141,8 @@ class Pi0Inference:
 
     def __del__(self):
         try:
-            wrappers.unregister_bf16_shadow(self.buffers["decoder_x"])
+            for b in self.episode_buffers:
+                wrappers.unregister_bf16_shadow(b["decoder_x"])
         except Exception:
             pass
 
@@ -112,14 +150,20 @@ class Pi0Inference:
         """Copy the inputs into their static buffers, replay, return the denoised chunk.
 
         The result is the static `diffusion_noise` buffer itself, not a copy: clone it before
-        the next call if it must survive.
+        the next call if it must survive. With `episodes=E > 1` the three inputs carry a leading
+        dimension E and the result is `(E, chunk, 32)`.
         """
-        b = self.buffers
-        b["observation_images_normalized"].copy_(images, non_blocking=True)
-        b["observation_state_normalized"].copy_(state, non_blocking=True)
-        b["diffusion_noise"].copy_(noise, non_blocking=True)
+        if self.episodes == 1:
+            b = self.buffers
+            dst = (b["observation_images_normalized"], b["observation_state_normalized"], b["diffusion_noise"])
+        else:
+            dst = (self._batched_observation_images_normalized, self._batched_observation_state_normalized,
+                   self._batched_diffusion_noise)
+        dst[0].copy_(images, non_blocking=True)
+        dst[1].copy_(state, non_blocking=True)
+        dst[2].copy_(noise, non_blocking=True)
         if self.graph is None:
             self._run()
         else:
             self.graph.replay()
-        return b["diffusion_noise"]
+        return dst[2]

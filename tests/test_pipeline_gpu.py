@@ -134,3 +134,27 @@ def test_frozen_pool_refuses_new_scratch(full_checkpoint):
     pool.get("a", (4,), torch.float32, "cuda")
     with pytest.raises(RuntimeError):
         pool.get("a", (8,), torch.float32, "cuda")
+
+
+def test_concurrent_episodes_match_the_single_episode_engine(full_checkpoint):
+    """The throughput profile (E episodes on concurrent streams inside one graph, shared weights, own buffers)
+    runs the same kernels per episode as the single-episode engine: results must be bit-identical."""
+    from flash_vla_b200 import Pi0Inference
+
+    E = 3
+    sets = [bench_inputs(seed=e) for e in range(E)]
+    single = Pi0Inference(full_checkpoint, num_views=3, chunk_size=50)
+    want = [single.forward(*s).clone() for s in sets]
+    del single
+    torch.cuda.empty_cache()
+    multi = Pi0Inference(full_checkpoint, num_views=3, chunk_size=50, episodes=E)
+    batched = [torch.stack([s[i] for s in sets]) for i in range(3)]
+    got = multi.forward(*batched).clone()
+    got2 = multi.forward(*batched).clone()
+    torch.cuda.synchronize()
+    assert got.shape == (E, 50, 32)
+    assert torch.equal(got, got2), "two replays of the same inputs must be bit-identical"
+    for e in range(E):
+        assert torch.equal(got[e], want[e]), f"episode {e} differs from the single-episode engine"
+    with pytest.raises(ValueError):
+        Pi0Inference(full_checkpoint, num_views=3, chunk_size=50, episodes=0, capture=False)
