@@ -35,7 +35,7 @@ class Pi0Inference:
 
     def __init__(self, checkpoint, num_views: int, chunk_size: int, steps: int = 10,
                  layers: int = 18, fused: bool = True, device: str = "cuda", plan=None,
-                 capture: bool = True, episodes: int = 1):
+                 capture: bool = True, episodes: int = 1, overlap: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("Pi0Inference needs a CUDA device; the B200 target has no CPU path")
         if episodes < 1:
@@ -43,6 +43,9 @@ class Pi0Inference:
         self.num_views, self.chunk_size = num_views, chunk_size
         self.steps, self.layers, self.fused = steps, layers, fused
         self.episodes = episodes
+        # overlap: the decoder's first Euler step runs on a second stream, one layer behind the prefix encoder
+        # (decoder layer L only needs the prefix K/V of encoder layer L); same kernels, same results
+        self.overlap = bool(overlap) and steps >= 1
         self.ops = op_table(fused, plan=plan)
         if episodes > 1:
             # the weight prefetch hint owns one side stream per device; concurrent episodes would contend for it
@@ -75,6 +78,7 @@ class Pi0Inference:
                     b[name] = batched[e]
                 setattr(self, "_batched_" + name, batched)
             self.streams = [torch.cuda.Stream(device=device) for _ in range(episodes)]
+        self.decoder_streams = [torch.cuda.Stream(device=device) for _ in range(episodes)] if self.overlap else []
         self.buffers, self.pool = self.episode_buffers[0], self.pools[0]
         self.graph = None
         if capture:
@@ -86,9 +90,25 @@ class Pi0Inference:
             b["encoder_x"][self.num_views * 256:].copy_(self.weights["language_embeds"])
         with wrappers.use_pool(self.pools[e]):
             pipeline.vision_encoder(self.ops, self.weights, b, self.num_views)
-            pipeline.transformer_encoder(self.ops, self.weights, b, self.encoder_seq_len)
+            if not self.overlap:
+                pipeline.transformer_encoder(self.ops, self.weights, b, self.encoder_seq_len)
+                pipeline.transformer_decoder(self.ops, self.weights, b, self.encoder_seq_len,
+                                             steps=self.steps, layers=self.layers)
+                return
+            main, side = torch.cuda.current_stream(), self.decoder_streams[e]
+            kv_ready = [torch.cuda.Event() for _ in range(pipeline.ENCODER_LAYERS)]
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                pipeline.decoder_prologue(self.ops, self.weights, b)
+            pipeline.transformer_encoder(self.ops, self.weights, b, self.encoder_seq_len,
+                                         after_qkv=lambda layer: kv_ready[layer].record(main))
+            with torch.cuda.stream(side):
+                pipeline.decoder_step(self.ops, self.weights, b, self.encoder_seq_len, 0, self.layers,
+                                      noise=b.get("diffusion_noise_f32"), prefetch_next_step=self.steps > 1,
+                                      before_layer=lambda layer: side.wait_event(kv_ready[layer]))
+            main.wait_stream(side)
             pipeline.transformer_decoder(self.ops, self.weights, b, self.encoder_seq_len,
-                                         steps=self.steps, layers=self.layers)
+                                         steps=self.steps, layers=self.layers, first_step=1)
 
     def _run(self):
         """One full pass per episode, in place on the static buffers; episodes run on streams of their own."""

@@ -39,10 +39,12 @@ def vision_encoder(ops, weights, buffers, num_views):
                                      w["vision_ffn_down_b"][layer], x, x)
 
 
-def transformer_encoder(ops, weights, buffers, encoder_seq_len):
+def transformer_encoder(ops, weights, buffers, encoder_seq_len, after_qkv=None):
     """Project vision tokens to encoder width and fill the prefix KV cache of all 18 layers.
 
-    The last layer only needs its K and V, so it stops after the QKV projection.
+    The last layer only needs its K and V, so it stops after the QKV projection. `after_qkv(layer)`,
+    if given, is called once layer `layer`'s prefix K/V have been enqueued: from then on a decoder
+    layer of the same index has everything it needs from the encoder.
     """
     w, b, S = weights, buffers, encoder_seq_len
     x = b["encoder_x"]
@@ -53,6 +55,8 @@ def transformer_encoder(ops, weights, buffers, encoder_seq_len):
         k_prefix, v_prefix = b["encoder_K"][layer, :S], b["encoder_V"][layer, :S]
         ops.encoder_norm_qkv_rope(x, w["encoder_attn_qkv_w"][layer], b["encoder_rope_weights"],
                                   b["encoder_Q"], k_prefix, v_prefix, b["encoder_x_norm"])
+        if after_qkv is not None:
+            after_qkv(layer)
         if layer == ENCODER_LAYERS - 1:
             return
         ops.encoder_attention(b["encoder_Q"], k_prefix, v_prefix, HEAD_DIM ** -0.5, b["encoder_attn"])
@@ -73,8 +77,9 @@ def _prefetch_decoder_layer(ops, weights, buffers, layer):
 
 
 def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LAYERS, noise=None,
-                 prefetch_next_step=False):
-    """One flow-matching Euler step over `noise` (default: the plan's master copy)."""
+                 prefetch_next_step=False, before_layer=None):
+    """One flow-matching Euler step over `noise` (default: the plan's master copy). `before_layer(layer)`,
+    if given, is called before layer `layer` is enqueued (the place to wait for that layer's prefix K/V)."""
     w, b, S = weights, buffers, encoder_seq_len
     if noise is None:
         noise = b["diffusion_noise_f32"] if "diffusion_noise_f32" in b else b["diffusion_noise"]
@@ -89,6 +94,8 @@ def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LA
     q = b["decoder_q_buf"]
     for layer in range(layers):
         k_cache, v_cache = b["encoder_K"][layer], b["encoder_V"][layer]
+        if before_layer is not None:
+            before_layer(layer)
         if layer + 1 < layers:
             _prefetch_decoder_layer(ops, w, b, layer + 1)
         elif prefetch_next_step:
@@ -106,9 +113,9 @@ def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LA
         ops.join_prefetch()                  # the side stream rejoins before the caller goes on
 
 
-def transformer_decoder(ops, weights, buffers, encoder_seq_len, steps=DIFFUSION_STEPS,
-                        layers=ENCODER_LAYERS):
-    """Denoise the action chunk in `diffusion_noise` over `steps` Euler steps."""
+def decoder_prologue(ops, weights, buffers):
+    """What the decoder needs before its first step and that does not depend on the encoder: the state
+    token's projection, the fp32 master copy of the noise, the first layer's weights on their way to L2."""
     b = buffers
     ops.decoder_state_proj(b["observation_state_normalized"], weights["decoder_state_in_proj_w"],
                            weights["decoder_state_in_proj_b"], b["decoder_state_buf"])
@@ -116,11 +123,27 @@ def transformer_decoder(ops, weights, buffers, encoder_seq_len, steps=DIFFUSION_
     if master is not None:
         master.copy_(b["diffusion_noise"])
     _prefetch_decoder_layer(ops, weights, b, 0)
-    for step in range(steps):
+
+
+def decoder_epilogue(buffers):
+    """Refresh the bf16 action chunk from its fp32 master."""
+    master = buffers.get("diffusion_noise_f32")
+    if master is not None:
+        buffers["diffusion_noise"].copy_(master)
+
+
+def transformer_decoder(ops, weights, buffers, encoder_seq_len, steps=DIFFUSION_STEPS,
+                        layers=ENCODER_LAYERS, first_step=0):
+    """Denoise the action chunk in `diffusion_noise` over `steps` Euler steps. `first_step > 0` resumes
+    after steps that were run separately (prologue included), see `Pi0Inference`."""
+    b = buffers
+    master = b.get("diffusion_noise_f32")
+    if first_step == 0:
+        decoder_prologue(ops, weights, b)
+    for step in range(first_step, steps):
         decoder_step(ops, weights, b, encoder_seq_len, step, layers, noise=master,
                      prefetch_next_step=step + 1 < steps)
-    if master is not None:
-        b["diffusion_noise"].copy_(master)
+    decoder_epilogue(b)
 
 
 def num_vision_tokens(num_views: int) -> int:
