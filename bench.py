@@ -19,7 +19,9 @@ Reported:
                cold); roofline_decoder is the same for the decoder gated FFN (HBM-bound).
   cpu_baseline the CPU fp32 oracle (a port: the reference has no CPU path) on this host's cores.
 
-`--impl reference` times that CPU oracle alone, as the reference arm.
+`--impl reference` times that CPU oracle alone, as the reference arm. `--episodes E` switches to the
+throughput profile (E independent episodes per GPU inside the graph; `ms_per_step` is then the time of one
+replay = E forwards); `--sweep` times the FFN GEMMs and the prefix attention alone.
 """
 from __future__ import annotations
 
