@@ -2,7 +2,7 @@
 
 Run once, in a container that has the reference checkout (it cannot travel to the GPU box):
 
-    TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py [/path/to/reference]
+    TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py /path/to/reference
 
 What is pinned, and against what:
   * rope.pt            - the reference's own `rope_table` (buffers.py:15-23) for the three
@@ -34,7 +34,9 @@ from pathlib import Path
 os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parents[1]
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden.py /path/to/reference (the flash-vla checkout)")
+REF = Path(sys.argv[1])
 sys.path.insert(0, str(REF / "src"))
 sys.path.insert(0, str(ROOT))
 
