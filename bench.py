@@ -369,6 +369,7 @@ SWEEP = {   # name: (M, K, N, gated, residual, layers cycled)
     "enc_gate": (768, 2048, 16384, True, False, 6),
     "enc_down": (768, 16384, 2048, False, True, 6),
     "enc_attn": (768 * 8, 256, 768, False, False, 6),     # prefix attention: flat queries, head dim, keys
+    "dec_attn": (51 * 8, 256, 819, False, False, 18),     # decoder attention: flat queries, head dim, keys (768 prefix + 51)
 }
 
 
@@ -394,6 +395,18 @@ def run_sweep(args):
                 kv = [torch.randn(2, N, K, device="cuda", generator=g).to(bf16) for _ in range(layers)]
                 o = torch.zeros(M, K, device="cuda", dtype=bf16)
                 ms = time_isolated_op(lambda i: ops.encoder_attention(q[i], kv[i][0], kv[i][1], K ** -0.5, o), layers, args.sweep_reps)
+                flops, nbytes = 4.0 * M * N * K, 2 * (2 * M * K + 2 * N * K)
+                rows[name] = {"queries": M, "keys": N, "head_dim": K, "ms_per_launch": ms, "tflops": flops / ms / 1e9,
+                              "gbs": nbytes / ms / 1e6, "algorithmic_bytes": nbytes, "flops": flops,
+                              "frac_of_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                              "frac_of_bf16": flops / ms / 1e9 / peaks["bf16_tflops"]}
+                continue
+            if name == "dec_attn":
+                q = torch.randn(M, K, device="cuda", generator=g).to(bf16)
+                kv = [(torch.randn(2, N, K, device="cuda", generator=g) * 0.1).to(bf16) for _ in range(layers)]
+                o = torch.zeros(M, K, device="cuda", dtype=bf16)
+                scores = torch.zeros(M, N, device="cuda", dtype=bf16)
+                ms = time_isolated_op(lambda i: ops.decoder_attention(q, kv[i][0], kv[i][1], scores, o, N - 51), layers, args.sweep_reps)
                 flops, nbytes = 4.0 * M * N * K, 2 * (2 * M * K + 2 * N * K)
                 rows[name] = {"queries": M, "keys": N, "head_dim": K, "ms_per_launch": ms, "tflops": flops / ms / 1e9,
                               "gbs": nbytes / ms / 1e6, "algorithmic_bytes": nbytes, "flops": flops,
