@@ -14,10 +14,17 @@ Reported:
   e2e          the same through the public API `Pi0Inference.forward` with pinned HOST inputs
                (host->device copies inside the timed region) and a device->host read of the
                action chunk every step.
-  roofline     the dominant kernel (encoder gated FFN, tensor-bound) timed alone over the 17
-               layers' distinct weights (134 MB per launch, larger than L2, so every launch is
-               cold); roofline_decoder is the same for the decoder gated FFN (HBM-bound).
+  roofline     the dominant kernel class by share of the forward, the decoder's weight-streaming cluster
+               GEMM (about 40 % of the step), at its largest call site: the gated FFN, 16.8 MB of weights
+               per launch, HBM-bound. Timed alone inside a CUDA graph that cycles the 18 layers' distinct
+               weights, so every launch reads its weights cold. roofline_encoder is the same for the
+               largest single launch, the prefix encoder's gated FFN (tensor-bound).
+  kernels      the same cold-in-graph timing for every GEMM of the isolated sweep configuration (decoder
+               gate/up and down, encoder gate/up and down), the other two decoder GEMMs and the two
+               attention kernels, each with its fraction of the measured peak.
+  throughput_profile  forwards/s of the 4-episodes-per-GPU profile, measured in the same run.
   cpu_baseline the CPU fp32 oracle (a port: the reference has no CPU path) on this host's cores.
+  env          GPU, driver, CUDA, torch, CPU model and core count of the run.
 
 `--impl reference` times that CPU oracle alone, as the reference arm. `--episodes E` switches to the
 throughput profile (E independent episodes per GPU inside the graph; `ms_per_step` is then the time of one
@@ -41,13 +48,13 @@ sys.path.insert(0, str(ROOT))
 import torch  # noqa: E402
 
 H100_PUBLISHED_MS = 15.18            # reference README.md:105-108, H100 SXM5, same shape
-ENC_GATE_FLOPS = 2 * 768 * 2048 * 2 * 16384          # 103.08 GFLOP per launch
-DEC_GATE_BYTES = 2 * 1024 * 4096 * 2 + 51 * 1024 * 2 + 51 * 4096 * 2   # weights + x + out, bytes per launch
 FORWARD_FLOPS = 4.006e12
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised in
-# profiles/tc5x2_gemm_encoder_gate.md and profiles/skinny_gemm_decoder_gate.md
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) is NOT measured by this program:
+# these are the figures of one ncu capture of each kernel, typed in here. The line says so
+# (`traffic_source`); if a kernel changes, re-capture it.
 ENC_GATE_DRAM_BYTES = 152.5e6
 DEC_GATE_DRAM_BYTES = 17.03e6
+TRAFFIC_SOURCE = "constant from an earlier ncu capture of this kernel (dram__bytes_read.sum + dram__bytes_write.sum, one launch); not measured by this run"
 
 
 def measured_peaks():
@@ -153,6 +160,35 @@ def cpu_oracle_weights(vision_layers: int, encoder_layers: int):
     return w
 
 
+def env_block():
+    """Where the numbers were taken: GPU, driver, CUDA, torch, host CPU (the reference stamps its runs the
+    same way, benchmarks/metrics.py:122-132)."""
+    env = {"torch": torch.__version__, "cuda_runtime": torch.version.cuda, "cpu_cores": os.cpu_count()}
+    try:
+        for line in Path("/proc/cpuinfo").read_text().splitlines():
+            if line.startswith("model name"):
+                env["cpu_model"] = line.split(":", 1)[1].strip()
+                break
+    except OSError:
+        pass
+    if torch.cuda.is_available():
+        props = torch.cuda.get_device_properties(torch.cuda.current_device())
+        env.update({"gpu": props.name, "sms": props.multi_processor_count, "hbm_gib": round(props.total_memory / 2 ** 30, 1),
+                    "compute_capability": f"{props.major}.{props.minor}"})
+        try:
+            out = subprocess.run(["nvidia-smi", "--query-gpu=driver_version", "--format=csv,noheader"],
+                                 capture_output=True, text=True, timeout=10).stdout.strip().splitlines()
+            env["driver"] = out[0] if out else None
+        except (OSError, subprocess.SubprocessError):
+            pass
+    try:
+        out = subprocess.run(["/usr/local/cuda/bin/nvcc", "--version"], capture_output=True, text=True, timeout=10).stdout
+        env["nvcc"] = next((l.split("release")[1].split(",")[0].strip() for l in out.splitlines() if "release" in l), None)
+    except (OSError, subprocess.SubprocessError):
+        pass
+    return env
+
+
 def run_oracle_sample(fraction_inv: int, weights, inputs):
     """One bounded sample: 27/f vision layers, 18/f encoder layers, ceil(10/f) decoder steps."""
     from oracle import pi0_ref as O
@@ -213,6 +249,7 @@ def run_reference(args):
         "cpu_baseline": {"value": value, "unit": "forwards/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "forwards/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference has no CPU implementation; this is the CPU fp32 restatement (oracle/pi0_ref.py)",
+        "env": env_block(),
     }
     print(json.dumps(line))
 
@@ -251,6 +288,38 @@ def time_isolated_op(fn, layers: int, reps: int):
     end.record()
     torch.cuda.synchronize()
     return start.elapsed_time(end) / (reps * layers)
+
+
+def measure_throughput_profile(weights, rank, world, n_gpus, K, W, episodes=4):
+    """Forwards/s with `episodes` independent episodes per GPU inside one captured pass (the throughput
+    configuration: same shapes, one replica per GPU, no inter-GPU communication)."""
+    from flash_vla_b200 import Pi0Inference
+    from flash_vla_b200.synthetic import bench_inputs
+    ck = dict(weights)
+    engine = Pi0Inference(ck, num_views=3, chunk_size=50, episodes=episodes)
+    sets = [bench_inputs(seed=rank * episodes + e) for e in range(episodes)]
+    images, state, noise = [torch.stack([s[i] for s in sets]).to(torch.bfloat16).cuda() for i in range(3)]
+    stream = torch.cuda.current_stream()
+    engine.forward(images, state, noise)
+    for _ in range(W):
+        engine.graph.replay()
+    barrier(world)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for _ in range(K):
+        engine.graph.replay()
+    end.record(stream)
+    torch.cuda.synchronize()
+    ms = max_over_ranks(start.elapsed_time(end), world)
+    barrier(world)
+    del engine
+    torch.cuda.empty_cache()
+    return {"episodes_per_gpu": episodes, "value": job_throughput(n_gpus * episodes, K, ms), "unit": "forwards/s",
+            "ms_per_replay": ms / K, "form": engine_form(episodes)}
+
+
+def engine_form(episodes):
+    return f"{episodes} independent single-episode passes on {episodes} concurrent streams inside one captured graph, shared weights"
 
 
 def run_ours(args):
@@ -331,31 +400,34 @@ def run_ours(args):
         # the published figure is ms/forward on one H100; express it in this line's unit
         line["vs_baseline"] = line["value"] / (1000.0 / H100_PUBLISHED_MS)
 
+    # the 4-episodes-per-GPU throughput profile, in the same run and at every N
+    if E == 1 and not args.no_throughput_profile:
+        line["throughput_profile"] = measure_throughput_profile(engine.weights, rank, world, args.gpus, K, W)
+    del engine
+    torch.cuda.empty_cache()
+
     if rank == 0 and args.gpus == 1 and E == 1:
-        w, b = engine.weights, engine.buffers
-        with wrappers.use_pool(engine.pool):
-            t_gate = time_isolated_op(lambda i: engine.ops.encoder_norm_gated_ffn(
-                b["encoder_x"], w["encoder_ffn_gate_w"][i], w["encoder_ffn_up_w"][i], b["encoder_hidden"],
-                b["encoder_x_norm"]), 17, 3)
-            t_dec = time_isolated_op(lambda i: engine.ops.decoder_norm_gated_ffn(
-                b["decoder_x"], w["decoder_ffn_gate_w"][i], w["decoder_ffn_up_w"][i], b["decoder_hidden"],
-                b["decoder_norm_factor_buf"]), 18, 20)
-        tf = ENC_GATE_FLOPS / (t_gate * 1e-3) / 1e12
-        line["roofline"] = {"kernel": "encoder_norm_gated_ffn (RMS norm kernel + two-SM tcgen05 gate/up GEMM with GeGLU epilogue, M=768 K=2048 N=2x16384)",
-                            "bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                            "frac": tf / peaks["bf16_tflops"], "traffic": ENC_GATE_DRAM_BYTES, "traffic_unit": "bytes per launch",
-                            "peak_source": peaks["source"] + " burst",
-                            "ms_per_launch": t_gate}
-        gbs = DEC_GATE_BYTES / (t_dec * 1e-3) / 1e9
-        line["roofline_decoder"] = {"kernel": "decoder_norm_gated_ffn (M=51 K=1024 N=2x4096, 16.8 MB of weights per launch)",
-                                    "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                    "frac": gbs / peaks["hbm_gbs"], "traffic": DEC_GATE_DRAM_BYTES, "traffic_unit": "bytes per launch",
-                                    "peak_source": peaks["source"],
-                                    "ms_per_launch": t_dec,
-                                    "note": "18 layers' weights cycled inside one CUDA graph"}
+        rows = sweep_rows(list(SWEEP), layers_cap=0, reps=10)
+        line["kernels"] = rows
+        dg, eg = rows["dec_gate"], rows["enc_gate"]
+        line["roofline"] = {"kernel": "skinny_gemm_kernel (decoder cluster GEMM) at decoder_norm_gated_ffn: M=51 K=1024 N=2x4096, "
+                                      "16.8 MB of weights per launch; this kernel class is about 40 % of the forward",
+                            "bound": "hbm", "achieved": dg["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": dg["gbs"] / peaks["hbm_gbs"], "traffic": DEC_GATE_DRAM_BYTES,
+                            "traffic_unit": "bytes per launch", "traffic_source": TRAFFIC_SOURCE,
+                            "peak_source": peaks["source"], "ms_per_launch": dg["ms_per_launch"],
+                            "algorithmic_bytes": dg["algorithmic_bytes"],
+                            "note": "18 layers' weights cycled inside one CUDA graph, CUDA events around the replays"}
+        line["roofline_encoder"] = {"kernel": "encoder_norm_gated_ffn (RMS norm kernel + two-SM tcgen05 gate/up GEMM with GeGLU epilogue, "
+                                              "M=768 K=2048 N=2x16384); the largest single launch, about 13 % of the forward",
+                                    "bound": "tensor", "achieved": eg["tflops"], "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                    "frac": eg["tflops"] / peaks["bf16_tflops"], "traffic": ENC_GATE_DRAM_BYTES,
+                                    "traffic_unit": "bytes per launch", "traffic_source": TRAFFIC_SOURCE,
+                                    "peak_source": peaks["source"] + " burst", "ms_per_launch": eg["ms_per_launch"]}
         if not args.no_cpu_baseline:
-            value, _, cores, sample = time_cpu_oracle(1, 0, budget_s=30.0)
+            value, _, cores, sample = time_cpu_oracle(3, 1, budget_s=30.0)
             line["cpu_baseline"] = {"value": value, "unit": "forwards/s", "cores": cores, "kind": "port", "sample": sample}
+    line["env"] = env_block()
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -364,6 +436,8 @@ def run_ours(args):
 
 
 SWEEP = {   # name: (M, K, N, gated, residual, layers cycled)
+    "dec_qkv": (51, 1024, 2560, False, False, 18),
+    "dec_o": (51, 2048, 1024, False, True, 18),
     "dec_gate": (51, 1024, 4096, True, False, 18),
     "dec_down": (51, 4096, 1024, False, True, 18),
     "enc_gate": (768, 2048, 16384, True, False, 6),
@@ -373,69 +447,83 @@ SWEEP = {   # name: (M, K, N, gated, residual, layers cycled)
 }
 
 
-def run_sweep(args):
-    """Isolated kernel roofline sweep (the four decoder / encoder FFN GEMMs and the prefix attention): bf16 weights ~ N(0, 0.02),
-    activations ~ N(0, 1), fp32 accumulate, distinct weight copies cycled inside one CUDA graph so every
-    launch streams its weights cold. One JSON line with HBM GB/s and TFLOP/s against the measured peaks."""
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py --sweep needs a CUDA device")
+def sweep_rows(names, layers_cap: int, reps: int):
+    """Isolated kernel timings: bf16 weights ~ N(0, 0.02), activations ~ N(0, 1), fp32 accumulate, distinct
+    weight copies cycled inside one CUDA graph so every launch streams its weights cold. Returns
+    {name: {ms_per_launch, tflops, gbs, algorithmic_bytes, flops, frac_of_hbm, frac_of_bf16, ...}}."""
     from flash_vla_b200 import op_table
     from flash_vla_b200.hardware.nvidia.b200.pi0.backends.cuda import wrappers
+    from flash_vla_b200.hardware.nvidia.b200.pi0.buffers import rope_table
     from flash_vla_b200.runtime.cuda import ScratchPool
     ops, peaks, bf16 = op_table(True), measured_peaks(), torch.bfloat16
     g = torch.Generator(device="cuda").manual_seed(0)
     rows = {}
-    names = [args.sweep_only] if args.sweep_only else list(SWEEP)
+
+    def row(ms, flops, nbytes, **shape):
+        return {**shape, "ms_per_launch": ms, "tflops": flops / ms / 1e9, "gbs": nbytes / ms / 1e6,
+                "algorithmic_bytes": nbytes, "flops": flops, "frac_of_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                "frac_of_bf16": flops / ms / 1e9 / peaks["bf16_tflops"]}
+
     with wrappers.use_pool(ScratchPool()):
         for name in names:
             M, K, N, gated, residual, layers = SWEEP[name]
-            layers = min(layers, args.sweep_layers) if args.sweep_layers else layers
-            if name == "enc_attn":
+            layers = min(layers, layers_cap) if layers_cap else layers
+            if name in ("enc_attn", "dec_attn"):
+                scale = 1.0 if name == "enc_attn" else 0.1
                 q = [torch.randn(M, K, device="cuda", generator=g).to(bf16) for _ in range(layers)]
-                kv = [torch.randn(2, N, K, device="cuda", generator=g).to(bf16) for _ in range(layers)]
+                kv = [(torch.randn(2, N, K, device="cuda", generator=g) * scale).to(bf16) for _ in range(layers)]
                 o = torch.zeros(M, K, device="cuda", dtype=bf16)
-                ms = time_isolated_op(lambda i: ops.encoder_attention(q[i], kv[i][0], kv[i][1], K ** -0.5, o), layers, args.sweep_reps)
-                flops, nbytes = 4.0 * M * N * K, 2 * (2 * M * K + 2 * N * K)
-                rows[name] = {"queries": M, "keys": N, "head_dim": K, "ms_per_launch": ms, "tflops": flops / ms / 1e9,
-                              "gbs": nbytes / ms / 1e6, "algorithmic_bytes": nbytes, "flops": flops,
-                              "frac_of_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
-                              "frac_of_bf16": flops / ms / 1e9 / peaks["bf16_tflops"]}
-                continue
-            if name == "dec_attn":
-                q = torch.randn(M, K, device="cuda", generator=g).to(bf16)
-                kv = [(torch.randn(2, N, K, device="cuda", generator=g) * 0.1).to(bf16) for _ in range(layers)]
-                o = torch.zeros(M, K, device="cuda", dtype=bf16)
-                scores = torch.zeros(M, N, device="cuda", dtype=bf16)
-                ms = time_isolated_op(lambda i: ops.decoder_attention(q, kv[i][0], kv[i][1], scores, o, N - 51), layers, args.sweep_reps)
-                flops, nbytes = 4.0 * M * N * K, 2 * (2 * M * K + 2 * N * K)
-                rows[name] = {"queries": M, "keys": N, "head_dim": K, "ms_per_launch": ms, "tflops": flops / ms / 1e9,
-                              "gbs": nbytes / ms / 1e6, "algorithmic_bytes": nbytes, "flops": flops,
-                              "frac_of_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
-                              "frac_of_bf16": flops / ms / 1e9 / peaks["bf16_tflops"]}
+                if name == "enc_attn":
+                    fn = lambda i: ops.encoder_attention(q[i], kv[i][0], kv[i][1], K ** -0.5, o)
+                else:
+                    scores = torch.zeros(M, N, device="cuda", dtype=bf16)
+                    fn = lambda i: ops.decoder_attention(q[i], kv[i][0], kv[i][1], scores, o, N - 51)
+                ms = time_isolated_op(fn, layers, reps)
+                rows[name] = row(ms, 4.0 * M * N * K, 2 * (2 * M * K + 2 * N * K), queries=M, keys=N, head_dim=K)
                 continue
             w = [(torch.randn(K, N, device="cuda", generator=g) * 0.02).to(bf16) for _ in range(layers * (2 if gated else 1))]
             x32 = torch.randn(M, K, device="cuda", generator=g)
-            x = x32 if (name == "dec_gate") else x32.to(bf16)          # the decoder's residual stream is fp32
-            out = torch.zeros(M, N, device="cuda", dtype=torch.float32 if name == "dec_down" else bf16)
+            f32_in = name in ("dec_gate", "dec_qkv")                   # the decoder's residual stream is fp32 ...
+            f32_out = name in ("dec_down", "dec_o")
+            x = x32 if f32_in else x32.to(bf16)
+            if f32_in:                                                 # ... with a bf16 shadow its GEMMs read, as in the engine
+                shadow = torch.zeros(M, K, device="cuda", dtype=bf16)
+                wrappers.register_bf16_shadow(x, shadow)
+            out = torch.zeros(M, N, device="cuda", dtype=torch.float32 if f32_out else bf16)
+            if f32_out:
+                wrappers.register_bf16_shadow(out, torch.zeros(M, N, device="cuda", dtype=bf16))
             xn = torch.zeros(M, K, device="cuda", dtype=bf16)
             if name == "dec_gate":
                 fn = lambda i: ops.decoder_norm_gated_ffn(x, w[2 * i], w[2 * i + 1], out, None)
             elif name == "enc_gate":
                 fn = lambda i: ops.encoder_norm_gated_ffn(x, w[2 * i], w[2 * i + 1], out, xn)
-            elif name == "dec_down":
+            elif name in ("dec_down", "dec_o"):
                 fn = lambda i: ops.decoder_ffn_down_residual(x, w[i], out)
+            elif name == "dec_qkv":
+                rope = rope_table(M, 768, 256, "cuda")
+                Q = torch.zeros(M * 8, 256, device="cuda", dtype=bf16)
+                Kc, Vc = torch.zeros(M, 256, device="cuda", dtype=bf16), torch.zeros(M, 256, device="cuda", dtype=bf16)
+                nf = torch.zeros(M, device="cuda", dtype=bf16)
+                fn = lambda i: ops.decoder_norm_qkv_rope(x, w[i], rope, Q, Kc, Vc, nf)
             else:
                 fn = lambda i: ops.encoder_ffn_down_residual(x, w[i], out)
-            ms = time_isolated_op(fn, layers, args.sweep_reps)
+            ms = time_isolated_op(fn, layers, reps)
             flops = 2.0 * M * K * N * (2 if gated else 1)
-            nbytes = K * N * 2 * (2 if gated else 1) + M * K * x.element_size() + M * N * out.element_size() * (2 if residual else 1)
-            rows[name] = {"M": M, "K": K, "N": N, "ms_per_launch": ms, "tflops": flops / ms / 1e9,
-                          "gbs": nbytes / ms / 1e6, "algorithmic_bytes": nbytes, "flops": flops,
-                          "frac_of_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
-                          "frac_of_bf16": flops / ms / 1e9 / peaks["bf16_tflops"]}
+            # weights once + the activation operand as the kernel reads it (bf16) + the output (read and written for a residual)
+            nbytes = K * N * 2 * (2 if gated else 1) + M * K * 2 + M * N * out.element_size() * (2 if residual else 1)
+            rows[name] = row(ms, flops, nbytes, M=M, K=K, N=N)
             del w
             torch.cuda.empty_cache()
-    print(json.dumps({"metric": "isolated_gemm_roofline", "peaks": peaks, "kernels": rows,
+    return rows
+
+
+def run_sweep(args):
+    """Isolated kernel roofline sweep: one JSON line with HBM GB/s and TFLOP/s against the measured peaks."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --sweep needs a CUDA device")
+    names = [args.sweep_only] if args.sweep_only else list(SWEEP)
+    rows = sweep_rows(names, args.sweep_layers, args.sweep_reps)
+    print(json.dumps({"metric": "isolated_gemm_roofline", "peaks": measured_peaks(), "kernels": rows,
                       "note": "fractions are of the measured copy bandwidth and measured cuBLAS bf16 burst rate"}))
 
 
@@ -461,6 +549,7 @@ def main():
     p.add_argument("--episodes", type=int, default=1,
                    help="independent episodes per GPU inside the graph (throughput profile; the default 1 is the headline workload)")
     p.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle leg (faster iteration)")
+    p.add_argument("--no-throughput-profile", action="store_true", help="skip the 4-episodes-per-GPU measurement")
     p.add_argument("--sweep", action="store_true", help="isolated GEMM roofline sweep instead of the forward pass")
     p.add_argument("--sweep-only", choices=list(SWEEP), default=None)
     p.add_argument("--sweep-layers", type=int, default=0, help="cap on distinct weight copies (small profiler runs)")

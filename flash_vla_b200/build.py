@@ -37,22 +37,30 @@ def source_digest() -> str:
     return h.hexdigest()
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Build the shared library unless an up-to-date one is present. Returns its path."""
-    digest = source_digest()
-    if not force and LIB.exists() and STAMP.exists() and STAMP.read_text().strip() == digest:
-        return LIB
+def build(force: bool = False, verbose: bool = False, debug: bool = False) -> Path:
+    """Build the shared library unless an up-to-date one is present. Returns its path.
+
+    `debug=True` builds a separate development library, libfvla_b200_debug.so, with -DFVLA_DEBUG: its
+    kernels can record %globaltimer stamps into a buffer registered through fvla_debug_set_timestamps.
+    The package never loads that file; the shipped library is built without the flag and contains none
+    of that code."""
+    lib = ROOT / "libfvla_b200_debug.so" if debug else LIB
+    stamp = Path(str(lib) + ".stamp")
+    flags = NVCC_FLAGS + (["-DFVLA_DEBUG"] if debug else [])
+    digest = source_digest() + ("-debug" if debug else "")
+    if not force and lib.exists() and stamp.exists() and stamp.read_text().strip() == digest:
+        return lib
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc, *NVCC_FLAGS, "-o", str(LIB)] + [str(p) for p in sorted(CSRC.glob("*.cu"))]
+    cmd = [nvcc, *flags, "-o", str(lib)] + [str(p) for p in sorted(CSRC.glob("*.cu"))]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or proc.returncode != 0:
         sys.stderr.write(proc.stdout + proc.stderr)
     if proc.returncode != 0:
         raise RuntimeError(f"nvcc failed ({proc.returncode}): {' '.join(cmd)}")
-    (ROOT / "libfvla_b200.ptxas.log").write_text(proc.stdout + proc.stderr)
-    STAMP.write_text(digest)
-    return LIB
+    Path(str(lib).replace(".so", ".ptxas.log")).write_text(proc.stdout + proc.stderr)
+    stamp.write_text(digest)
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose=True))
+    print(build(force="--force" in sys.argv, verbose=True, debug="--debug" in sys.argv))

@@ -259,11 +259,11 @@ template <int HD, int STAGES = 2>
 inline int launch_attention(const AttnArgs& a, dim3 grid, cudaStream_t st) {
     constexpr int smem = (1 + 2 * STAGES) * 64 * (HD * 2 + 16);
     auto kern = attention_kernel<HD, STAGES>;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceFlag configured;
+    if (!configured.get()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
-        configured = true;
+        configured.set();
     }
     cudaError_t e = launch_pdl(kern, grid, dim3(128), smem, st, a);
     if (e != cudaSuccess) { set_error("attention_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
@@ -290,7 +290,7 @@ struct DecAttnArgs {
     int mask_rows, mask_key_le;
     int prefix_keys;            // keys [0, prefix_keys) were not written by the preceding kernel
     int* status;
-    unsigned long long* dbg;    // optional development aid: 8 globaltimer stamps per CTA
+    FVLA_DBG_MEMBER
 };
 
 namespace decattn {
@@ -324,9 +324,8 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_BAR + 16);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    unsigned long long* dbg = p.dbg ? p.dbg + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8 : nullptr;
-    auto stamp = [&](int i) { if (dbg && tid == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); dbg[i] = t; } };
-    stamp(0);
+    FVLA_DBG_CTA(p, blockIdx.y * gridDim.x + blockIdx.x);
+    FVLA_STAMP(0);
     uint32_t rank;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
     const int q0 = blockIdx.x * BQ;
@@ -370,14 +369,14 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    stamp(1);
+    FVLA_STAMP(1);
     load_rows(sQ, p.q, q0, q0, p.nq, BQ);
     load_rows(sK, p.k, key_beg, max(key_beg, pre_end), key_end, 128);
     load_rows(sV, p.v, key_beg, max(key_beg, pre_end), key_end, 128);
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
-    stamp(2);
+    FVLA_STAMP(2);
 
     const int rg = warp & 1, kh = (warp >> 1) & 1, dh = warp >> 2;
     const int row_lo = q0 + rg * 16 + (lane >> 2);
@@ -474,7 +473,7 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
         }
     }
     __syncthreads();                                   // K and V are dead from here on
-    stamp(3);
+    FVLA_STAMP(3);
 
     float* half_o = reinterpret_cast<float*>(smem + OFF_HALF);            // [32][OP]
     float* half_ml = half_o + BQ * OP;                                      // m[32], l[32]
@@ -519,7 +518,7 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
-    stamp(4);
+    FVLA_STAMP(4);
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");     // peers' barriers are initialised
     if (tid == 0) {
         for (int r = 0; r < owners; ++r) {
@@ -541,7 +540,7 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
             if (done) { ok = true; break; }
         }
         if (!ok) *abort_flag = 1;
-        stamp(5);
+        FVLA_STAMP(5);
         const float* red = reinterpret_cast<const float*>(smem + OFF_RED);
         const float* lse_in = reinterpret_cast<const float*>(smem + OFF_LSE_IN);
         const int r4 = tid >> 6, c4 = (tid & 63) * 4;
@@ -567,19 +566,19 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
     }
     // outgoing copies read this CTA's staging area: stay until every owner has everything
     // (execution barrier only; nothing read after it was written by a peer)
-    stamp(6);
+    FVLA_STAMP(6);
     asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
-    stamp(7);
+    FVLA_STAMP(7);
     if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 3);
 }
 
 inline int launch_decoder_attention_cluster(const DecAttnArgs& a, bool pdl, cudaStream_t st) {
     auto kern = decoder_attention_cluster_kernel;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceFlag configured;
+    if (!configured.get()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, decattn::SMEM);
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
-        configured = true;
+        configured.set();
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((a.nq + decattn::BQ - 1) / decattn::BQ, decattn::SPL, 1);

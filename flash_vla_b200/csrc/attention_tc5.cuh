@@ -309,11 +309,11 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
 inline int launch_attention_tc5(const void* Q, const void* K, const void* V, void* out, int nq, int nk, float scale_log2,
                                 int* status, cudaStream_t st) {
     auto kern = attention_tc5_kernel;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceFlag configured;
+    if (!configured.get()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
-        configured = true;
+        configured.set();
     }
     CUtensorMap tmQ, tmK, tmV;
     int rc = tc5::make_map(&tmQ, Q, HD, (uint64_t)nq, HD, 64, BQ);
@@ -521,11 +521,11 @@ vision_attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tm
 // qkv: [views * 256, 3 * heads * 72] bf16; out: [views * 256, heads * 72] bf16.
 inline int launch_vision_attention_tc5(const void* qkv, void* out, int views, int heads, int* status, cudaStream_t st) {
     auto kern = vision_attention_tc5_kernel;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceFlag configured;
+    if (!configured.get()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
-        configured = true;
+        configured.set();
     }
     const uint64_t cols = (uint64_t)3 * heads * HDIM, rows = (uint64_t)views * TOK;
     CUtensorMap tmQ, tmK, tmV;

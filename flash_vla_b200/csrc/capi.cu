@@ -73,7 +73,6 @@ static size_t op_ws_bytes(int M, int N, int K, bool dual) {
         size_t t = tc5::plan_tc5(M, N, K, true).ws_bytes;
         size_t t2 = tc5x2::plan_pair_plain(M, N, K, true).ws_bytes;
         if (t2 > t) t = t2;
-        if (getenv("FVLA_DEBUG_TC5_PLAN")) t = 256 * 64 + (size_t)4 * (M + 127) * (N + 255) * 4;      // room for any forced plan
         if (t > gemm) gemm = t;
     }
     return ws_factor_bytes(M) + ws_xnorm_bytes(M, K) + gemm;
@@ -114,19 +113,19 @@ static bool tc5_enabled() {
     return enabled == 1;
 }
 
-// FVLA_DEBUG_TIMESTAMPS=<device address, decimal> makes the skinny GEMM record per-CTA
-// globaltimer stamps there (development aid; unset in normal use).
-static unsigned long long* debug_timestamps() {
-    const char* v = getenv("FVLA_DEBUG_TIMESTAMPS");
-    if (!v) return nullptr;
-    // FVLA_DEBUG_TIMESTAMPS_SLOTS=n gives successive launches their own 2048-entry slot (n slots, cyclic)
-    static int slots = -1, next = 0;
-    if (slots < 0) { const char* s = getenv("FVLA_DEBUG_TIMESTAMPS_SLOTS"); slots = s ? atoi(s) : 1; if (slots < 1) slots = 1; }
-    unsigned long long* base = reinterpret_cast<unsigned long long*>(strtoull(v, nullptr, 10));
-    unsigned long long* p = base + (size_t)(next % slots) * 2048;
-    ++next;
+#ifdef FVLA_DEBUG
+// Development builds only: the timestamp buffer the instrumented kernels write to. It is registered
+// through fvla_debug_set_timestamps (below), which checks that it is device memory of sufficient size;
+// successive launches take successive 2048-entry slots, cyclically.
+static unsigned long long* g_dbg_base = nullptr;
+static int g_dbg_slots = 0, g_dbg_next = 0;
+unsigned long long* debug_next_slot() {
+    if (g_dbg_base == nullptr || g_dbg_slots < 1) return nullptr;
+    unsigned long long* p = g_dbg_base + (size_t)(g_dbg_next % g_dbg_slots) * 2048;
+    ++g_dbg_next;
     return p;
 }
+#endif
 
 // GEMM dispatch: tcgen05 for M > 64, the warp-level kernel (with split-K) for the skinny shapes.
 // FVLA_GEMM_PAIR=0 keeps the gated FFN on the one-SM kernel (diagnostic switch).
@@ -201,6 +200,10 @@ int fvla_vision_patch_embed(const void* images, const void* patch_w, const void*
                             const void* pos_emb, void* out, int views, void* ws, size_t ws_bytes,
                             void* stream) {
     FVLA_REQUIRE(views > 0, "patch_embed: views=%d", views);
+    FVLA_REQUIRE(images != nullptr && patch_w != nullptr && patch_b != nullptr && pos_emb != nullptr && out != nullptr,
+                 "patch_embed: null pointer");
+    FVLA_REQUIRE(aligned16(images) && aligned16(patch_w) && aligned16(patch_b) && aligned16(pos_emb) && aligned16(out) &&
+                 aligned16(ws), "patch_embed: every pointer must be 16-byte aligned");
     if (ws == nullptr || ws_bytes < fvla_patch_embed_workspace_bytes(views)) {
         set_error("patch_embed: workspace of %zu bytes needed", fvla_patch_embed_workspace_bytes(views));
         return FVLA_ERR_WORKSPACE;
@@ -228,24 +231,31 @@ static __device__ __align__(256) unsigned char g_patch_scratch[FVLA_NOALLOC_MAX_
 
 // In host code `g_patch_scratch` is only a handle for the symbol, not an address the GPU can use;
 // the device address is looked up once per device (with that device current) and cached.
-static void* patch_scratch_device_ptr() {
-    constexpr int kMaxDevices = 64;
-    static void* cached[kMaxDevices] = {};
+static void* patch_scratch_device_ptr(cudaStream_t stream) {
+    static std::atomic<void*> cached[kMaxDevices];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
         set_error("patch_embed_noalloc: cannot identify the current device");
         return nullptr;
     }
-    if (cached[dev] == nullptr) {
-        void* ptr = nullptr;
+    void* ptr = cached[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
+        // The look-up is a runtime call that must not happen inside a stream capture: refuse clearly
+        // instead of letting it invalidate the caller's capture.
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+            set_error("patch_embed_noalloc: the first call on a device looks up the built-in scratch and must be made "
+                      "outside stream capture");
+            return nullptr;
+        }
         cudaError_t e = cudaGetSymbolAddress(&ptr, g_patch_scratch);
         if (e != cudaSuccess || ptr == nullptr) {
             set_error("patch_embed_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
             return nullptr;
         }
-        cached[dev] = ptr;
+        cached[dev].store(ptr, std::memory_order_release);
     }
-    return cached[dev];
+    return ptr;
 }
 
 static int norm_linear(const void* x, const void* nw, const void* nb, const void* w, const void* b,
@@ -267,7 +277,7 @@ int fvla_vision_patch_embed_noalloc(const void* images, const void* patch_w, con
                   views, FVLA_NOALLOC_MAX_VIEWS, sizeof(g_patch_scratch));
         return FVLA_ERR_WORKSPACE;
     }
-    void* scratch = patch_scratch_device_ptr();
+    void* scratch = patch_scratch_device_ptr(S(stream));
     if (scratch == nullptr) return FVLA_ERR_LAUNCH;
     // The patchify kernel rewrites every element it later reads, zero padding included, so the
     // previous call's contents never need clearing.
@@ -376,22 +386,33 @@ int fvla_encoder_attention(const void* Q, const void* K, const void* V, void* ou
     return launch_attention<256>(a, dim3(q_tiles, 1, 1), S(stream));
 }
 
+// bf16 copy of `count` fp32 values (count % 4 == 0), for the kernels that cannot maintain a shadow of the
+// fp32 residual stream in their own epilogue.
+static int refresh_shadow(const void* src, void* dst, size_t count, cudaStream_t st) {
+    FVLA_REQUIRE(count % 4 == 0 && aligned16(src) && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0, "shadow refresh: misaligned");
+    const int blocks = (int)((count / 4 + 255) / 256);
+    f32_to_bf16_kernel<<<blocks, 256, 0, st>>>(static_cast<const float*>(src), Bm(dst), count / 4);
+    return check_launch("f32_to_bf16_kernel");
+}
+
 int fvla_linear_residual(const void* x, const void* weight, void* out, int out_is_f32, void* out_shadow, int M,
                          int N, int K, void* ws, size_t ws_bytes, void* stream) {
     if (tc5_enabled() && skinny::plan_skinny(M, N, K, false).ok && aligned16(x) && aligned16(weight)) {
         skinny::SkinnyArgs sa{};
         sa.x = x; sa.x_f32 = 0; sa.ldx = K; sa.M = M; sa.N = N; sa.K = K;
         sa.out = out; sa.out_f32 = out_is_f32; sa.ldo = N; sa.out_shadow = Bm(out_shadow);
-        sa.status = device_status_ptr(); sa.dbg = debug_timestamps();
+        sa.status = device_status_ptr(); FVLA_DBG_ATTACH(sa);
         return skinny::launch_skinny<skinny::EPI_RESIDUAL>(sa, weight, nullptr, N, S(stream));
     }
-    FVLA_REQUIRE(out_shadow == nullptr, "linear_residual: a bf16 shadow is only maintained for M <= 64 shapes");
+    FVLA_REQUIRE(out_shadow == nullptr || out_is_f32, "linear_residual: a bf16 shadow only makes sense for an fp32 `out`");
     GemmArgs a;
     a.A = B(x); a.lda = K; a.B = B(weight); a.ldb = N; a.C = out; a.ldc = N; a.c_f32 = out_is_f32;
     a.R = out; a.ldr = N; a.M = M; a.N = N; a.K = K;
     void* gws; size_t gn;
     gemm_ws(ws, ws_bytes, M, K, &gws, &gn);
-    return launch_gemm(a, gws, gn, S(stream));
+    int rc = launch_gemm(a, gws, gn, S(stream));
+    if (rc || out_shadow == nullptr) return rc;
+    return refresh_shadow(out, out_shadow, (size_t)M * N, S(stream));      // these kernels do not write the shadow themselves
 }
 
 int fvla_encoder_norm_gated_ffn(const void* x, const void* gate_w, const void* up_w, void* out, void* x_norm,
@@ -430,17 +451,19 @@ int fvla_decoder_small_proj(const void* x, int x_is_f32, const void* weight, con
         skinny::SkinnyArgs sa{};
         sa.x = x; sa.x_f32 = x_is_f32; sa.ldx = K; sa.M = M; sa.N = N; sa.K = K;
         sa.out = out; sa.out_f32 = out_is_f32; sa.ldo = N; sa.bias = B(bias); sa.act = act;
-        sa.out_shadow = Bm(out_shadow); sa.status = device_status_ptr(); sa.dbg = debug_timestamps();
+        sa.out_shadow = Bm(out_shadow); sa.status = device_status_ptr(); FVLA_DBG_ATTACH(sa);
         return skinny::launch_skinny<skinny::EPI_BIAS>(sa, weight, nullptr, N, S(stream));
     }
     FVLA_REQUIRE(!x_is_f32, "small_proj: fp32 input only for K <= 64");
-    FVLA_REQUIRE(out_shadow == nullptr, "small_proj: a bf16 shadow is only maintained by the cluster kernel");
+    FVLA_REQUIRE(out_shadow == nullptr || out_is_f32, "small_proj: a bf16 shadow only makes sense for an fp32 `out`");
     GemmArgs a;
     a.A = B(x); a.lda = K; a.B = B(weight); a.ldb = N; a.C = out; a.ldc = N; a.c_f32 = out_is_f32;
     a.bias = B(bias); a.act = act; a.M = M; a.N = N; a.K = K;
     void* gws; size_t gn;
     gemm_ws(ws, ws_bytes, M, K, &gws, &gn);
-    return launch_gemm(a, gws, gn, S(stream));
+    int rc = launch_gemm(a, gws, gn, S(stream));
+    if (rc || out_shadow == nullptr) return rc;
+    return refresh_shadow(out, out_shadow, (size_t)M * N, S(stream));
 }
 
 // Shared front half of the two decoder norm+GEMM ops: factor (and, for an fp32 residual stream,
@@ -470,7 +493,7 @@ int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* x_shadow
         skinny::SkinnyArgs sa{};
         sa.x = x; sa.x_f32 = x_is_f32; sa.x_shadow = B(x_shadow); sa.ldx = Kdim; sa.M = M; sa.N = N; sa.K = Kdim; sa.need_factor = 1;
         sa.rope = B(rope); sa.q = Bm(Q); sa.k = Bm(K); sa.v = Bm(V); sa.heads = heads; sa.head_dim = head_dim;
-        sa.factor_out = Bm(norm_factor); sa.status = device_status_ptr(); sa.dbg = debug_timestamps();
+        sa.factor_out = Bm(norm_factor); sa.status = device_status_ptr(); FVLA_DBG_ATTACH(sa);
         return skinny::launch_skinny<skinny::EPI_QKV_ROPE>(sa, weight_qkv, nullptr, N, S(stream));
     }
     GemmArgs a;
@@ -498,7 +521,7 @@ int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* ou
         d.nq = queries; d.nk = keys; d.keys_per_split = ((keys + 7) / 8 + 7) / 8 * 8;
         d.scale_log2 = kLog2e / sqrtf((float)head_dim);
         d.mask_rows = heads; d.mask_key_le = encoder_seq_len; d.prefix_keys = encoder_seq_len;
-        d.status = device_status_ptr(); d.dbg = debug_timestamps();
+        d.status = device_status_ptr(); FVLA_DBG_ATTACH(d);
         return launch_decoder_attention_cluster(d, pdl_enabled(), S(stream));
     }
     const int splits = (keys + 127) / 128;
@@ -523,7 +546,7 @@ int fvla_decoder_norm_gated_ffn(const void* x, int x_is_f32, const void* x_shado
     if (tc5_enabled() && skinny::plan_skinny(M, N, K, true).ok && aligned16(x) && aligned16(gate_w) && aligned16(up_w)) {
         skinny::SkinnyArgs sa{};
         sa.x = x; sa.x_f32 = x_is_f32; sa.x_shadow = B(x_shadow); sa.ldx = K; sa.M = M; sa.N = N; sa.K = K; sa.need_factor = 1;
-        sa.out = out; sa.out_f32 = 0; sa.ldo = N; sa.factor_out = Bm(norm_factor); sa.status = device_status_ptr(); sa.dbg = debug_timestamps();
+        sa.out = out; sa.out_f32 = 0; sa.ldo = N; sa.factor_out = Bm(norm_factor); sa.status = device_status_ptr(); FVLA_DBG_ATTACH(sa);
         return skinny::launch_skinny<skinny::EPI_GEGLU>(sa, gate_w, up_w, N, S(stream));
     }
     GemmArgs a;
@@ -563,10 +586,8 @@ int fvla_l2_prefetch(const void* const* ptrs, const size_t* bytes, int count, vo
         a.ptr[i] = static_cast<const uint8_t*>(ptrs[i]);
         a.bytes[i] = bytes[i];
     }
-    int mode = 0, grid = 148, threads = 32; unsigned long long chunk = 8192;
-    if (const char* v = getenv("FVLA_DEBUG_PREFETCH")) sscanf(v, "%d,%d,%d,%llu", &mode, &grid, &threads, &chunk);
-    a.mode = mode; a.chunk = chunk;
-    l2_prefetch_kernel<<<grid, threads, 0, S(stream)>>>(a);
+    a.mode = 0; a.chunk = 8192;
+    l2_prefetch_kernel<<<148, 32, 0, S(stream)>>>(a);
     return check_launch("l2_prefetch_kernel");
 }
 
@@ -577,5 +598,36 @@ int fvla_embed_rows(const void* table, const long long* ids, void* out, int rows
     if (e != cudaSuccess) { set_error("embed_rows_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("embed_rows_kernel");
 }
+
+// ---- failure-detection self-test ---------------------------------------------------------------
+int fvla_selftest_wait_timeout(const void* x, const void* weight, void* out, int M, int N, int K,
+                               unsigned spin_limit, void* stream) {
+    FVLA_REQUIRE(spin_limit > 0 && spin_limit <= (1u << 16), "selftest: spin_limit must be in 1..65536");
+    FVLA_REQUIRE(x != nullptr && weight != nullptr && out != nullptr && aligned16(x) && aligned16(weight) && aligned16(out),
+                 "selftest: null or misaligned pointer");
+    if (!skinny::plan_skinny(M, N, K, false).ok) { set_error("selftest: shape %dx%dx%d is not a cluster-GEMM shape", M, N, K); return FVLA_ERR_UNSUPPORTED; }
+    skinny::SkinnyArgs sa{};
+    sa.x = x; sa.x_f32 = 0; sa.ldx = K; sa.M = M; sa.N = N; sa.K = K;
+    sa.out = out; sa.out_f32 = 0; sa.ldo = N;
+    sa.status = device_status_ptr();
+    sa.spin_limit = spin_limit;
+    sa.expect_extra_bytes = 16;           // the owners' barrier expects 16 bytes that no CTA ever sends
+    return skinny::launch_skinny<skinny::EPI_RESIDUAL>(sa, weight, nullptr, N, S(stream));
+}
+
+#ifdef FVLA_DEBUG
+// Development builds only (not declared in the public header): register the device buffer that the
+// instrumented kernels stamp; `slots` x 2048 entries of 8 bytes. NULL unregisters.
+int fvla_debug_set_timestamps(void* ptr, size_t bytes, int slots) {
+    if (ptr == nullptr) { g_dbg_base = nullptr; g_dbg_slots = 0; return FVLA_OK; }
+    cudaPointerAttributes attr{};
+    FVLA_REQUIRE(cudaPointerGetAttributes(&attr, ptr) == cudaSuccess && attr.type == cudaMemoryTypeDevice,
+                 "debug timestamps: not a device pointer");
+    FVLA_REQUIRE(slots >= 1 && bytes >= (size_t)slots * 2048 * sizeof(unsigned long long) && (reinterpret_cast<uintptr_t>(ptr) & 7u) == 0,
+                 "debug timestamps: buffer of %d x 16384 bytes needed", slots);
+    g_dbg_base = static_cast<unsigned long long*>(ptr); g_dbg_slots = slots; g_dbg_next = 0;
+    return FVLA_OK;
+}
+#endif
 
 }  // extern "C"

@@ -6,6 +6,8 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+#include <atomic>
+
 #include "../../include/flash_vla_b200.h"
 
 namespace fvla {
@@ -86,6 +88,21 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Host-side state that CUDA keeps per device (function attributes, SM count, symbol addresses) is
+// cached per device ordinal, so that one process may drive several GPUs. Entries are atomics: two
+// host threads racing on the first call both do the (idempotent) set-up, neither reads a torn value.
+constexpr int kMaxDevices = 64;
+inline int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    return dev;
+}
+struct PerDeviceFlag {
+    std::atomic<int> done[kMaxDevices];
+    bool get() const { return done[current_device()].load(std::memory_order_acquire) != 0; }
+    void set() { done[current_device()].store(1, std::memory_order_release); }
+};
+
 // FVLA_PDL=0 turns programmatic dependent launch off (diagnostic switch).
 inline bool pdl_enabled() {
     static int on = -1;
@@ -110,6 +127,32 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
+
+// Development aid, compiled only with -DFVLA_DEBUG (the shipped library is built without it and then
+// none of this exists, neither in the kernels' argument structs nor in their code): kernels record
+// %globaltimer stamps, 8 per CTA, into a device buffer that the developer registered through
+// fvla_debug_set_timestamps (validated there; successive launches rotate through its slots).
+#ifdef FVLA_DEBUG
+unsigned long long* debug_next_slot();
+#define FVLA_DBG_MEMBER unsigned long long* dbg;
+#define FVLA_DBG_ATTACH(args) (args).dbg = ::fvla::debug_next_slot()
+#define FVLA_DBG_CTA(args, cta) unsigned long long* fvla_dbg = (args).dbg ? (args).dbg + (size_t)(cta) * 8 : nullptr
+#define FVLA_STAMP_ANY(i)                                                          \
+    do {                                                                           \
+        if (fvla_dbg) {                                                            \
+            unsigned long long t_;                                                 \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                 \
+            fvla_dbg[i] = t_;                                                      \
+        }                                                                          \
+    } while (0)
+#define FVLA_STAMP(i) do { if (threadIdx.x == 0) FVLA_STAMP_ANY(i); } while (0)
+#else
+#define FVLA_DBG_MEMBER
+#define FVLA_DBG_ATTACH(args) ((void)0)
+#define FVLA_DBG_CTA(args, cta) ((void)0)
+#define FVLA_STAMP_ANY(i) ((void)0)
+#define FVLA_STAMP(i) ((void)0)
+#endif
 
 // Host-side: record the message of the last failing call on this thread.
 void set_error(const char* fmt, ...);

@@ -288,7 +288,6 @@ inline GemmPlan plan_gemm_mma(int M, int N, int K, bool dual) {
         int want = (160 + g.tiles_n - 1) / g.tiles_n;          // about one CTA per SM
         int max_splits = ktiles / 2 > 0 ? ktiles / 2 : 1;      // at least 128 of K per split
         int s = want < max_splits ? want : max_splits;
-        if (const char* dbg = getenv("FVLA_DEBUG_SPLITS")) s = atoi(dbg);
         if (s < 1) s = 1;
         int per = (ktiles + s - 1) / s;
         g.k_per_split = per * 64;
@@ -303,11 +302,11 @@ template <int BM, int BN, int STAGES, int WM, int WN, bool DUAL>
 inline int launch_gemm_cfg(const GemmArgs& a, dim3 grid, cudaStream_t st) {
     constexpr int smem = STAGES * (BM * 64 * 2 + (DUAL ? 2 : 1) * 64 * BN * 2);
     auto kern = gemm_mma_kernel<BM, BN, STAGES, WM, WN, DUAL>;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceFlag configured;
+    if (!configured.get()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
-        configured = true;
+        configured.set();
     }
     kern<<<grid, WM * WN * 32, smem, st>>>(a);
     return check_launch("gemm_mma_kernel");

@@ -13,10 +13,12 @@
 //     partials of its slice of tokens; after one cluster barrier CTA r sums them in rank order
 //     (deterministic) and runs the fused epilogue: RMS-factor + RoPE + scatter to Q/K/V, GeGLU,
 //     bias, or in-place residual add into the fp32 stream.
-// The activation operand is read straight from the residual stream (fp32 or bf16), converted to
-// bf16 in registers and written into the swizzled operand layout by the CTA itself; the per-token
-// sum of squares for the RMS factor is taken from the same registers and reduced with the
-// partials. No separate norm kernel, no global-memory scratch, no semaphores.
+// The activation operand arrives by TMA as bf16 rows: either the activation itself (bf16) or the bf16
+// shadow that the kernels writing the fp32 residual stream keep beside it; the per-token sum of
+// squares for the RMS factor is read back from that operand tile in shared memory while the MMAs run
+// and is reduced with the partials. (An fp32 activation without a shadow is still accepted: the CTA
+// then converts its slice in registers.) No separate norm kernel, no global-memory scratch, no
+// semaphores.
 #pragma once
 
 #include <cuda.h>
@@ -53,7 +55,9 @@ struct SkinnyArgs {
     const bf16* rope; bf16* q; bf16* k; bf16* v; int heads, head_dim;
     bf16* factor_out;                         // optional bf16 copy of the factors
     int* status;
-    unsigned long long* dbg;                   // optional development aid: 8 globaltimer stamps per CTA
+    uint32_t spin_limit;                       // polls before a wait gives up (0 = the default limit)
+    uint32_t expect_extra_bytes;               // self-test only: bytes the owners wait for that no peer sends
+    FVLA_DBG_MEMBER
 };
 
 // MMA: A = W tile (MN-major, 128 n x 16 k), B = x tile (K-major, 64 tokens x 16 k), D fp32 128x64.
@@ -89,13 +93,6 @@ __device__ __forceinline__ void cluster_sync_all() {
 //   ssq_local 64 x 2 fp32, barriers, tmem slot, abort flag
 constexpr int THREADS = 512;
 
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define FVLA_STAMP(i) do { if (dbg && tid == 0) dbg[i] = gtime(); } while (0)
-
 __device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster_addr, uint32_t src_cta_addr, uint32_t bytes,
                                                  uint32_t mbar_cluster_addr) {
     asm volatile(
@@ -125,7 +122,7 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + off_bar + (MAX_KB + 2) * 8 + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    unsigned long long* dbg = p.dbg ? p.dbg + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8 : nullptr;
+    FVLA_DBG_CTA(p, blockIdx.y * gridDim.x + blockIdx.x);
     FVLA_STAMP(0);
     const uint32_t rank = cluster_ctarank();                 // position along K within the cluster
     const int tile = blockIdx.x;
@@ -143,7 +140,7 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
         mbar_init(in_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        if (i_own) mbar_expect_tx(in_bar, (uint32_t)(S - 1) * (uint32_t)TS * (512u + (p.need_factor ? 4u : 0u)));      // S - 1 peers send
+        if (i_own) mbar_expect_tx(in_bar, (uint32_t)(S - 1) * (uint32_t)TS * (512u + (p.need_factor ? 4u : 0u)) + p.expect_extra_bytes);      // S - 1 peers send
     }
     // One lane per k-block sets up that block's barrier and requests its weights: all of this
     // CTA's share of W is in flight within a few hundred cycles of kernel start.
@@ -331,7 +328,7 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
     FVLA_STAMP(4);
     // Owner phase: this CTA finishes tokens [rank*TS, rank*TS + TS), summing partials in rank order.
     if (i_own) {
-        mbar_wait(in_bar, 0, abort_flag);
+        mbar_wait(in_bar, 0, abort_flag, p.spin_limit ? p.spin_limit : tc5::kSpinLimit);
         FVLA_STAMP(5);
 #pragma unroll
         for (int j = 0; j < PRE; ++j) {
@@ -445,12 +442,12 @@ inline int launch_skinny(SkinnyArgs a, const void* W, const void* W2, int ldw, c
     if (!pl.ok) { set_error("skinny gemm: shape %dx%dx%d not supported", a.M, a.N, a.K); return FVLA_ERR_UNSUPPORTED; }
     a.splits = pl.splits; a.kblocks = pl.kblocks;
     auto kern = skinny_gemm_kernel<EPI>;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceFlag configured;
+    if (!configured.get()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
-        configured = true;
+        configured.set();
     }
     CUtensorMap tmW, tmW2, tmX;
     int rc = tc5::make_map(&tmW, W, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)ldw, 64, 64);

@@ -28,7 +28,7 @@ namespace tc5 {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -48,9 +48,11 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
-// Bounded wait; false when the limit ran out (the caller then abandons its loop).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+// Bounded wait; false when the limit ran out (the caller then abandons its loop). `limit` is the number
+// of polls; the default is far beyond any legitimate wait of these kernels (tens of microseconds).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t limit = kSpinLimit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;
     }
@@ -144,7 +146,7 @@ struct Tc5Args {
     float* partial;            // [tile][split][BN/4 column quads][128 rows][4] fp32 partial products (splits > 1)
     int* counters;             // one self-resetting arrival counter per tile (splits > 1)
     int* status;               // device word: set non-zero when a bounded wait ran out
-    unsigned long long* dbg;   // optional development aid: globaltimer stamps, 8 per CTA
+    FVLA_DBG_MEMBER
 };
 
 // Epilogue for 8 adjacent columns of one row (a: first / gate accumulator, u: up accumulator).
@@ -256,9 +258,8 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const GemmArgs& p = args.g;
     const int num_tiles = args.tiles_m * args.tiles_n * args.splits;      // work items: (tile, k-split)
-    unsigned long long* dbg = args.dbg ? args.dbg + (size_t)blockIdx.x * 8 : nullptr;
-    auto stamp = [&](int i) { if (dbg) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); dbg[i] = t; } };
-    if (threadIdx.x == 0) stamp(0);
+    FVLA_DBG_CTA(args, blockIdx.x);
+    if (threadIdx.x == 0) FVLA_STAMP_ANY(0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -280,7 +281,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
     // initialisation already published them; the matching wait sits where the first remote access is)
     if (CLUSTER) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     // Set-up above touched only this CTA's own shared memory and TMEM.
-    if (threadIdx.x == 0) stamp(1);
+    if (threadIdx.x == 0) FVLA_STAMP_ANY(1);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -347,7 +348,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait(full_bar(s), ph, abort_flag)) goto mma_done;
                     tc_fence_after();
-                    if (it == 0) stamp(2);
+                    if (it == 0) FVLA_STAMP_ANY(2);
                     const uint32_t sA = smem_base + s * Cfg::STAGE_BYTES;
 #pragma unroll
                     for (int k16 = 0; k16 < BK / 16; ++k16) {
@@ -361,7 +362,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                     umma_commit(empty_bar(s));              // slot reusable once these MMAs have read it
                 }
                 umma_commit(accfull_bar(acc));              // accumulator complete
-                if (tcount == 0) stamp(3);
+                if (tcount == 0) FVLA_STAMP_ANY(3);
             }
         }
     mma_done:;
@@ -412,7 +413,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
             if (!mbar_wait(accfull_bar(acc), acc_ph, abort_flag)) break;
             if (tile + (int)gridDim.x >= num_tiles) { if (p.trigger_early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }      // last accumulator complete
             tc_fence_after();
-            if (tcount == 0 && threadIdx.x == 64) stamp(4);
+            if (tcount == 0 && threadIdx.x == 64) FVLA_STAMP_ANY(4);
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * Cfg::ACC_COLS + chalf * HALF;
             bool from_partials = false;
             bool from_cluster = false;
@@ -600,7 +601,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
             }
             tc_fence_before();
             __syncwarp();
-            if (tcount == 0 && threadIdx.x == 64) stamp(5);
+            if (tcount == 0 && threadIdx.x == 64) FVLA_STAMP_ANY(5);
             if (!from_partials && lane == 0) mbar_arrive(accempty_bar(acc));
         }
     }
@@ -616,7 +617,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
         tc_fence_after();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
-    if (threadIdx.x == 0) stamp(6);
+    if (threadIdx.x == 0) FVLA_STAMP_ANY(6);
     if (threadIdx.x == 0 && *abort_flag && args.status) atomicExch(args.status, 1);
 }
 
@@ -655,12 +656,13 @@ inline int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t
 }
 
 inline int num_sms() {
-    static int sms = 0;
+    static std::atomic<int> cached[kMaxDevices];
+    const int dev = current_device();
+    int sms = cached[dev].load(std::memory_order_relaxed);
     if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
+        cached[dev].store(sms, std::memory_order_relaxed);
     }
     return sms;
 }
@@ -699,11 +701,11 @@ template <int BN, bool DUAL, int STAGES, bool ROPE = false, bool CLUSTER = false
 inline int launch_tc5_cfg(const GemmArgs& g, int* status, cudaStream_t st, int splits = 1, void* ws = nullptr) {
     using Cfg = Tc5Cfg<BN, DUAL, STAGES>;
     auto kern = tc5_gemm_kernel<BN, DUAL, STAGES, ROPE, CLUSTER>;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceFlag configured;
+    if (!configured.get()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
-        configured = true;
+        configured.set();
     }
     CUtensorMap tmA, tmB, tmB2;
     int rc = make_map(&tmA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, BM);
@@ -726,7 +728,7 @@ inline int launch_tc5_cfg(const GemmArgs& g, int* status, cudaStream_t st, int s
         a.partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + counters);
     }
     a.status = status;
-    { const char* v = getenv("FVLA_DEBUG_TIMESTAMPS"); a.dbg = v ? reinterpret_cast<unsigned long long*>(strtoull(v, nullptr, 10)) : nullptr; }
+    FVLA_DBG_ATTACH(a);
     int tiles = a.tiles_m * a.tiles_n * splits;
     int grid = tiles < num_sms() ? tiles : num_sms();
     cudaError_t e;
@@ -760,17 +762,9 @@ inline int launch_gemm_tc5(GemmArgs g, int* status, cudaStream_t st, void* ws = 
     if (g.B2 != nullptr) return launch_tc5_cfg<128, true, 4>(g, status, st);
     if (g.rope != nullptr) return launch_tc5_cfg<128, false, 6, true>(g, status, st);
     Tc5Plan pl = plan_tc5(g.M, g.N, g.K, ws != nullptr);
-    if (const char* dbg = getenv("FVLA_DEBUG_TC5_PLAN")) {          // "bn,splits": development aid
-        int bn = 128, sp = 1;
-        if (sscanf(dbg, "%d,%d", &bn, &sp) == 2 && ws != nullptr) {
-            pl.bn = bn; pl.splits = sp;
-            pl.ws_bytes = sp > 1 ? 256 * ((((size_t)((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn)) * 4 + 255) / 256) +
-                                       (size_t)sp * ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn) * BM * bn * 4 : 0;
-        }
-    }
     // Split-K reduced inside clusters (128-wide tiles, one work item per CTA, no scratch): taken when its
     // estimate (mainloop + epilogue + one 64 KB push per extra split) beats the plan above.
-    if (g.rope == nullptr && !g.c_f32 && !getenv("FVLA_DEBUG_TC5_PLAN")) {
+    if (g.rope == nullptr && !g.c_f32) {
         const int tiles = ((g.M + BM - 1) / BM) * ((g.N + 127) / 128), k_iters = (g.K + BK - 1) / BK;
         int best_s = 0;
         float best_t = pl.est_us;

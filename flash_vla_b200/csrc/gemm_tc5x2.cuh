@@ -352,11 +352,11 @@ inline PairPlan plan_pair_plain(int M, int N, int K, bool ws_ok) {
 template <bool DUAL>
 inline int launch_pair(const GemmArgs& g, int splits, void* ws, int* status, cudaStream_t st) {
     auto kern = tc5x2_gemm_kernel<DUAL>;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceFlag configured;
+    if (!configured.get()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
-        configured = true;
+        configured.set();
     }
     CUtensorMap tmA, tmG, tmU;
     int rc = make_map(&tmA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, 128);

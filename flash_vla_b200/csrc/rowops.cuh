@@ -184,6 +184,14 @@ __global__ void __launch_bounds__(256) action_out_kernel(const XT* __restrict__ 
     }
 }
 
+// dst[i] = bf16(src[i]), four values per thread.
+__global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* __restrict__ src, bf16* __restrict__ dst, size_t quads) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= quads) return;
+    const float4 v = reinterpret_cast<const float4*>(src)[i];
+    reinterpret_cast<uint2*>(dst)[i] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+}
+
 // Pulls up to 8 byte ranges from HBM into L2 without touching any SM-side storage: every thread
 // issues bulk L2 prefetches for 8 KB pieces. Meant to run on a side stream next to the decoder, whose
 // weight-streaming GEMMs then find the next layer's weights in L2 instead of waiting on HBM.

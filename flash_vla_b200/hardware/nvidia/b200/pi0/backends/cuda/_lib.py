@@ -33,6 +33,7 @@ SIGNATURES: dict[str, list] = {
     "fvla_decoder_action_out_proj": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
     "fvla_l2_prefetch": [ctypes.POINTER(c_void_p), ctypes.POINTER(c_size_t), _I, _P],
     "fvla_embed_rows": [_P, _P, _P, _I, _I, ctypes.c_longlong, _P],
+    "fvla_selftest_wait_timeout": [_P, _P, _P, _I, _I, _I, ctypes.c_uint, _P],
 }
 QUERIES: dict[str, tuple] = {
     "fvla_last_error": ([], c_char_p),

@@ -44,11 +44,13 @@ def use_pool(pool: ScratchPool):
         _POOL = previous
 
 
-# fp32 tensor (by base address) -> (its bf16 shadow, the fp32 tensor). A shadow is a bf16 copy
-# that every op of this backend refreshes when it writes the fp32 tensor, so that the GEMMs reading
-# the tensor can fetch ready-made bf16 rows by TMA instead of converting fp32 in the kernel. Code
-# that writes a registered tensor by other means must call `sync_shadow` afterwards.
-_SHADOWS: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+# A bf16 shadow is a bf16 copy of an fp32 tensor that every op of this backend refreshes when it writes
+# the fp32 tensor, so that the GEMMs reading the tensor can fetch ready-made bf16 rows by TMA instead of
+# converting fp32 in the kernel. The pairing lives ON the fp32 tensor object (an attribute), not in a
+# table keyed by address: it is found again through `view._base`, it cannot outlive the tensor, and a
+# later allocation that happens to reuse the address is never mistaken for it. Code that writes a
+# registered tensor by other means must call `sync_shadow` afterwards.
+_SHADOW_ATTR = "_fvla_bf16_shadow"
 
 
 def register_bf16_shadow(master: torch.Tensor, shadow: torch.Tensor) -> None:
@@ -57,36 +59,41 @@ def register_bf16_shadow(master: torch.Tensor, shadow: torch.Tensor) -> None:
         raise ValueError("register_bf16_shadow: need an fp32 master and a bf16 shadow of equal shape")
     if not (master.is_contiguous() and shadow.is_contiguous()):
         raise ValueError("register_bf16_shadow: tensors must be contiguous")
-    _SHADOWS[master.data_ptr()] = (shadow, master)
+    if master._base is not None:
+        raise ValueError("register_bf16_shadow: register the owning tensor, not a view of it")
+    setattr(master, _SHADOW_ATTR, shadow)
     shadow.copy_(master)
 
 
 def unregister_bf16_shadow(master: torch.Tensor) -> None:
-    _SHADOWS.pop(master.data_ptr(), None)
+    if hasattr(master, _SHADOW_ATTR):
+        delattr(master, _SHADOW_ATTR)
+
+
+def _shadow_and_offset(t: torch.Tensor):
+    """(shadow tensor, element offset of `t` inside its owner) when `t` is a registered fp32 tensor or a
+    contiguous view of one, else (None, 0)."""
+    if not isinstance(t, torch.Tensor) or t.dtype != torch.float32:
+        return None, 0
+    owner = t if t._base is None else t._base
+    shadow = getattr(owner, _SHADOW_ATTR, None)
+    if shadow is None:
+        return None, 0
+    return shadow, (t.data_ptr() - owner.data_ptr()) // 4
 
 
 def _shadow_of(t: torch.Tensor):
     """Device address inside the registered shadow that mirrors the first element of `t` (which may be
     a row-offset view of the master), or None."""
-    if t.dtype != torch.float32:
-        return None
-    ptr = t.data_ptr()
-    for base, (shadow, master) in _SHADOWS.items():
-        offset = ptr - base
-        if 0 <= offset < master.numel() * 4 and offset % 4 == 0:
-            return shadow.data_ptr() + offset // 2
-    return None
+    shadow, first = _shadow_and_offset(t)
+    return None if shadow is None else shadow.data_ptr() + 2 * first
 
 
 def sync_shadow(t: torch.Tensor) -> None:
     """Refresh the shadow rows mirroring `t` after `t` was written outside this backend."""
-    ptr = t.data_ptr()
-    for base, (shadow, master) in _SHADOWS.items():
-        offset = ptr - base
-        if 0 <= offset < master.numel() * 4:
-            first = offset // 4
-            shadow.view(-1)[first:first + t.numel()].copy_(t.reshape(-1))
-            return
+    shadow, first = _shadow_and_offset(t)
+    if shadow is not None:
+        shadow.view(-1)[first:first + t.numel()].copy_(t.reshape(-1))
 
 
 # Side stream on which `prefetch_l2` runs, per device, and whether work on it still has to be joined.

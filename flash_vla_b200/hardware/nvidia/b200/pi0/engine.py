@@ -35,7 +35,7 @@ class Pi0Inference:
 
     def __init__(self, checkpoint, num_views: int, chunk_size: int, steps: int = 10,
                  layers: int = 18, fused: bool = True, device: str = "cuda", plan=None,
-                 capture: bool = True, episodes: int = 1, overlap: bool = True):
+                 capture: bool = True, episodes: int = 1, overlap: bool = True, embedding_table=None):
         if not torch.cuda.is_available():
             raise RuntimeError("Pi0Inference needs a CUDA device; the B200 target has no CPU path")
         if episodes < 1:
@@ -53,6 +53,16 @@ class Pi0Inference:
                 if hasattr(self.ops, name):
                     delattr(self.ops, name)
         self.prompt_len = int(checkpoint["language_embeds"].shape[0])
+        # With an embedding table the prompt lookup is part of the captured pass: the graph gathers
+        # table[prompt_ids] straight into the prefix rows, and `set_prompt(ids)` only rewrites the ids.
+        self.embedding_table = None
+        self.prompt_ids = None
+        if embedding_table is not None and self.prompt_len:
+            table = embedding_table.to(device=device, dtype=torch.bfloat16).contiguous()
+            if table.ndim != 2 or table.shape[1] != checkpoint["language_embeds"].shape[1]:
+                raise ValueError(f"embedding_table must be (vocab, {checkpoint['language_embeds'].shape[1]})")
+            self.embedding_table = table
+            self.prompt_ids = torch.zeros(self.prompt_len, dtype=torch.int64, device=device)
 
         expected = weight_shapes(self.prompt_len)
         missing = sorted(set(expected) - set(checkpoint))
@@ -86,7 +96,9 @@ class Pi0Inference:
 
     def _run_episode(self, e: int):
         b = self.episode_buffers[e]
-        if self.prompt_len:
+        if self.prompt_len and self.embedding_table is not None:
+            self.ops.embed_prompt(self.embedding_table, self.prompt_ids, b["encoder_x"][self.num_views * 256:])
+        elif self.prompt_len:
             b["encoder_x"][self.num_views * 256:].copy_(self.weights["language_embeds"])
         with wrappers.use_pool(self.pools[e]):
             pipeline.vision_encoder(self.ops, self.weights, b, self.num_views)
@@ -140,31 +152,33 @@ class Pi0Inference:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
 
-    def set_prompt(self, ids, embedding_table):
-        """Replace the prompt: language_embeds[r] = embedding_table[ids[r]] (row gather on the device).
+    def set_prompt(self, ids, embedding_table=None):
+        """Replace the prompt: the prefix rows after the image tokens become embedding_table[ids].
 
         The prompt length is fixed at construction (it sets the static buffer plan and the captured graph):
-        `ids` must hold exactly `prompt_len` token ids. The gather writes into the static tensor the graph
-        reads, so the next `forward` uses the new prompt. An extension: the reference takes only
-        precomputed `language_embeds` (engine.py:43, :60).
+        `ids` must hold exactly `prompt_len` token ids. An engine built with `embedding_table=` gathers
+        inside its captured pass from a static id buffer; this call then only copies the ids there (a
+        table passed here must be omitted). Otherwise the gather runs here, outside the graph, into the
+        static `language_embeds` tensor the graph reads. Either way the next `forward` uses the new
+        prompt. An extension: the reference takes only precomputed `language_embeds` (engine.py:43, :60).
         """
         ids = torch.as_tensor(ids, dtype=torch.int64).reshape(-1)
         if ids.numel() != self.prompt_len:
             raise ValueError(f"set_prompt: {ids.numel()} ids for an engine built with prompt_len={self.prompt_len}")
         if self.prompt_len == 0:
             return
+        if self.embedding_table is not None:
+            if embedding_table is not None:
+                raise ValueError("set_prompt: this engine gathers from the table given at construction")
+            self.prompt_ids.copy_(ids, non_blocking=True)
+            return
+        if embedding_table is None:
+            raise ValueError("set_prompt: an embedding table is needed (none was given at construction)")
         target = self.weights["language_embeds"]
         table = embedding_table.to(device=target.device, dtype=torch.bfloat16)
         if table.ndim != 2 or table.shape[1] != target.shape[1]:
             raise ValueError(f"set_prompt: embedding table must be (vocab, {target.shape[1]})")
         self.ops.embed_prompt(table.contiguous(), ids.to(target.device), target)
-
-    def __del__(self):
-        try:
-            for b in self.episode_buffers:
-                wrappers.unregister_bf16_shadow(b["decoder_x"])
-        except Exception:
-            pass
 
     def forward(self, images, state, noise):
         """Copy the inputs into their static buffers, replay, return the denoised chunk.
@@ -179,6 +193,9 @@ class Pi0Inference:
         else:
             dst = (self._batched_observation_images_normalized, self._batched_observation_state_normalized,
                    self._batched_diffusion_noise)
+        for name, src, to in zip(("images", "state", "noise"), (images, state, noise), dst):
+            if tuple(src.shape) != tuple(to.shape):          # copy_ would broadcast silently
+                raise ValueError(f"forward: {name} has shape {tuple(src.shape)}, expected {tuple(to.shape)}")
         dst[0].copy_(images, non_blocking=True)
         dst[1].copy_(state, non_blocking=True)
         dst[2].copy_(noise, non_blocking=True)

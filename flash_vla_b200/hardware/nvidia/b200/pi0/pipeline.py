@@ -144,7 +144,3 @@ def transformer_decoder(ops, weights, buffers, encoder_seq_len, steps=DIFFUSION_
         decoder_step(ops, weights, b, encoder_seq_len, step, layers, noise=master,
                      prefetch_next_step=step + 1 < steps)
     decoder_epilogue(b)
-
-
-def num_vision_tokens(num_views: int) -> int:
-    return num_views * VISION_TOKENS

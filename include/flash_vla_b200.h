@@ -45,6 +45,14 @@ unsigned long long fvla_launch_count(void);
  * bounded waits (1..6: which kernel; its output is then invalid) or met a bad token id (7). Reading
  * clears the word. Negative: error code. This one call synchronises `stream`. */
 int fvla_device_status(void* stream);
+/* No counterpart in the reference (which has no device-side error reporting, only Python exceptions).
+ * Failure-detection self-test: runs the decoder's cluster GEMM (out += x(M,K) @ W(K,N), all bf16, a
+ * shape fvla_linear_residual serves with M <= 64) with the CTAs that finish the tiles told to wait for
+ * 16 bytes that no CTA ever sends, and with that wait limited to `spin_limit` polls (1..65536). The
+ * kernel must give up, release its tensor memory and return within milliseconds; fvla_device_status
+ * then reports 2 and `out` is unspecified. Nothing faults and the context stays usable. */
+int fvla_selftest_wait_timeout(const void* x, const void* weight, void* out, int M, int N, int K,
+                               unsigned spin_limit, void* stream);
 
 /* Scratch needed by a GEMM-shaped op of the given logical size. `dual` = 1 for gated FFNs. */
 size_t fvla_gemm_workspace_bytes(int M, int N, int K, int dual);
@@ -106,8 +114,9 @@ size_t fvla_encoder_attention_workspace_bytes(int queries, int keys);
 int fvla_encoder_attention(const void* Q, const void* K, const void* V, void* out, int queries,
                            int keys, int head_dim, float scale, void* ws, size_t ws_bytes, void* stream);
 /* wrappers.py:366-371, :383-392 (encoder) and :176-189 (decoder): out += x(M,K) @ W(K,N). out is
- * bf16, or an fp32 residual stream when out_is_f32 != 0. out_shadow (may be NULL; M <= 64 only) is a
- * bf16 tensor of out's shape that receives the rounded new value, for a later GEMM to read. */
+ * bf16, or an fp32 residual stream when out_is_f32 != 0. out_shadow (may be NULL; fp32 out only) is a
+ * bf16 tensor of out's shape that receives the rounded new value, for a later GEMM to read: written by
+ * the GEMM's own epilogue for M <= 64, by a small conversion kernel after it otherwise. */
 int fvla_linear_residual(const void* x, const void* weight, void* out, int out_is_f32, void* out_shadow,
                          int M, int N, int K, void* ws, size_t ws_bytes, void* stream);
 /* wrappers.py:374-380: x_norm = rms(x); out = gelu(x_norm @ Wg) * (x_norm @ Wu). */
@@ -129,7 +138,12 @@ int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* x_shadow
                                int head_dim, void* ws, size_t ws_bytes, void* stream);
 /* fused_wrappers.py:88-115 (and the unfused chain wrappers.py:147-173): softmax(Q K^T / sqrt(hd))
  * V over all `keys`, with rows < heads (the state token) limited to keys j <= encoder_seq_len.
- * out may alias Q. */
+ * out may alias Q.
+ * Precondition on K / V rows [0, encoder_seq_len) (the prefix cache): they must be complete before the
+ * kernel that precedes this call in `stream` STARTS, not merely before it ends. The kernel fetches those
+ * rows while its predecessor is still finishing (programmatic dependent launch) and only waits for the
+ * predecessor before reading Q and the rows from encoder_seq_len on. A caller whose previous kernel in
+ * the stream writes the prefix rows must put an event or another kernel between the two. */
 int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* out, int queries,
                            int keys, int head_dim, int heads, int encoder_seq_len, void* ws,
                            size_t ws_bytes, void* stream);

@@ -27,6 +27,14 @@ Three precision levels:
     is stored, as any bf16-storage implementation must.
   * `faithful=True`: additionally rounds at the reference kernels' internal
     rounding points (listed per op), to attribute differences.
+
+A fourth switch, `operands_bf16=True` (decoder ops only), answers a different question: how far
+from the fp32 result must ANY bf16 tensor-core implementation land? It rounds to bf16 exactly
+the activation operands a tensor-core GEMM has to take in bf16 (the rows fed to the QKV, gate/up,
+out, down and action-MLP projections; Q, K, V and the probabilities in attention) and keeps the
+residual stream, every accumulator, the norm factors, RoPE and the Euler update in fp32. The
+distance of that run from the plain fp32 run is the floor below which the step tolerance of a
+config cannot be pushed by better kernels.
 """
 from __future__ import annotations
 
@@ -116,8 +124,13 @@ def _rotate_scatter(proj, rope, Q, K, V):
     V.copy_(proj[:, (heads + 1) * hd:])
 
 
-def _make_ops(fused: bool, faithful: bool) -> dict:
+def _make_ops(fused: bool, faithful: bool, operands_bf16: bool = False) -> dict:
     R = faithful
+    A = operands_bf16
+
+    def _a(x):
+        """A tensor-core activation operand: bf16 when `operands_bf16`, else as stored."""
+        return _r(_f(x), A)
 
     # ------------------------------------------------------------------ vision
     def vision_patch_embed(images, patch_w, patch_b, pos_emb, out):
@@ -229,7 +242,7 @@ def _make_ops(fused: bool, faithful: bool) -> dict:
 
     def decoder_action_mlp(x, weight, bias, out):
         """wrappers.py:123-128."""
-        out.copy_(_f(x) @ _f(weight) + _f(bias))
+        out.copy_(_a(x) @ _f(weight) + _f(bias))
         return out
 
     def decoder_norm_qkv_rope(x, weight_qkv, rope, Q, K, V, norm_factor):
@@ -238,7 +251,7 @@ def _make_ops(fused: bool, faithful: bool) -> dict:
         M = x.shape[0]
         f = rms_factor(x)
         norm_factor[:M].copy_(f)
-        proj = (_f(x) @ _f(weight_qkv)) * _r(f, R)[:, None]
+        proj = (_a(x) @ _f(weight_qkv)) * _r(f, R)[:, None]
         _rotate_scatter(proj, rope, Q, K, V)
 
     def _attn_mask(queries, keys, encoder_seq_len):
@@ -252,20 +265,20 @@ def _make_ops(fused: bool, faithful: bool) -> dict:
         The state token (flat rows 0..7) sees the prefix and itself; action tokens see all."""
         queries, hd = Q.shape
         keys = K.shape[0]
-        s = (_f(Q) @ _f(K).T) * (hd ** -0.5)
+        s = (_a(Q) @ _a(K).T) * (hd ** -0.5)
         if not fused:
             s = _r(s, R)
         s = s.masked_fill(~_attn_mask(queries, keys, encoder_seq_len), float("-inf"))
         p = torch.softmax(s, dim=-1)
         if not fused:
             scores[:, :keys].copy_(p)
-        o = _r(p, R) @ _f(V)
+        o = _r(p, R or A) @ _a(V)
         out.copy_(o)
         return out
 
     def decoder_out_proj_residual(x, weight, out):
         """wrappers.py:176-181."""
-        out.copy_(_f(out) + _f(x) @ _f(weight))
+        out.copy_(_f(out) + _a(x) @ _f(weight))
         return out
 
     decoder_ffn_down_residual = decoder_out_proj_residual       # wrappers.py:184-189
@@ -277,8 +290,8 @@ def _make_ops(fused: bool, faithful: bool) -> dict:
         M = x.shape[0]
         f = rms_factor(x)
         if fused:
-            g = (_f(x) @ _f(gate_w)) * _r(f, R)[:, None]
-            u = (_f(x) @ _f(up_w)) * _r(f, R)[:, None]
+            g = (_a(x) @ _f(gate_w)) * _r(f, R)[:, None]
+            u = (_a(x) @ _f(up_w)) * _r(f, R)[:, None]
         else:
             norm_factor[:M].copy_(f)
             xs = _r(_f(x) * _r(f, R)[:, None], R)
@@ -302,10 +315,11 @@ def _make_ops(fused: bool, faithful: bool) -> dict:
     return {k: v for k, v in locals().items() if callable(v) and not k.startswith("_")}
 
 
-def op_table(fused: bool = True, faithful: bool = False) -> SimpleNamespace:
+
+def op_table(fused: bool = True, faithful: bool = False, operands_bf16: bool = False) -> SimpleNamespace:
     """Oracle op table: the 19 reference op names plus `vision_attention` and
     `encoder_attention` (which the reference pipeline imports directly)."""
-    return SimpleNamespace(**_make_ops(fused, faithful))
+    return SimpleNamespace(**_make_ops(fused, faithful, operands_bf16))
 
 
 # ---------------------------------------------------------------------------

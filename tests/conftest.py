@@ -53,3 +53,11 @@ def full_checkpoint():
     from flash_vla_b200.models.pi0 import random_checkpoint
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     return random_checkpoint(prompt_len=0, wscale=0.02, seed=0, device="cpu")
+
+
+@pytest.fixture(scope="session")
+def decoder_checkpoint():
+    """The decoder tensors of the same checkpoint, drawn once per session (a draw walks the whole
+    2.7 G-parameter stream on one CPU thread, about a minute, whatever is kept)."""
+    from flash_vla_b200.models.pi0 import random_checkpoint
+    return random_checkpoint(prompt_len=0, wscale=0.02, seed=0, device="cpu", only=("decoder_",))

@@ -1,0 +1,79 @@
+"""The OpenPI -> target checkpoint converter against the REFERENCE'S OWN converter.
+
+`tests/golden/openpi_checkpoint.json` holds SHA-256 digests of the 38 tensors that the reference's
+`target_checkpoint` (eval/baselines/openpi.py:129-313) produced from a seeded synthetic full-shape
+OpenPI state dict. The package's converter must reproduce every digest bit for bit on the same state.
+One tensor, `decoder_action_fused_time_biases`, goes through OpenPI's `create_sinusoidal_pos_embedding`,
+which the reference imports from a package that is not available: the fixture lists it as unpinned (the
+generator supplied this repository's restatement of that function), so for it the test only shows that
+nothing changed since the fixture was made, and checks the restated formula independently.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import math
+
+import pytest
+import torch
+
+from conftest import GOLDEN
+from flash_vla_b200.models.pi0 import openpi, weight_shapes
+
+
+def _sha(t: torch.Tensor) -> str:
+    return hashlib.sha256(t.contiguous().view(torch.uint8).numpy().tobytes()).hexdigest()
+
+
+def test_converter_reproduces_the_reference_converter_bit_for_bit():
+    gold = json.loads((GOLDEN / "openpi_checkpoint.json").read_text())
+    state = openpi.synthetic_openpi_state(seed=gold["state"]["seed"], scale=gold["state"]["scale"])
+    out = openpi.target_checkpoint(state)
+    assert list(out) == list(weight_shapes(0)) and len(out) == 38
+    assert set(gold["sha256"]) == set(out)
+    wrong = [name for name, digest in gold["sha256"].items() if _sha(out[name]) != digest]
+    assert not wrong, f"tensors that differ from the reference converter's output: {wrong}"
+    assert gold["unpinned"] == ["decoder_action_fused_time_biases"]
+    assert all(v.dtype == torch.bfloat16 for v in out.values())
+
+    # a missing source tensor is reported by name, as the reference does (openpi.py:75-79)
+    del state["state_proj.bias"]
+    with pytest.raises(KeyError, match="state_proj.bias"):
+        openpi.target_checkpoint(state)
+
+
+def test_adjacent_pair_permutation_maps_half_split_rope_to_interleaved_rope():
+    """Rotating the converted layout by adjacent pairs equals rotating the original by half-split."""
+    g = torch.Generator().manual_seed(0)
+    heads, d, rows = 3, 8, 5
+    w = torch.randn(rows, heads * d, generator=g)
+    p = openpi.adjacent_pair_columns(w, heads)
+    theta = torch.randn(d // 2, generator=g)
+    cos, sin = torch.cos(theta), torch.sin(theta)
+    x = w.view(rows, heads, d)
+    half = torch.cat([x[..., : d // 2] * cos - x[..., d // 2:] * sin, x[..., d // 2:] * cos + x[..., : d // 2] * sin], dim=-1)
+    y = p.view(rows, heads, d // 2, 2)
+    pair = torch.stack([y[..., 0] * cos - y[..., 1] * sin, y[..., 1] * cos + y[..., 0] * sin], dim=-1)
+    # the rotated pair (2p, 2p+1) of the new layout holds dims (p, d/2 + p) of the old one
+    assert torch.allclose(pair[..., 0], half[..., : d // 2], atol=1e-6)
+    assert torch.allclose(pair[..., 1], half[..., d // 2:], atol=1e-6)
+
+
+def test_time_embedding_formula():
+    t = torch.tensor([1.0, 0.5, 0.1])
+    e = openpi.sinusoidal_time_embedding(t, 8, 4e-3, 4.0)
+    assert e.shape == (3, 8) and e.dtype == torch.float64
+    periods = [4e-3 * (4.0 / 4e-3) ** (j / 3) for j in range(4)]
+    for i, ti in enumerate(t.tolist()):
+        for j, pj in enumerate(periods):
+            assert math.isclose(e[i, j].item(), math.sin(2 * math.pi * ti / pj), abs_tol=1e-9)
+            assert math.isclose(e[i, 4 + j].item(), math.cos(2 * math.pi * ti / pj), abs_tol=1e-9)
+
+
+def test_error_metrics_match_the_reference_report():
+    a = torch.randn(50, 32, generator=torch.Generator().manual_seed(1))
+    m = openpi.error_metrics(a, a + 1e-3)
+    assert set(m) == {"max_abs", "mean_abs", "rms_error", "p99_abs", "cosine_similarity"}
+    assert math.isclose(m["max_abs"], 1e-3, rel_tol=1e-2) and m["cosine_similarity"] > 0.999999
+    with pytest.raises(ValueError):
+        openpi.error_metrics(a, a[:1])

@@ -119,11 +119,11 @@ def test_bf16_faithful_mode_rounds_where_the_reference_does():
     assert (outs[0][0] - outs[1][0]).abs().max() < 0.05
 
 
-def test_checkpoint_generator_reproduces_reference_hashes():
+def test_checkpoint_generator_reproduces_reference_hashes(decoder_checkpoint):
     """SHA-256 of tensors drawn by the reference's random_checkpoint (stored by make_golden)."""
-    from flash_vla_b200.models.pi0 import random_checkpoint
     gold = json.loads((GOLDEN / "checkpoint.json").read_text())
-    ck = random_checkpoint(**gold["args"], only=("decoder_",))
+    assert gold["args"] == {"prompt_len": 0, "wscale": 0.02, "seed": 0, "device": "cpu"}
+    ck = decoder_checkpoint
     checked = 0
     for name, digest in gold["sha256"].items():
         if name in ck:
@@ -133,21 +133,45 @@ def test_checkpoint_generator_reproduces_reference_hashes():
     assert checked >= 6
 
 
-def test_decoder_step_fixture_reproduces():
-    """The stored decoder-step result (made through the reference's transformer_decoder) is what
-    the oracle's own orchestration gives today."""
-    from flash_vla_b200.models.pi0 import random_checkpoint
+def _decoder_step(w32, kv_scale, ops):
     from flash_vla_b200.synthetic import decoder_step_inputs
-    gold = torch.load(GOLDEN / "decoder_step.pt")["kv01"]
-    ck = random_checkpoint(prompt_len=0, wscale=0.02, seed=0, device="cpu", only=("decoder_",))
-    K, V, st, nz = decoder_step_inputs(gold["kv_scale"])
+    K, V, st, nz = decoder_step_inputs(kv_scale)
     b, S = O.allocate_buffers(3, 50, 0)
     b["encoder_K"][:, :768] = K.float()
     b["encoder_V"][:, :768] = V.float()
     b["observation_state_normalized"].copy_(st)
     b["diffusion_noise"].copy_(nz)
-    O.transformer_decoder(O.op_table(True), {k: v.float() for k, v in ck.items()}, b, S, steps=1)
-    assert (b["diffusion_noise"] - gold["out"]).abs().max().item() < 1e-4
+    O.transformer_decoder(ops, w32, b, S, steps=1)
+    return b["diffusion_noise"]
+
+
+def test_decoder_step_fixture_reproduces(decoder_checkpoint):
+    """The stored decoder-step result (made through the reference's transformer_decoder) is what
+    the oracle's own orchestration gives today."""
+    gold = torch.load(GOLDEN / "decoder_step.pt")["kv01"]
+    w32 = {k: v.float() for k, v in decoder_checkpoint.items()}
+    out = _decoder_step(w32, gold["kv_scale"], O.op_table(True))
+    assert (out - gold["out"]).abs().max().item() < 1e-4
+
+
+@pytest.mark.parametrize("tag", ["kv1", "kv01"])
+def test_bf16_operand_floor_of_the_decoder_step(decoder_checkpoint, tag):
+    """How close to fp32 can a bf16 tensor-core implementation get on the one-step decoder config?
+
+    Run the step in fp32 with ONLY the tensor-core activation operands rounded to bf16 (weights are bf16
+    already; residual stream, accumulators, norm factors, RoPE, softmax and the Euler update stay fp32).
+    On a prefix K/V drawn from N(0, 1) that alone lands above the 2e-2 per-step tolerance the full
+    forward meets: the tolerance is unreachable on this input for any implementation that feeds
+    bf16 operands to the tensor cores. The GPU parity test bounds the CUDA path by 1.25 x this floor."""
+    gold = torch.load(GOLDEN / "decoder_step.pt")[tag]
+    w32 = {k: v.float() for k, v in decoder_checkpoint.items()}
+    out = _decoder_step(w32, gold["kv_scale"], O.op_table(True, False, True))
+    floor = (out - gold["out"]).abs().max().item()
+    print(f"\n[{tag}] bf16-operand floor: {floor:.4g} (stored {gold['operand_bf16_max_abs']:.4g}; "
+          f"reference numerics restated: {gold['bf16_faithful_max_abs']:.4g})")
+    assert abs(floor - gold["operand_bf16_max_abs"]) <= 1e-3 * max(1.0, floor)
+    assert floor > 2e-2, "if this ever drops below the step tolerance, tighten the GPU test to 2e-2"
+    assert floor < gold["bf16_faithful_max_abs"]          # and it is still below the reference's own numerics
 
 
 def test_error_metrics_fields():

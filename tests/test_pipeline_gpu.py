@@ -4,11 +4,12 @@ Tolerances are the ones the benchmark definition states: per Euler step (teacher
 both sides start the step from the oracle's noise) max-abs <= 2e-2; on the final action chunk
 of the free-running 10-step pass cosine >= 0.999.
 
-On the synthetic-prefix decoder step (prefix K/V drawn from N(0,1) instead of coming from the
-encoder) bf16 GEMM operands alone put any tensor-core implementation about 3e-2 from the fp32
-result: the restatement of the reference's own numerics (bf16 buffers and every kernel-internal
-rounding) sits at 6.4e-2, a figure stored with the fixture. That case therefore requires the
-CUDA path to be at least as close to fp32 as the reference's numerics are, and within 5e-2.
+On the synthetic-prefix decoder step (prefix K/V drawn from N(0,1) or N(0,0.1) instead of coming
+from the encoder) the 2e-2 step tolerance is not reachable by a bf16 tensor-core implementation:
+fp32 arithmetic with nothing but the tensor-core activation operands rounded to bf16 already lands
+3e-2 to 4e-2 from the fp32 result (`operand_bf16_max_abs` in the fixture, reproduced on the CPU by
+tests/test_oracle.py::test_bf16_operand_floor_of_the_decoder_step). That case is therefore bounded
+by 1.25 x that floor, and must also stay below the restated numerics of the reference itself.
 """
 from __future__ import annotations
 
@@ -58,15 +59,25 @@ def test_one_decoder_step(device_weights, tag, fused):
     err_x = (b["decoder_x"].float().cpu() - gold["decoder_x"]).abs()
     print(f"\n[{tag} fused={fused}] step max-abs {err:.4g}; decoder_x max-abs {err_x.max().item():.4g} "
           f"(|x| max {gold['decoder_x'].abs().max().item():.3g})")
-    assert err <= max(STEP_MAX_ABS, min(5e-2, gold["bf16_faithful_max_abs"]))
+    floor = gold["operand_bf16_max_abs"]
+    bound = STEP_MAX_ABS if 1.25 * floor <= STEP_MAX_ABS else 1.25 * floor
+    assert err <= bound, f"step max-abs {err:.4g} exceeds {bound:.4g} (bf16-operand floor {floor:.4g})"
+    assert err <= gold["bf16_faithful_max_abs"]
     # the bf16 view differs from the master only by its own rounding
     assert (b["diffusion_noise"].float() - b["diffusion_noise_f32"]).abs().max().item() <= \
         b["diffusion_noise_f32"].abs().max().item() * 2 ** -8
 
 
-@pytest.mark.parametrize("prompt_len", [0, 48, 49])
+# Bounds on the strided stage probes of a full forward, against the fp32 oracle: (relative RMS error,
+# max-abs error as a fraction of max |ref|). Cosine alone would hide one wrong row or tile edge in 10^4
+# values; a max-abs bound does not. The figures are about twice what the kernels measure.
+PROBE_BOUNDS = {"vision_x": (1.5e-2, 4e-2), "encoder_x": (1.5e-2, 4e-2), "encoder_K": (2e-2, 6e-2), "encoder_V": (2e-2, 6e-2)}
+
+
+@pytest.mark.parametrize("prompt_len", [0, 48, 49, 256])
 def test_full_forward(full_checkpoint, prompt_len):
-    """Whole pass in one CUDA graph: vision + prefix encoder + 10 decoder steps."""
+    """Whole pass in one CUDA graph: vision + prefix encoder + 10 decoder steps. Prompt 256 (prefix
+    1024, 1075 decoder keys) is the reference's second benchmark workload (benchmarks/e2e.py:8-11)."""
     from flash_vla_b200 import Pi0Inference
     from flash_vla_b200.hardware.nvidia.b200.pi0 import pipeline
     from flash_vla_b200.hardware.nvidia.b200.pi0.backends.cuda import wrappers
@@ -77,14 +88,22 @@ def test_full_forward(full_checkpoint, prompt_len):
         rows = prompt_embeds(prompt_len)[1]
         ck["language_embeds"] = torch.zeros_like(rows)           # the prompt arrives through set_prompt below
     images, state, noise = bench_inputs()
-    engine = Pi0Inference(ck, num_views=3, chunk_size=50)
+    # a small table holding the prompt's rows in shuffled order; the ids undo the shuffle
+    perm = torch.randperm(max(prompt_len, 1), generator=torch.Generator().manual_seed(9))
+    in_graph = prompt_len in (49, 256)            # these two gather inside the captured pass from a static id buffer
+    engine = Pi0Inference(ck, num_views=3, chunk_size=50, embedding_table=rows[perm] if in_graph else None)
     assert engine.encoder_seq_len == 768 + prompt_len
     if prompt_len:
-        # a small table holding the prompt's rows in shuffled order; the ids undo the shuffle
-        perm = torch.randperm(prompt_len, generator=torch.Generator().manual_seed(9))
-        engine.set_prompt(torch.argsort(perm), rows[perm])
+        if in_graph:
+            engine.set_prompt(torch.argsort(perm))
+            with pytest.raises(ValueError):
+                engine.set_prompt(torch.argsort(perm), rows[perm])
+        else:
+            engine.set_prompt(torch.argsort(perm), rows[perm])
         with pytest.raises(ValueError):
             engine.set_prompt(torch.arange(prompt_len + 1), rows)
+    with pytest.raises(ValueError):
+        engine.forward(images[:1], state, noise)           # a wrong input shape must not broadcast
     out = engine.forward(images, state, noise).clone()
     out2 = engine.forward(images, state, noise).clone()
     torch.cuda.synchronize()
@@ -99,9 +118,12 @@ def test_full_forward(full_checkpoint, prompt_len):
         if name in ("encoder_K", "encoder_V"):      # decoder rows hold the last step's K/V on both sides
             got, ref = got[:, : S // 32], ref[:, : S // 32]
         e = (got.float().cpu() - ref).abs()
-        print(f"\n[p{prompt_len}] {name}: max-abs {e.max().item():.4g}, rel-rms "
-              f"{(e.pow(2).mean().sqrt() / ref.pow(2).mean().sqrt()).item():.4g}, cos {cosine(got, ref):.6f}")
+        rel_rms = (e.pow(2).mean().sqrt() / ref.pow(2).mean().sqrt()).item()
+        rel_max = e.max().item() / ref.abs().max().item()
+        print(f"\n[p{prompt_len}] {name}: max-abs {e.max().item():.4g} ({rel_max:.4g} of max |ref|), rel-rms "
+              f"{rel_rms:.4g}, cos {cosine(got, ref):.6f}")
         assert cosine(got, ref) >= 0.999, name
+        assert rel_rms <= PROBE_BOUNDS[name][0] and rel_max <= PROBE_BOUNDS[name][1], (name, rel_rms, rel_max)
 
     cos = cosine(out, gold["actions"])
     print(f"\n[p{prompt_len}] final actions: cosine {cos:.6f}, max-abs "
@@ -156,5 +178,54 @@ def test_concurrent_episodes_match_the_single_episode_engine(full_checkpoint):
     assert torch.equal(got, got2), "two replays of the same inputs must be bit-identical"
     for e in range(E):
         assert torch.equal(got[e], want[e]), f"episode {e} differs from the single-episode engine"
+    # and every episode is right on its own inputs, not merely equal to another CUDA run: the oracle's
+    # result for the inputs of seeds 1 and 2 is a committed fixture (seed 0 is forward_p0.pt)
+    for e in range(E):
+        gold = torch.load(GOLDEN / ("forward_p0.pt" if e == 0 else f"forward_p0_seed{e}.pt"))
+        cos = cosine(got[e], gold["actions"])
+        err = (got[e].float().cpu() - gold["actions"]).abs().max().item()
+        print(f"\n[episode {e}] cosine {cos:.6f}, max-abs {err:.4g}")
+        assert cos >= FINAL_COSINE
     with pytest.raises(ValueError):
         Pi0Inference(full_checkpoint, num_views=3, chunk_size=50, episodes=0, capture=False)
+
+
+def test_engine_with_a_chunk_beyond_the_cluster_gemm(full_checkpoint):
+    """chunk_size 64 gives M = 65 decoder rows, one more than the cluster GEMM's 64 token slots: the
+    decoder GEMMs then run on the general kernels, which cannot refresh the bf16 shadow of the fp32
+    residual stream in their epilogue (a conversion kernel follows them instead). The engine must still
+    build and agree with the oracle (one step, two layers, as the reference's own bisection runs do)."""
+    from flash_vla_b200 import Pi0Inference
+    from oracle import pi0_ref as O
+
+    images, state, noise = bench_inputs(chunk_size=64)
+    engine = Pi0Inference(full_checkpoint, num_views=3, chunk_size=64, steps=1, layers=2)
+    out = engine.forward(images, state, noise).float().cpu()
+    w32 = {k: v.float() for k, v in full_checkpoint.items()}
+    ref, _ = O.forward(w32, images, state, noise, chunk_size=64, steps=1, layers=2)
+    err = (out - ref).abs().max().item()
+    print(f"\n[chunk 64] one step, two layers: max-abs {err:.4g}")
+    assert err <= STEP_MAX_ABS
+    del engine
+    torch.cuda.empty_cache()
+
+
+def test_two_devices_in_one_process(full_checkpoint):
+    """One process driving two GPUs: kernel attributes, SM counts and the status word are per device, so
+    the second engine must work as well as the first and both must match the fixture."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from flash_vla_b200 import Pi0Inference
+
+    gold = torch.load(GOLDEN / "forward_p0.pt")
+    images, state, noise = bench_inputs()
+    outs = []
+    for dev in (0, 1):
+        with torch.cuda.device(dev):
+            engine = Pi0Inference(full_checkpoint, num_views=3, chunk_size=50, device=f"cuda:{dev}")
+            outs.append(engine.forward(images, state, noise).float().cpu())
+            torch.cuda.synchronize(dev)
+            del engine
+            torch.cuda.empty_cache()
+    assert torch.equal(outs[0], outs[1])
+    assert cosine(outs[0], gold["actions"]) >= FINAL_COSINE

@@ -35,7 +35,7 @@ def test_noalloc_patch_embed_matches_the_scratch_taking_entry_point():
     stream = torch.cuda.current_stream().cuda_stream
     # two calls in a row with different sizes and data: the second one finds the first one's
     # patches still in the shared array and must not be affected by them
-    for views, seed in ((3, 1), (1, 2), (3, 3)):
+    for views, seed in ((3, 1), (1, 2), (3, 3), (4, 5)):          # 4 views fill the array exactly
         img, pw, pb, pos = _inputs(views, seed)
         want = torch.zeros(views, 256, 1152, dtype=bf16, device="cuda")
         nbytes = lib.fvla_patch_embed_workspace_bytes(views)
@@ -66,3 +66,4 @@ def test_noalloc_patch_embed_rejects_more_views_than_its_array_holds():
     assert "at most 4 views" in message
     torch.cuda.synchronize()
     assert (out == 0).all()                                     # nothing was launched
+
