@@ -272,20 +272,22 @@ inline int launch_attention(const AttnArgs& a, dim3 grid, cudaStream_t st) {
 
 
 // ---------------------------------------------------------------------------------------------
-// Decoder attention in one launch: keys split over the 8 CTAs of a thread-block cluster, partial
-// results merged through distributed shared memory (no partial buffers in global memory, no
-// second kernel). Grid = (ceil(queries / 32), 8), cluster (1, 8), 8 warps per CTA. Warp w works on
+// Decoder attention in one launch: keys split over the CTAs of a thread-block cluster (8 for up to
+// 1024 keys, one more per further 128 keys, at most 11), partial results merged through distributed
+// shared memory (no partial buffers in global memory, no second kernel). Grid = (ceil(queries / 32),
+// splits), cluster (1, splits), 8 warps per CTA. Warp w works on
 // query rows 16 (w & 1) .. + 16 of the 32-row block, key block (w >> 1) & 1 of the CTA's <= 128 keys
 // and half (w >> 2) of the head dimension: it sums Q K^T over its 128 of the 256 dimensions, swaps
 // that partial 16 x 64 score tile with the warp holding the other half (both then own the full
 // scores and run the same softmax) and multiplies P with its 128 columns of V. The two key blocks are
 // merged in shared memory, the normalised 32 x 256 partial and its log-sum-exp are staged, and rank
-// r receives rows 4r .. 4r+3 from all 8 ranks by bulk copy, combines them with log-sum-exp weights
+// r < 8 receives rows 4r .. 4r+3 from all ranks by bulk copy, combines them with log-sum-exp weights
 // in rank order and writes bf16.
 // ---------------------------------------------------------------------------------------------
 struct DecAttnArgs {
     const bf16* q; const bf16* k; const bf16* v; bf16* out;
     int nq, nk, keys_per_split;
+    int splits;                 // cluster size: CTAs sharing the keys of one 32-row query block (8..11)
     float scale_log2;
     int mask_rows, mask_key_le;
     int prefix_keys;            // keys [0, prefix_keys) were not written by the preceding kernel
@@ -294,15 +296,16 @@ struct DecAttnArgs {
 };
 
 namespace decattn {
-constexpr int HD = 256, BQ = 32, SPL = 8, PITCH = HD * 2 + 16, CH = HD / 8, THREADS = 256;
+constexpr int HD = 256, BQ = 32, MIN_SPL = 8, MAX_SPL = 11, PITCH = HD * 2 + 16, CH = HD / 8, THREADS = 256;
 constexpr int OP = HD + 8;                          // fp32 row pitch of the merge / staging buffers: rows 8 banks apart
 constexpr int SLICE = 4 * OP * 4;                   // bytes of the 4 staged rows one owner receives from one rank
 constexpr int Q_BYTES = BQ * PITCH, KV_BYTES = 128 * PITCH;
-constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + KV_BYTES, OFF_RED = OFF_V + KV_BYTES;   // RED: [src 8][4 rows][OP] fp32
-constexpr int OFF_LSE_IN = OFF_RED + SPL * SLICE;                                        // [src 8][4] fp32
-constexpr int OFF_SX = OFF_LSE_IN + SPL * 4 * 4;                                         // score swap: [warp 8][32][lane 32] fp32
+constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + KV_BYTES;
+constexpr int OFF_SX = OFF_V + KV_BYTES;                                                 // score swap: [warp 8][32][lane 32] fp32
 constexpr int OFF_BAR = OFF_SX + 8 * 32 * 32 * 4;
-constexpr int SMEM = OFF_BAR + 64;
+constexpr int OFF_RED = OFF_BAR + 64;                                                    // RED: [src spl][4 rows][OP] fp32, then LSE_IN [src spl][4] fp32
+constexpr int smem_bytes(int spl) { return OFF_RED + spl * (SLICE + 16); }
+static_assert(smem_bytes(MAX_SPL) <= 227 * 1024, "the largest cluster's receive buffers must fit in shared memory");
 // staging areas alias K (half-merge buffer) and V (final partial) once the MMAs are done
 constexpr int OFF_HALF = OFF_K;                    // [32 rows][OP] fp32 + m[32] + l[32]
 constexpr int OFF_STAGE = OFF_V;                   // [32 rows][OP] fp32 + lse[32]
@@ -322,6 +325,8 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
     const uint32_t sQ = sbase, sK = sbase + OFF_K, sV = sbase + OFF_V;
     const uint32_t in_bar = sbase + OFF_BAR;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_BAR + 16);
+    const int SPL = p.splits;
+    const int OFF_LSE_IN = OFF_RED + SPL * SLICE;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     FVLA_DBG_CTA(p, blockIdx.y * gridDim.x + blockIdx.x);
@@ -332,7 +337,7 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
     const int key_beg = (int)rank * p.keys_per_split;
     const int key_end = min(p.nk, key_beg + p.keys_per_split);
     const int rows_here = min(BQ, p.nq - q0);
-    const int owners = (rows_here + 3) / 4;
+    const int owners = (rows_here + 3) / 4;                  // at most 8: ranks beyond that only send
     const bool i_own = (int)rank < owners;
 
     if (tid == 0) {
@@ -547,11 +552,10 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
         const int row = q0 + (int)rank * 4 + r4;
         if (ok && row < p.nq) {
             float mx = -INFINITY;
-#pragma unroll
             for (int s = 0; s < SPL; ++s) mx = fmaxf(mx, lse_in[s * 4 + r4]);
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             float wsum = 0.f;
-#pragma unroll
+#pragma unroll 4
             for (int s = 0; s < SPL; ++s) {
                 const float l = lse_in[s * 4 + r4];
                 const float w = l == -INFINITY ? 0.f : exp2f(l - mx);
@@ -576,18 +580,23 @@ inline int launch_decoder_attention_cluster(const DecAttnArgs& a, bool pdl, cuda
     auto kern = decoder_attention_cluster_kernel;
     static PerDeviceFlag configured;
     if (!configured.get()) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, decattn::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, decattn::smem_bytes(decattn::MAX_SPL));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);      // clusters of 9..11
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
         configured.set();
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((a.nq + decattn::BQ - 1) / decattn::BQ, decattn::SPL, 1);
+    if (a.splits < decattn::MIN_SPL || a.splits > decattn::MAX_SPL || a.keys_per_split > 128 || a.keys_per_split * a.splits < a.nk) {
+        set_error("decoder attention: %d keys do not fit %d splits of %d", a.nk, a.splits, a.keys_per_split);
+        return FVLA_ERR_UNSUPPORTED;
+    }
+    cfg.gridDim = dim3((a.nq + decattn::BQ - 1) / decattn::BQ, a.splits, 1);
     cfg.blockDim = dim3(decattn::THREADS, 1, 1);
-    cfg.dynamicSmemBytes = decattn::SMEM;
+    cfg.dynamicSmemBytes = decattn::smem_bytes(a.splits);
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = decattn::SPL; attr[0].val.clusterDim.z = 1;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = a.splits; attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;

@@ -166,7 +166,7 @@ using namespace fvla;
 extern "C" {
 
 const char* fvla_last_error(void) { return g_error; }
-int fvla_abi_version(void) { return 1; }
+int fvla_abi_version(void) { return 2; }
 unsigned long long fvla_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int fvla_device_status(void* stream) {
@@ -332,8 +332,11 @@ int fvla_vision_linear_bias_residual(const void* x, const void* weight, const vo
 }
 
 int fvla_encoder_norm_qkv_rope(const void* x, const void* weight_qkv, const void* rope, void* Q, void* K,
-                               void* V, void* x_norm, int M, int Kdim, int heads, int head_dim, void* stream) {
+                               void* V, void* x_norm, int M, int Kdim, int heads, int head_dim, int group_rows,
+                               int kv_group_pitch, void* stream) {
     FVLA_REQUIRE(M > 64, "encoder_norm_qkv_rope: M=%d must exceed 64 (no split-K scratch is taken)", M);
+    FVLA_REQUIRE(group_rows >= 0 && (group_rows == 0 || (M % group_rows == 0 && kv_group_pitch >= group_rows)),
+                 "encoder_norm_qkv_rope: M=%d is not a whole number of sequences of %d rows (K/V pitch %d rows)", M, group_rows, kv_group_pitch);
     int rc = rownorm(x, 0, nullptr, nullptr, x_norm, nullptr, nullptr, M, Kdim, 1, S(stream));
     if (rc) return rc;
     GemmArgs a;
@@ -341,6 +344,7 @@ int fvla_encoder_norm_qkv_rope(const void* x, const void* weight_qkv, const void
     a.M = M; a.N = (heads + 2) * head_dim; a.K = Kdim;
     a.rope = B(rope); a.q = Bm(Q); a.k = Bm(K); a.v = Bm(V); a.heads = heads; a.head_dim = head_dim;
     a.round_first = 1;
+    a.group_rows = group_rows; a.kv_group_pitch = kv_group_pitch;
     a.trigger_early = 1;      // the next kernel (prefix attention / down projection) runs one CTA per SM
     return launch_gemm(a, nullptr, 0, S(stream));
 }
@@ -515,10 +519,11 @@ int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* ou
         set_error("decoder_attention: workspace of %zu bytes needed", fvla_decoder_attention_workspace_bytes(queries, keys));
         return FVLA_ERR_WORKSPACE;
     }
-    if (tc5_enabled() && keys <= 1024) {        // cluster kernel: 8 key splits of at most 128 keys
+    if (tc5_enabled() && keys <= decattn::MAX_SPL * 128) {        // cluster kernel: 8..11 key splits of at most 128 keys
         DecAttnArgs d{};
         d.q = B(Q); d.k = B(K); d.v = B(V); d.out = Bm(out);
-        d.nq = queries; d.nk = keys; d.keys_per_split = ((keys + 7) / 8 + 7) / 8 * 8;
+        d.splits = (keys + 127) / 128 < decattn::MIN_SPL ? decattn::MIN_SPL : (keys + 127) / 128;
+        d.nq = queries; d.nk = keys; d.keys_per_split = ((keys + d.splits - 1) / d.splits + 7) / 8 * 8;
         d.scale_log2 = kLog2e / sqrtf((float)head_dim);
         d.mask_rows = heads; d.mask_key_le = encoder_seq_len; d.prefix_keys = encoder_seq_len;
         d.status = device_status_ptr(); FVLA_DBG_ATTACH(d);
@@ -575,20 +580,6 @@ int fvla_decoder_action_out_proj(const void* x, int x_is_f32, const void* weight
         e = launch_pdl(action_out_kernel<bf16, bf16>, dim3(M), dim3(256), 0, st, B(x), B(weight), B(bias), Bm(out), Bm(mirror), Bm(norm_factor), K);
     if (e != cudaSuccess) { set_error("action_out_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("action_out_kernel");
-}
-
-int fvla_l2_prefetch(const void* const* ptrs, const size_t* bytes, int count, void* stream) {
-    FVLA_REQUIRE(count > 0 && count <= 8 && ptrs != nullptr && bytes != nullptr, "l2_prefetch: 1..8 ranges, got %d", count);
-    PrefetchArgs a;
-    a.count = count;
-    for (int i = 0; i < count; ++i) {
-        FVLA_REQUIRE(ptrs[i] != nullptr && aligned16(ptrs[i]), "l2_prefetch: range %d is null or not 16-byte aligned", i);
-        a.ptr[i] = static_cast<const uint8_t*>(ptrs[i]);
-        a.bytes[i] = bytes[i];
-    }
-    a.mode = 0; a.chunk = 8192;
-    l2_prefetch_kernel<<<148, 32, 0, S(stream)>>>(a);
-    return check_launch("l2_prefetch_kernel");
 }
 
 int fvla_embed_rows(const void* table, const long long* ids, void* out, int rows, int dim, long long vocab, void* stream) {

@@ -26,6 +26,11 @@ struct GemmArgs {
     // RoPE + scatter epilogue (used when rope != nullptr; C is ignored)
     const bf16* rope = nullptr; bf16* q = nullptr; bf16* k = nullptr; bf16* v = nullptr;
     int heads = 0, head_dim = 0, round_first = 0;
+    // Rows may be several sequences of `group_rows` tokens laid end to end (a batch of episodes): the RoPE
+    // entry of a row is then that of its position inside its sequence, and sequence g's K / V rows go to
+    // rows [g * kv_group_pitch, + group_rows) of the K / V destinations (each sequence's cache also holds
+    // rows this GEMM does not write). group_rows = 0: one sequence, contiguous K / V.
+    int group_rows = 0, kv_group_pitch = 0;
     // split-K
     int splits = 1, k_per_split = 0; float* partial = nullptr; int* counters = nullptr;
     // Programmatic dependent launch: 1 = let the next kernel be scheduled once this CTA's last
@@ -34,6 +39,11 @@ struct GemmArgs {
     // norm, SigLIP attention) would be packed onto the few SMs that are idle at that moment.
     int trigger_early = 0;
 };
+
+__device__ __forceinline__ int rope_row(const GemmArgs& p, int row) { return p.group_rows > 0 ? row % p.group_rows : row; }
+__device__ __forceinline__ size_t kv_row(const GemmArgs& p, int row) {
+    return p.group_rows > 0 ? (size_t)(row / p.group_rows) * p.kv_group_pitch + row % p.group_rows : (size_t)row;
+}
 
 // Residual values of one (row, col..col+1) pair. Loaded for every fragment BEFORE any store of
 // the epilogue: the residual may alias the destination, so the compiler cannot move a load above
@@ -67,12 +77,12 @@ __device__ __forceinline__ void gemm_epilogue_pair(const GemmArgs& p, int row, i
         if (col < qd + hd) {
             if (p.round_first) { a0 = round_bf16(a0); a1 = round_bf16(a1); }
             float2 cs = unpack_bf16x2(
-                __ldg(reinterpret_cast<const uint32_t*>(p.rope + (size_t)row * hd + (col % hd))));
+                __ldg(reinterpret_cast<const uint32_t*>(p.rope + (size_t)rope_row(p, row) * hd + (col % hd))));
             float r0 = a0 * cs.x - a1 * cs.y, r1 = a1 * cs.x + a0 * cs.y;
             a0 = r0; a1 = r1;
-            dst = col < qd ? p.q + (size_t)row * qd + col : p.k + (size_t)row * hd + (col - qd);
+            dst = col < qd ? p.q + (size_t)row * qd + col : p.k + kv_row(p, row) * hd + (col - qd);
         } else {
-            dst = p.v + (size_t)row * hd + (col - qd - hd);
+            dst = p.v + kv_row(p, row) * hd + (col - qd - hd);
         }
         *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(a0, a1);
         return;

@@ -187,7 +187,7 @@ __device__ __forceinline__ void epilogue8(const GemmArgs& p, int row, int col, f
     if (p.rope) {
         const int hd = p.head_dim, qd = p.heads * hd;
         if (col < qd + hd) {
-            uint4 cs = __ldg(reinterpret_cast<const uint4*>(p.rope + (size_t)row * hd + (col % hd)));
+            uint4 cs = __ldg(reinterpret_cast<const uint4*>(p.rope + (size_t)rope_row(p, row) * hd + (col % hd)));
             const uint32_t csw[4] = {cs.x, cs.y, cs.z, cs.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -197,9 +197,9 @@ __device__ __forceinline__ void epilogue8(const GemmArgs& p, int row, int col, f
                 a[2 * i] = x0 * c.x - x1 * c.y;
                 a[2 * i + 1] = x1 * c.x + x0 * c.y;
             }
-            dst = col < qd ? p.q + (size_t)row * qd + col : p.k + (size_t)row * hd + (col - qd);
+            dst = col < qd ? p.q + (size_t)row * qd + col : p.k + kv_row(p, row) * hd + (col - qd);
         } else {
-            dst = p.v + (size_t)row * hd + (col - qd - hd);
+            dst = p.v + kv_row(p, row) * hd + (col - qd - hd);
         }
     } else if (p.c_f32) {
         float4* d = reinterpret_cast<float4*>(static_cast<float*>(p.C) + (size_t)row * p.ldc + col);
@@ -403,7 +403,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                     const int grow = m0 + quad * 32 + sr + 8 * i, gcol = n0 + c * 32 + sp * 8;
                     if (ROPE && plain && p.rope) {
                         if (grow < p.M && gcol < rope_qd + p.head_dim)
-                            rco[c][i] = __ldg(reinterpret_cast<const uint4*>(p.rope + (size_t)grow * p.head_dim + (gcol % p.head_dim)));
+                            rco[c][i] = __ldg(reinterpret_cast<const uint4*>(p.rope + (size_t)rope_row(p, grow) * p.head_dim + (gcol % p.head_dim)));
                     } else if (plain && p.R && grow < p.M && gcol < p.N) {
                         const int rr = p.res_mod > 0 ? grow % p.res_mod : grow;
                         rco[c][i] = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.R) + (size_t)rr * p.ldr + gcol);
@@ -553,6 +553,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                     const int col0 = n0 + c * 32;                  // first column of this chunk
                     bf16* out_base = static_cast<bf16*>(p.C);
                     int out_ld = p.ldc, out_col = col0;
+                    bool kv_dst = false;                           // K / V destination: rows follow the sequence-group mapping
                     if (ROPE && p.rope) {
                         // res[] holds this row's 16 (cos, sin) pairs for the chunk's 16 column pairs
                         if (col0 < rope_qd + p.head_dim) {
@@ -565,8 +566,8 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                             }
                         }
                         if (col0 < rope_qd) { out_base = p.q; out_ld = rope_qd; }
-                        else if (col0 < rope_qd + p.head_dim) { out_base = p.k; out_ld = p.head_dim; out_col = col0 - rope_qd; }
-                        else { out_base = p.v; out_ld = p.head_dim; out_col = col0 - rope_qd - p.head_dim; }
+                        else if (col0 < rope_qd + p.head_dim) { out_base = p.k; out_ld = p.head_dim; out_col = col0 - rope_qd; kv_dst = true; }
+                        else { out_base = p.v; out_ld = p.head_dim; out_col = col0 - rope_qd - p.head_dim; kv_dst = true; }
                     } else if (p.act == 1) finish([](float v) { return gelu_f(v); });
                     else if (p.act == 2) finish([](float v) { return silu_f(v); });
                     else finish([](float v) { return v; });
@@ -580,7 +581,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                     for (int i = 0; i < 4; ++i) {
                         const int grow = m0 + quad * 32 + sr + 8 * i, gcol = n0 + c * 32 + sp * 8;
                         if (grow < p.M && gcol < p.N)
-                            *reinterpret_cast<uint4*>(out_base + (size_t)grow * out_ld + out_col + sp * 8) =
+                            *reinterpret_cast<uint4*>(out_base + (kv_dst ? kv_row(p, grow) : (size_t)grow) * out_ld + out_col + sp * 8) =
                                 *reinterpret_cast<const uint4*>(stg + (sr + 8 * i) * 80 + sp * 16);
                     }
                     __syncwarp();

@@ -192,25 +192,6 @@ __global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* __restric
     reinterpret_cast<uint2*>(dst)[i] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
 }
 
-// Pulls up to 8 byte ranges from HBM into L2 without touching any SM-side storage: every thread
-// issues bulk L2 prefetches for 8 KB pieces. Meant to run on a side stream next to the decoder, whose
-// weight-streaming GEMMs then find the next layer's weights in L2 instead of waiting on HBM.
-struct PrefetchArgs { const uint8_t* ptr[8]; unsigned long long bytes[8]; int count; int mode; unsigned long long chunk; };
-__global__ void __launch_bounds__(256) l2_prefetch_kernel(const PrefetchArgs a) {
-    const unsigned long long CH = a.chunk;
-    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
-    for (int r = 0; r < a.count; ++r) {
-        const unsigned long long n = (a.bytes[r] + CH - 1) / CH;
-        for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-            const unsigned long long off = i * CH;
-            const unsigned long long left = a.bytes[r] - off;
-            const uint32_t sz = (uint32_t)(left < CH ? (left & ~15ull) : CH);      // whole 16-byte units only
-            if (a.mode == 0) { if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.ptr[r] + off), "r"(sz) : "memory"); }
-            else { for (uint32_t b = 0; b < sz; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.ptr[r] + off + b) : "memory"); }
-        }
-    }
-}
-
 // out[r, :] = table[ids[r], :] for bf16 rows of `dim` elements (dim % 8 == 0): the prompt embedding
 // lookup. One CTA per row, 16-byte copies. An id outside [0, vocab) yields a zero row and sets the device
 // status word, so a bad prompt is reported instead of reading out of bounds.

@@ -22,7 +22,7 @@ SIGNATURES: dict[str, list] = {
     "fvla_vision_linear_bias_residual": [_P, _P, _P, _P, _P, _I, _I, _I, _P, _Z, _P],
     "fvla_vision_norm_ffn_up": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fvla_encoder_projector": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
-    "fvla_encoder_norm_qkv_rope": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "fvla_encoder_norm_qkv_rope": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "fvla_encoder_attention": [_P, _P, _P, _P, _I, _I, _I, _F, _P, _Z, _P],
     "fvla_linear_residual": [_P, _P, _P, _I, _P, _I, _I, _I, _P, _Z, _P],
     "fvla_encoder_norm_gated_ffn": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
@@ -31,7 +31,6 @@ SIGNATURES: dict[str, list] = {
     "fvla_decoder_attention": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _Z, _P],
     "fvla_decoder_norm_gated_ffn": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _Z, _P],
     "fvla_decoder_action_out_proj": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
-    "fvla_l2_prefetch": [ctypes.POINTER(c_void_p), ctypes.POINTER(c_size_t), _I, _P],
     "fvla_embed_rows": [_P, _P, _P, _I, _I, ctypes.c_longlong, _P],
     "fvla_selftest_wait_timeout": [_P, _P, _P, _I, _I, _I, ctypes.c_uint, _P],
 }

@@ -96,46 +96,6 @@ def sync_shadow(t: torch.Tensor) -> None:
         shadow.view(-1)[first:first + t.numel()].copy_(t.reshape(-1))
 
 
-# Side stream on which `prefetch_l2` runs, per device, and whether work on it still has to be joined.
-_PREFETCH: dict = {"streams": {}, "pending": None}
-
-
-def prefetch_l2(*tensors: torch.Tensor) -> None:
-    """Start pulling `tensors` (up to 8, contiguous) into L2 on a side stream, ordered after the work
-    already enqueued on the current stream. The decoder calls this one layer ahead of its weight reads.
-    Legal during stream capture (the side stream joins the capture); `join_prefetch` must follow."""
-    import ctypes
-    if not tensors:
-        return
-    main = torch.cuda.current_stream()
-    dev = tensors[0].device
-    side = _PREFETCH["streams"].get(dev.index)
-    if side is None:
-        side = _PREFETCH["streams"][dev.index] = torch.cuda.Stream(device=dev)
-    fork = torch.cuda.Event()
-    fork.record(main)
-    side.wait_event(fork)
-    n = len(tensors)
-    ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in tensors])
-    sizes = (ctypes.c_size_t * n)(*[t.numel() * t.element_size() for t in tensors])
-    for t in tensors:
-        if not t.is_contiguous():
-            raise ValueError("prefetch_l2: tensors must be contiguous")
-    _lib.call("fvla_l2_prefetch", ptrs, sizes, n, side.cuda_stream)
-    _PREFETCH["pending"] = side
-
-
-def join_prefetch() -> None:
-    """Make the current stream wait for the side-stream prefetches issued so far."""
-    side = _PREFETCH["pending"]
-    if side is None:
-        return
-    done = torch.cuda.Event()
-    done.record(side)
-    torch.cuda.current_stream().wait_event(done)
-    _PREFETCH["pending"] = None
-
-
 def embed_prompt(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[r] = table[ids[r]]: the prompt embedding lookup (a plain row gather, no scaling). Not in the
     reference table, which only accepts precomputed `language_embeds` (engine.py:43, :60)."""
@@ -262,14 +222,38 @@ def encoder_projector(x, norm_w, norm_b, proj_w, proj_b, out, x_norm):
     return _norm_linear("fvla_encoder_projector", x, norm_w, norm_b, proj_w, proj_b, out, x_norm)
 
 
+def _kv_destination(name: str, t: torch.Tensor, M: int, hd: int):
+    """K / V destination of the prefix QKV projection as (address, sequence rows, pitch in rows).
+    2-D (M, hd) contiguous: one sequence. 3-D (sequences, rows, hd) whose (rows, hd) blocks are contiguous
+    and evenly spaced: a batch of episodes, each block being the prefix rows of that episode's cache."""
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != torch.bfloat16:
+        raise ValueError(f"{name}: expected a bf16 CUDA tensor")
+    if t.ndim == 2:
+        return _chk(name, t, (M, hd)), 0, 0
+    if t.ndim != 3 or t.shape[2] != hd or t.shape[0] * t.shape[1] != M or t.stride(2) != 1 or t.stride(1) != hd \
+            or t.stride(0) % hd or t.stride(0) < t.shape[1] * hd:
+        raise ValueError(f"{name}: expected (M, hd) or evenly spaced (sequences, rows, hd) blocks, got shape "
+                         f"{tuple(t.shape)} strides {t.stride()}")
+    return t.data_ptr(), t.shape[1], t.stride(0) // hd
+
+
 def encoder_norm_qkv_rope(x, weight_qkv, rope, Q, K, V, x_norm):
-    """RMS norm, QKV projection rounded to bf16, RoPE, scatter to Q/K/V (wrappers.py:347-363)."""
+    """RMS norm, QKV projection rounded to bf16, RoPE, scatter to Q/K/V (wrappers.py:347-363).
+
+    Extension for batches of episodes: when K and V are 3-D views (episodes, S, hd) of the episodes' caches,
+    x holds the episodes' S-row sequences end to end, `rope` is the table of ONE sequence, and each episode's
+    K / V rows land in its own cache."""
     M, Kdim = x.shape
-    hd = V.shape[1]
+    hd = V.shape[-1]
     heads = Q.shape[0] // M
+    k_ptr, group, pitch = _kv_destination("K", K, M, hd)
+    v_ptr, group_v, pitch_v = _kv_destination("V", V, M, hd)
+    if (group, pitch) != (group_v, pitch_v):
+        raise ValueError("encoder_norm_qkv_rope: K and V must have the same layout")
+    rope_rows = group or M
     _lib.call("fvla_encoder_norm_qkv_rope", _chk("x", x), _chk("weight_qkv", weight_qkv, (Kdim, (heads + 2) * hd)),
-              _chk("rope", rope[:M], (M, hd)), _chk("Q", Q, (M * heads, hd)), _chk("K", K, (M, hd)),
-              _chk("V", V, (M, hd)), _chk("x_norm", x_norm[:M], (M, Kdim)), M, Kdim, heads, hd, _stream())
+              _chk("rope", rope[:rope_rows], (rope_rows, hd)), _chk("Q", Q, (M * heads, hd)), k_ptr, v_ptr,
+              _chk("x_norm", x_norm[:M], (M, Kdim)), M, Kdim, heads, hd, group, pitch, _stream())
 
 
 def encoder_attention(Q, K, V, scale, out):
@@ -431,4 +415,4 @@ DECODER_WRAPPERS = {f.__name__: f for f in (
 
 # `sync_shadow` rides in the table so that orchestration code can reach it through `ops`.
 ALL_WRAPPERS = {**VISION_WRAPPERS, **ENCODER_WRAPPERS, **DECODER_WRAPPERS, "sync_shadow": sync_shadow,
-                "prefetch_l2": prefetch_l2, "join_prefetch": join_prefetch, "embed_prompt": embed_prompt}
+                "embed_prompt": embed_prompt}

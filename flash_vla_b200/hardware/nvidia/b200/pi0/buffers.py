@@ -37,6 +37,78 @@ def rope_table(seq_len: int, offset: int, head_dim: int, device) -> torch.Tensor
     return table.reshape(seq_len, head_dim)
 
 
+def _prefix_plan(add, num_views: int, S: int, cache: int, episodes: int) -> None:
+    """Buffers of SigLIP and the prefix encoder for `episodes` sequences of S tokens laid end to end."""
+    E = episodes
+    add("observation_images_normalized", E * num_views, 224, 224, 3)
+    for name, width in (("vision_x", VISION_DIM), ("vision_x_norm", VISION_DIM),
+                        ("vision_QKV", 3 * VISION_DIM), ("vision_attn", VISION_DIM),
+                        ("vision_hidden", VISION_FFN)):
+        add(name, E * num_views, VISION_TOKENS, width)
+    add("encoder_rope_weights", S, HEAD_DIM)
+    add("encoder_x", E * S, ENCODER_DIM)
+    add("encoder_x_norm", E * S, ENCODER_DIM)
+    if E == 1:
+        add("encoder_K", ENCODER_LAYERS, cache, HEAD_DIM)
+        add("encoder_V", ENCODER_LAYERS, cache, HEAD_DIM)
+    else:
+        add("encoder_K", E, ENCODER_LAYERS, cache, HEAD_DIM)
+        add("encoder_V", E, ENCODER_LAYERS, cache, HEAD_DIM)
+    add("encoder_Q", E * S * DECODER_HEADS, HEAD_DIM)
+    add("encoder_attn", E * S, DECODER_HEADS * HEAD_DIM)
+    add("encoder_hidden", E * S, ENCODER_FFN)
+
+
+def _decoder_plan(add, chunk_size: int, cache: int) -> None:
+    D = chunk_size + 1
+    add("observation_state_normalized", ACTION_DIM)
+    add("diffusion_noise", chunk_size, ACTION_DIM)
+    add("diffusion_noise_f32", chunk_size, ACTION_DIM, dtype=torch.float32)
+    add("decoder_rope_weights", D, HEAD_DIM)
+    add("decoder_x", D, DECODER_DIM, dtype=torch.float32)
+    add("decoder_x_bf16", D, DECODER_DIM)
+    add("decoder_x_buf", chunk_size, DECODER_DIM)
+    add("decoder_state_buf", 1, DECODER_DIM)
+    add("decoder_norm_factor_buf", D)
+    add("decoder_q_buf", D * DECODER_HEADS, HEAD_DIM)
+    add("decoder_attn_buf", D * DECODER_HEADS, cache)
+    add("decoder_hidden", D, DECODER_FFN)
+
+
+def _materialise(plan, device):
+    return {name: torch.zeros(shape, dtype=dtype, device=device) for name, (shape, dtype) in plan.items()}
+
+
+def allocate_batched_buffers(num_views: int, chunk_size: int, prompt_len: int, episodes: int, device: str):
+    """Buffer plan of the throughput profile: `episodes` independent episodes whose SigLIP tower and prefix
+    encoder run as ONE pass over all episodes' tokens (M = episodes x S rows, so every vision and prefix
+    weight is streamed once for the whole batch) while each episode keeps its own KV cache and decoder
+    buffers. Returns (prefix, [decoder buffers per episode], S): `prefix` holds the batched tensors;
+    every per-episode dict also carries views `encoder_K` / `encoder_V` (18, S + D, 256) of its own cache
+    and `observation_images_normalized` of its own views, so the decoder ops see the single-episode layout."""
+    S = num_views * VISION_TOKENS + prompt_len
+    D = chunk_size + 1
+    cache = S + D
+    plan: dict[str, tuple[tuple[int, ...], torch.dtype]] = {}
+
+    def add(name, *shape, dtype=torch.bfloat16):
+        plan[name] = (shape, dtype)
+
+    _prefix_plan(add, num_views, S, cache, episodes)
+    prefix = _materialise(plan, device)
+    prefix["encoder_rope_weights"].copy_(rope_table(S, 0, HEAD_DIM, device))
+    per_episode = []
+    for e in range(episodes):
+        plan.clear()
+        _decoder_plan(add, chunk_size, cache)
+        b = _materialise(plan, device)
+        b["decoder_rope_weights"].copy_(rope_table(D, S, HEAD_DIM, device))
+        b["encoder_K"], b["encoder_V"] = prefix["encoder_K"][e], prefix["encoder_V"][e]
+        b["observation_images_normalized"] = prefix["observation_images_normalized"][e * num_views:(e + 1) * num_views]
+        per_episode.append(b)
+    return prefix, per_episode, S
+
+
 def allocate_static_buffers(num_views: int, chunk_size: int, prompt_len: int,
                             device: str) -> tuple[dict[str, torch.Tensor], int]:
     """Allocate every persistent buffer and fill the two RoPE tables. Returns (buffers, S)."""

@@ -6,11 +6,18 @@ all decoder steps into a single graph on a side stream. `forward` copies the thr
 their static buffers and replays. Public surface and life cycle follow the reference engine
 (`.../h100/pi0/engine.py:26-86`).
 
-`episodes=E > 1` is the throughput profile: E independent episodes share the weights, each has its own
-static buffers and scratch pool, and the captured graph forks into E streams, one pass each, and joins
-again. The decoder's kernels are latency-bound at batch 1 and leave SMs idle; running episodes side by
-side fills them. Every episode runs exactly the kernels of the single-episode engine, so its result is
-bit-identical to that engine's.
+`episodes=E > 1` is the throughput profile, a separate execution plan for a batch of E independent
+episodes that share the weights:
+  * SigLIP and the prefix encoder run ONCE over all episodes' tokens (M = E x S rows): every vision and
+    prefix weight (4.8 of the 5.4 GB) is streamed once for the whole batch and the GEMMs have E times
+    the tiles to fill the GPU with; only the attention kernels, which mix tokens, run per episode;
+  * each episode has its own KV cache and decoder buffers, and the E action-expert decoders run on E
+    streams inside the captured graph, side by side: their kernels are latency-bound at batch 1 and
+    leave SMs idle, which concurrent episodes fill. Decoder layer L of every episode starts as soon as
+    the batched encoder has produced layer L's prefix K/V.
+`batch_prefix=False` keeps the older form (E complete single-episode passes on E streams), whose
+per-episode results are bit-identical to the single-episode engine; the batched form runs the same
+per-row arithmetic but through differently shaped GEMM launches, so it agrees to rounding.
 """
 from __future__ import annotations
 
@@ -21,7 +28,7 @@ from flash_vla_b200.runtime.cuda import ScratchPool
 
 from . import pipeline
 from .backends.cuda import wrappers
-from .buffers import allocate_static_buffers
+from .buffers import allocate_batched_buffers, allocate_static_buffers
 from .ops import op_table
 
 
@@ -35,7 +42,8 @@ class Pi0Inference:
 
     def __init__(self, checkpoint, num_views: int, chunk_size: int, steps: int = 10,
                  layers: int = 18, fused: bool = True, device: str = "cuda", plan=None,
-                 capture: bool = True, episodes: int = 1, overlap: bool = True, embedding_table=None):
+                 capture: bool = True, episodes: int = 1, overlap: bool = True, embedding_table=None,
+                 batch_prefix: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("Pi0Inference needs a CUDA device; the B200 target has no CPU path")
         if episodes < 1:
@@ -47,11 +55,6 @@ class Pi0Inference:
         # (decoder layer L only needs the prefix K/V of encoder layer L); same kernels, same results
         self.overlap = bool(overlap) and steps >= 1
         self.ops = op_table(fused, plan=plan)
-        if episodes > 1:
-            # the weight prefetch hint owns one side stream per device; concurrent episodes would contend for it
-            for name in ("prefetch_l2", "join_prefetch"):
-                if hasattr(self.ops, name):
-                    delattr(self.ops, name)
         self.prompt_len = int(checkpoint["language_embeds"].shape[0])
         # With an embedding table the prompt lookup is part of the captured pass: the graph gathers
         # table[prompt_ids] straight into the prefix rows, and `set_prompt(ids)` only rewrites the ids.
@@ -75,12 +78,30 @@ class Pi0Inference:
                 raise ValueError(f"checkpoint[{name!r}] has shape {tuple(value.shape)}, expected {shape}")
             self.weights[name] = value.to(device=device, dtype=torch.bfloat16).contiguous()
         self.episode_buffers, self.pools = [], []
-        for _ in range(episodes):
-            buffers, self.encoder_seq_len = allocate_static_buffers(num_views, chunk_size, self.prompt_len, device)
-            wrappers.register_bf16_shadow(buffers["decoder_x"], buffers["decoder_x_bf16"])
-            self.episode_buffers.append(buffers)
-            self.pools.append(ScratchPool())
-        if episodes > 1:
+        self.batch_prefix = bool(batch_prefix) and episodes > 1
+        self.prefix_buffers, self.prefix_pool = None, None
+        if self.batch_prefix:
+            self.prefix_buffers, self.episode_buffers, self.encoder_seq_len = allocate_batched_buffers(
+                num_views, chunk_size, self.prompt_len, episodes, device)
+            self.prefix_pool = ScratchPool()
+            for buffers in self.episode_buffers:
+                wrappers.register_bf16_shadow(buffers["decoder_x"], buffers["decoder_x_bf16"])
+                self.pools.append(ScratchPool())
+            for name in ("observation_state_normalized", "diffusion_noise"):
+                batched = torch.zeros((episodes,) + tuple(self.episode_buffers[0][name].shape), dtype=torch.bfloat16, device=device)
+                for e, b in enumerate(self.episode_buffers):
+                    b[name] = batched[e]
+                setattr(self, "_batched_" + name, batched)
+            self._batched_observation_images_normalized = self.prefix_buffers["observation_images_normalized"].view(
+                episodes, num_views, 224, 224, 3)
+            self.streams = [torch.cuda.Stream(device=device) for _ in range(episodes)]
+        else:
+            for _ in range(episodes):
+                buffers, self.encoder_seq_len = allocate_static_buffers(num_views, chunk_size, self.prompt_len, device)
+                wrappers.register_bf16_shadow(buffers["decoder_x"], buffers["decoder_x_bf16"])
+                self.episode_buffers.append(buffers)
+                self.pools.append(ScratchPool())
+        if episodes > 1 and not self.batch_prefix:
             # inputs and the result of all episodes live in three batched tensors, so `forward` stays three copies
             for name in ("observation_images_normalized", "observation_state_normalized", "diffusion_noise"):
                 batched = torch.zeros((episodes,) + tuple(self.episode_buffers[0][name].shape), dtype=torch.bfloat16, device=device)
@@ -88,7 +109,7 @@ class Pi0Inference:
                     b[name] = batched[e]
                 setattr(self, "_batched_" + name, batched)
             self.streams = [torch.cuda.Stream(device=device) for _ in range(episodes)]
-        self.decoder_streams = [torch.cuda.Stream(device=device) for _ in range(episodes)] if self.overlap else []
+        self.decoder_streams = [torch.cuda.Stream(device=device) for _ in range(episodes)] if self.overlap and not self.batch_prefix else []
         self.buffers, self.pool = self.episode_buffers[0], self.pools[0]
         self.graph = None
         if capture:
@@ -116,14 +137,51 @@ class Pi0Inference:
                                          after_qkv=lambda layer: kv_ready[layer].record(main))
             with torch.cuda.stream(side):
                 pipeline.decoder_step(self.ops, self.weights, b, self.encoder_seq_len, 0, self.layers,
-                                      noise=b.get("diffusion_noise_f32"), prefetch_next_step=self.steps > 1,
+                                      noise=b.get("diffusion_noise_f32"),
                                       before_layer=lambda layer: side.wait_event(kv_ready[layer]))
             main.wait_stream(side)
             pipeline.transformer_decoder(self.ops, self.weights, b, self.encoder_seq_len,
                                          steps=self.steps, layers=self.layers, first_step=1)
 
+    def _run_batched(self):
+        """The throughput plan: one SigLIP + prefix-encoder pass over all episodes' rows on the current stream,
+        the episodes' decoders on one stream each, every decoder layer gated on the batched encoder's K/V."""
+        E, S, p = self.episodes, self.encoder_seq_len, self.prefix_buffers
+        main = torch.cuda.current_stream()
+        if self.prompt_len:
+            for e in range(E):
+                rows = p["encoder_x"][e * S + self.num_views * 256:(e + 1) * S]
+                if self.embedding_table is not None:
+                    self.ops.embed_prompt(self.embedding_table, self.prompt_ids, rows)
+                else:
+                    rows.copy_(self.weights["language_embeds"])
+        for e, stream in enumerate(self.streams):               # what the decoders can do before any K/V exists
+            stream.wait_stream(main)
+            with torch.cuda.stream(stream), wrappers.use_pool(self.pools[e]):
+                pipeline.decoder_prologue(self.ops, self.weights, self.episode_buffers[e])
+        kv_ready = [torch.cuda.Event() for _ in range(pipeline.ENCODER_LAYERS)]
+        with wrappers.use_pool(self.prefix_pool):
+            pipeline.vision_encoder(self.ops, self.weights, p, self.num_views)
+            pipeline.transformer_encoder_batched(self.ops, self.weights, p, S, self.num_views, E,
+                                                 after_qkv=lambda layer: kv_ready[layer].record(main))
+        for e, stream in enumerate(self.streams):
+            b = self.episode_buffers[e]
+            with torch.cuda.stream(stream), wrappers.use_pool(self.pools[e]):
+                if self.steps >= 1:
+                    pipeline.decoder_step(self.ops, self.weights, b, S, 0, self.layers, noise=b.get("diffusion_noise_f32"),
+                                          before_layer=lambda layer, st=stream: st.wait_event(kv_ready[layer]))
+                else:
+                    stream.wait_event(kv_ready[-1])
+                pipeline.transformer_decoder(self.ops, self.weights, b, S, steps=self.steps, layers=self.layers,
+                                             first_step=min(1, self.steps))
+        for stream in self.streams:
+            main.wait_stream(stream)
+
     def _run(self):
         """One full pass per episode, in place on the static buffers; episodes run on streams of their own."""
+        if self.batch_prefix:
+            self._run_batched()
+            return
         if self.episodes == 1:
             self._run_episode(0)
             return
@@ -140,7 +198,7 @@ class Pi0Inference:
         for _ in range(3):
             self._run()
         torch.cuda.synchronize()
-        for pool in self.pools:
+        for pool in self.pools + ([self.prefix_pool] if self.prefix_pool is not None else []):
             pool.freeze()
         self.graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()

@@ -8,8 +8,6 @@ all on the B200 side of the drop-in boundary:
     `ops.encoder_attention`) into preallocated buffers instead of being torch calls.
   * When the buffer plan holds `diffusion_noise_f32`, the Euler updates accumulate in it and
     the bf16 `diffusion_noise` is refreshed once at the end of the decoder.
-  * When the table offers `prefetch_l2`, the decoder asks for the next layer's weights and prefix K/V
-    one layer ahead (a hint on a side stream; results do not depend on it).
 """
 from __future__ import annotations
 
@@ -18,7 +16,9 @@ from flash_vla_b200.models.pi0.spec import (DECODER_HEADS, DIFFUSION_STEPS, ENCO
 
 
 def vision_encoder(ops, weights, buffers, num_views):
-    """Patch-embed the views and run the 27 SigLIP layers in place on `vision_x`."""
+    """Patch-embed the views and run the 27 SigLIP layers in place on `vision_x`. The buffers may hold the
+    views of several episodes back to back (`num_views` is the count per episode): every op of the tower
+    works per view or per token, so a batch is simply more rows."""
     if num_views == 2:
         raise NotImplementedError("num_views == 2 is not supported (as in the reference, pipeline.py:23)")
     w, b = weights, buffers
@@ -66,18 +66,39 @@ def transformer_encoder(ops, weights, buffers, encoder_seq_len, after_qkv=None):
         ops.encoder_ffn_down_residual(b["encoder_hidden"], w["encoder_ffn_down_w"][layer], x)
 
 
-_DECODER_LAYER_WEIGHTS = ("decoder_attn_qkv_w", "decoder_attn_o_w", "decoder_ffn_gate_w", "decoder_ffn_up_w",
-                          "decoder_ffn_down_w")
-
-
-def _prefetch_decoder_layer(ops, weights, buffers, layer):
-    if hasattr(ops, "prefetch_l2"):
-        ops.prefetch_l2(*[weights[name][layer] for name in _DECODER_LAYER_WEIGHTS],
-                        buffers["encoder_K"][layer], buffers["encoder_V"][layer])
+def transformer_encoder_batched(ops, weights, buffers, encoder_seq_len, num_views, episodes, after_qkv=None):
+    """The prefix encoder over `episodes` sequences of `encoder_seq_len` tokens laid end to end in the batched
+    buffers (`allocate_batched_buffers`): every projection runs once over all rows, so its weights are
+    streamed once for the whole batch; attention, which mixes tokens, runs per episode. K / V of layer L go
+    straight into rows [0, S) of every episode's cache. Same ops and call order per layer as
+    `transformer_encoder`."""
+    w, b, S, E = weights, buffers, encoder_seq_len, episodes
+    x = b["encoder_x"]
+    for e in range(E):
+        views = slice(e * num_views, (e + 1) * num_views)
+        ops.encoder_projector(b["vision_x"][views], w["vision_final_norm_w"], w["vision_final_norm_b"],
+                              w["encoder_multi_modal_projector_w"], w["encoder_multi_modal_projector_b"],
+                              x[e * S:(e + 1) * S], b["vision_x_norm"][views])
+    for layer in range(ENCODER_LAYERS):
+        k_prefix, v_prefix = b["encoder_K"][:, layer, :S], b["encoder_V"][:, layer, :S]      # (E, S, 256) views
+        ops.encoder_norm_qkv_rope(x, w["encoder_attn_qkv_w"][layer], b["encoder_rope_weights"],
+                                  b["encoder_Q"], k_prefix, v_prefix, b["encoder_x_norm"])
+        if after_qkv is not None:
+            after_qkv(layer)
+        if layer == ENCODER_LAYERS - 1:
+            return
+        for e in range(E):
+            rows = slice(e * S, (e + 1) * S)
+            ops.encoder_attention(b["encoder_Q"][e * S * DECODER_HEADS:(e + 1) * S * DECODER_HEADS], k_prefix[e], v_prefix[e],
+                                  HEAD_DIM ** -0.5, b["encoder_attn"][rows])
+        ops.encoder_out_proj_residual(b["encoder_attn"], w["encoder_attn_o_w"][layer], x)
+        ops.encoder_norm_gated_ffn(x, w["encoder_ffn_gate_w"][layer], w["encoder_ffn_up_w"][layer],
+                                   b["encoder_hidden"], b["encoder_x_norm"])
+        ops.encoder_ffn_down_residual(b["encoder_hidden"], w["encoder_ffn_down_w"][layer], x)
 
 
 def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LAYERS, noise=None,
-                 prefetch_next_step=False, before_layer=None):
+                 before_layer=None):
     """One flow-matching Euler step over `noise` (default: the plan's master copy). `before_layer(layer)`,
     if given, is called before layer `layer` is enqueued (the place to wait for that layer's prefix K/V)."""
     w, b, S = weights, buffers, encoder_seq_len
@@ -96,10 +117,6 @@ def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LA
         k_cache, v_cache = b["encoder_K"][layer], b["encoder_V"][layer]
         if before_layer is not None:
             before_layer(layer)
-        if layer + 1 < layers:
-            _prefetch_decoder_layer(ops, w, b, layer + 1)
-        elif prefetch_next_step:
-            _prefetch_decoder_layer(ops, w, b, 0)
         ops.decoder_norm_qkv_rope(x, w["decoder_attn_qkv_w"][layer], b["decoder_rope_weights"], q,
                                   k_cache[S:], v_cache[S:], nf)
         ops.decoder_attention(q, k_cache, v_cache, b["decoder_attn_buf"], q, S)
@@ -109,20 +126,17 @@ def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LA
         ops.decoder_ffn_down_residual(b["decoder_hidden"], w["decoder_ffn_down_w"][layer], x)
     ops.decoder_action_out_proj(x[1:], w["decoder_action_fused_out_proj_w"],
                                 w["decoder_action_fused_out_proj_b"], noise, nf)
-    if not prefetch_next_step and hasattr(ops, "join_prefetch"):
-        ops.join_prefetch()                  # the side stream rejoins before the caller goes on
 
 
 def decoder_prologue(ops, weights, buffers):
     """What the decoder needs before its first step and that does not depend on the encoder: the state
-    token's projection, the fp32 master copy of the noise, the first layer's weights on their way to L2."""
+    token's projection and the fp32 master copy of the noise."""
     b = buffers
     ops.decoder_state_proj(b["observation_state_normalized"], weights["decoder_state_in_proj_w"],
                            weights["decoder_state_in_proj_b"], b["decoder_state_buf"])
     master = b.get("diffusion_noise_f32")
     if master is not None:
         master.copy_(b["diffusion_noise"])
-    _prefetch_decoder_layer(ops, weights, b, 0)
 
 
 def decoder_epilogue(buffers):
@@ -141,6 +155,5 @@ def transformer_decoder(ops, weights, buffers, encoder_seq_len, steps=DIFFUSION_
     if first_step == 0:
         decoder_prologue(ops, weights, b)
     for step in range(first_step, steps):
-        decoder_step(ops, weights, b, encoder_seq_len, step, layers, noise=master,
-                     prefetch_next_step=step + 1 < steps)
+        decoder_step(ops, weights, b, encoder_seq_len, step, layers, noise=master)
     decoder_epilogue(b)

@@ -103,10 +103,14 @@ int fvla_encoder_projector(const void* x, const void* norm_w, const void* norm_b
                            void* stream);
 /* wrappers.py:347-363: x_norm = rms(x); proj = bf16(x_norm @ W); RoPE on adjacent pairs of the
  * Q heads and K; scatter to Q (M, heads*hd), K (M, hd), V (M, hd). rope is (M, hd) interleaved
- * cos/sin. */
+ * cos/sin.
+ * group_rows > 0 (an extension for batches of episodes): the M rows are M / group_rows sequences laid end
+ * to end; rope is then (group_rows, hd) and is indexed by the position inside the sequence, and sequence
+ * g's K / V rows go to rows [g * kv_group_pitch, + group_rows) of K / V (each sequence's cache holds
+ * further rows that this call leaves alone). group_rows = 0: one sequence, contiguous K / V. */
 int fvla_encoder_norm_qkv_rope(const void* x, const void* weight_qkv, const void* rope, void* Q,
                                void* K, void* V, void* x_norm, int M, int Kdim, int heads,
-                               int head_dim, void* stream);
+                               int head_dim, int group_rows, int kv_group_pitch, void* stream);
 /* kernels/attention.py:29-34: unmasked multi-query attention, Q flat (tokens*heads, hd). With `ws`
  * (fvla_encoder_attention_workspace_bytes; contents need no initialisation) the keys are split over
  * twice as many CTAs and a second kernel merges the halves; NULL keeps the single-kernel form. */
@@ -157,12 +161,6 @@ int fvla_decoder_norm_gated_ffn(const void* x, int x_is_f32, const void* x_shado
 int fvla_decoder_action_out_proj(const void* x, int x_is_f32, const void* weight, const void* bias, void* out,
                                  int out_is_f32, void* mirror, void* norm_factor, int M, int N,
                                  int K, void* stream);
-
-/* No counterpart in the reference. Enqueues a small kernel that pulls `count` (1..8) byte ranges
- * (16-byte aligned starts) from HBM into L2. The decoder GEMMs read every weight once per Euler step,
- * always cold; a host that runs this on a second stream one layer ahead of them turns that read into
- * an L2 hit. Purely a hint: no data is modified and no result depends on it. */
-int fvla_l2_prefetch(const void* const* ptrs, const size_t* bytes, int count, void* stream);
 
 /* No counterpart in the reference, which accepts only precomputed `language_embeds` (engine.py:43, :60):
  * out[r, :] = table[ids[r], :], bf16 rows of `dim` elements (dim % 8 == 0), ids int64 on the device. An id

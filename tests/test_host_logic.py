@@ -47,8 +47,7 @@ def test_op_table_contract():
         "decoder_action_mlp", "decoder_norm_qkv_rope", "decoder_attention", "decoder_out_proj_residual",
         "decoder_ffn_down_residual", "decoder_norm_gated_ffn", "decoder_action_out_proj"}
     assert reference_names <= set(cuda.ALL_WRAPPERS)
-    assert set(cuda.ALL_WRAPPERS) - reference_names == {"vision_attention", "encoder_attention", "sync_shadow",
-                                                              "prefetch_l2", "join_prefetch", "embed_prompt"}
+    assert set(cuda.ALL_WRAPPERS) - reference_names == {"vision_attention", "encoder_attention", "sync_shadow", "embed_prompt"}
     assert set(DEFAULT_FUSED_OPS) == {"decoder_norm_gated_ffn", "decoder_action_out_proj", "decoder_attention"}
     fused, unfused = op_table(True), op_table(False)
     assert fused.decoder_attention is cuda.FUSED_WRAPPERS["decoder_attention"]
@@ -90,6 +89,22 @@ def test_buffer_plan():
     assert torch.equal(rope_table(13, 5, 256, "cpu"), O.rope_table(13, 5))
 
 
+def test_batched_buffer_plan():
+    from flash_vla_b200.hardware.nvidia.b200.pi0.buffers import allocate_batched_buffers
+    prefix, episodes, S = allocate_batched_buffers(3, 50, 49, 2, "cpu")
+    assert S == 817 and len(episodes) == 2
+    assert prefix["vision_x"].shape == (6, 256, 1152) and prefix["encoder_x"].shape == (2 * 817, 2048)
+    assert prefix["encoder_K"].shape == (2, 18, 868, 256) and prefix["encoder_rope_weights"].shape == (817, 256)
+    for e, b in enumerate(episodes):
+        assert b["encoder_K"].shape == (18, 868, 256) and b["encoder_K"].data_ptr() == prefix["encoder_K"][e].data_ptr()
+        assert b["observation_images_normalized"].shape == (3, 224, 224, 3)
+        assert b["decoder_x"].dtype == torch.float32 and "vision_x" not in b
+        assert torch.equal(b["decoder_rope_weights"], O.rope_table(51, 817))
+    # the K / V destination the batched QKV projection gets: evenly spaced (episodes, S, 256) blocks
+    k = prefix["encoder_K"][:, 3, :S]
+    assert k.shape == (2, 817, 256) and k.stride() == (18 * 868 * 256, 256, 1)
+
+
 def test_package_pipeline_with_oracle_ops(monkeypatch):
     """The package's orchestration, driven by the oracle's op table on the CPU, must equal the
     oracle's own orchestration (which make_golden checks against the reference's pipeline.py).
@@ -127,6 +142,66 @@ def test_package_pipeline_with_oracle_ops(monkeypatch):
     assert torch.allclose(b["encoder_K"][:L], ref_buffers["encoder_K"][:L], atol=1e-5)
     with pytest.raises(NotImplementedError):
         pipeline.vision_encoder(ops, w, b, 2)
+
+
+def test_batched_prefix_pipeline_equals_independent_episodes(monkeypatch):
+    """The throughput plan's orchestration (SigLIP and the prefix encoder once over all episodes' rows,
+    K/V scattered into per-episode caches, decoders per episode) driven by the oracle's ops on the CPU must
+    give, for every episode, what an independent single-episode pass gives."""
+    from types import SimpleNamespace
+    from flash_vla_b200.hardware.nvidia.b200.pi0 import pipeline
+    from flash_vla_b200.models.pi0.spec import weight_shapes
+    L, E, P = 2, 2, 5
+    monkeypatch.setattr(pipeline, "VISION_LAYERS", L)
+    monkeypatch.setattr(pipeline, "ENCODER_LAYERS", L)
+    monkeypatch.setattr(O, "VISION_LAYERS", L)
+    monkeypatch.setattr(O, "ENCODER_LAYERS", L)
+    g = torch.Generator().manual_seed(1)
+    w = {}
+    for name, shape in weight_shapes(P).items():
+        shape = tuple(L if (i == 0 and s in (27, 18) and len(shape) > 1 and name != "decoder_action_fused_time_biases") else s
+                      for i, s in enumerate(shape))
+        w[name] = torch.randn(shape, generator=g) * 0.02
+    inputs = [(torch.rand(3, 224, 224, 3, generator=g) * 2 - 1, torch.randn(32, generator=g), torch.randn(50, 32, generator=g))
+              for _ in range(E)]
+    want = [O.forward(w, *inp, steps=2, layers=L)[0].clone() for inp in inputs]
+
+    # the oracle's QKV op writes (M, hd) K / V; the batched plan hands it (episodes, S, hd) views of the caches
+    base = O.op_table(True)
+
+    def qkv(x, weight, rope, Q, K, V, x_norm):
+        if K.ndim == 2:
+            return base.encoder_norm_qkv_rope(x, weight, rope, Q, K, V, x_norm)
+        n, S = K.shape[0], K.shape[1]
+        for e in range(n):                      # rope is one sequence's table: apply per sequence
+            rows = slice(e * S, (e + 1) * S)
+            base.encoder_norm_qkv_rope(x[rows], weight, rope, Q[e * S * 8:(e + 1) * S * 8], K[e], V[e], x_norm[rows])
+
+    ops = SimpleNamespace(**{**vars(base), "encoder_norm_qkv_rope": qkv})
+    S, D = 768 + P, 51
+    ref_b, _ = O.allocate_buffers(3, 50, P)
+    prefix = {k: (torch.zeros((E * v.shape[0],) + tuple(v.shape[1:])) if k.startswith(("vision_", "observation_images"))
+                  or k in ("encoder_x", "encoder_x_norm", "encoder_Q", "encoder_attn", "encoder_hidden") else v)
+              for k, v in ref_b.items()}
+    prefix["encoder_K"] = torch.zeros(E, L, S + D, 256)
+    prefix["encoder_V"] = torch.zeros(E, L, S + D, 256)
+    episodes = []
+    for e, (images, state, noise) in enumerate(inputs):
+        b, _ = O.allocate_buffers(3, 50, P)
+        b["diffusion_noise_f32"] = torch.zeros(50, 32)
+        b["observation_state_normalized"].copy_(state)
+        b["diffusion_noise"].copy_(noise)
+        b["encoder_K"], b["encoder_V"] = prefix["encoder_K"][e], prefix["encoder_V"][e]
+        prefix["observation_images_normalized"][3 * e:3 * e + 3].copy_(images)
+        prefix["encoder_x"][e * S + 768:(e + 1) * S].copy_(w["language_embeds"])
+        episodes.append(b)
+    pipeline.vision_encoder(ops, w, prefix, 3)
+    seen = []
+    pipeline.transformer_encoder_batched(ops, w, prefix, S, 3, E, after_qkv=seen.append)
+    assert seen == list(range(L))
+    for e, b in enumerate(episodes):
+        pipeline.transformer_decoder(ops, w, b, S, steps=2, layers=L)
+        assert torch.allclose(b["diffusion_noise"], want[e], atol=1e-5), f"episode {e}"
 
 
 def test_engine_refuses_to_run_without_cuda():

@@ -297,22 +297,6 @@ def test_bad_arguments_raise_before_launch(ops):
     torch.cuda.synchronize()
 
 
-def test_prefetch_l2_is_a_pure_hint(ops):
-    """The side-stream L2 prefetch changes no data, joins back, and rejects more than 8 ranges."""
-    from flash_vla_b200.hardware.nvidia.b200.pi0.backends.cuda._lib import FvlaError
-    g = torch.Generator().manual_seed(3)
-    ts = [rnd(g, 1024, 512).cuda() for _ in range(3)] + [torch.randn(1000, generator=g).cuda()]
-    before = [t.clone() for t in ts]
-    ops[1].prefetch_l2(*ts)
-    ops[1].join_prefetch()
-    torch.cuda.synchronize()
-    for t, b in zip(ts, before):
-        assert torch.equal(t, b)
-    with pytest.raises(FvlaError):
-        ops[1].prefetch_l2(*[ts[0]] * 9)
-    ops[1].join_prefetch()
-
-
 @pytest.mark.parametrize("rows", [1, 48, 49])
 def test_embed_prompt_is_a_row_gather(ops, rows):
     """Prompt embedding lookup against the oracle's gather, ids at both ends of the vocabulary included."""
