@@ -446,6 +446,14 @@ SWEEP = {   # name: (M, K, N, gated, residual, layers cycled)
     "enc_down": (768, 16384, 2048, False, True, 6),
     "enc_attn": (768 * 8, 256, 768, False, False, 6),     # prefix attention: flat queries, head dim, keys
     "dec_attn": (51 * 8, 256, 819, False, False, 18),     # decoder attention: flat queries, head dim, keys (768 prefix + 51)
+    # the remaining call sites of the M = 768 stages (row norm kernel included where the op has one)
+    "enc_qkv": (768, 2048, 2560, False, False, 9),
+    "enc_o": (768, 2048, 2048, False, True, 9),
+    "vis_qkv": (768, 1152, 3456, False, False, 9),
+    "vis_attn": (3 * 16 * 256, 72, 256, False, False, 9), # SigLIP attention: views x heads x queries, head dim, keys
+    "vis_o": (768, 1152, 1152, False, True, 9),
+    "vis_up": (768, 1152, 4304, False, False, 9),
+    "vis_down": (768, 4304, 1152, False, True, 9),
 }
 
 
@@ -483,7 +491,39 @@ def sweep_rows(names, layers_cap: int, reps: int):
                 ms = time_isolated_op(fn, layers, reps)
                 rows[name] = row(ms, 4.0 * M * N * K, 2 * (2 * M * K + 2 * N * K), queries=M, keys=N, head_dim=K)
                 continue
+            if name == "vis_attn":
+                qkv = [torch.randn(3, 256, 3 * 1152, device="cuda", generator=g).to(bf16) for _ in range(layers)]
+                o = torch.zeros(3, 256, 1152, device="cuda", dtype=bf16)
+                ms = time_isolated_op(lambda i: ops.vision_attention(qkv[i], o), layers, reps)
+                rows[name] = row(ms, 4.0 * M * N * K, 2 * 4 * 768 * 1152, queries=M, keys=N, head_dim=K)
+                continue
             w = [(torch.randn(K, N, device="cuda", generator=g) * 0.02).to(bf16) for _ in range(layers * (2 if gated else 1))]
+            if name.startswith(("vis_", "enc_qkv", "enc_o")):
+                x = torch.randn(M, K, device="cuda", generator=g).to(bf16)
+                bias = (torch.randn(N, device="cuda", generator=g) * 0.02).to(bf16)
+                nw = torch.ones(K, device="cuda", dtype=bf16)
+                nb = torch.zeros(K, device="cuda", dtype=bf16)
+                xn = torch.zeros(M, K, device="cuda", dtype=bf16)
+                out = torch.zeros(M, N, device="cuda", dtype=bf16)
+                if name == "enc_qkv":
+                    rope = rope_table(M, 0, 256, "cuda")
+                    Q = torch.zeros(M * 8, 256, device="cuda", dtype=bf16)
+                    Kc, Vc = torch.zeros(M, 256, device="cuda", dtype=bf16), torch.zeros(M, 256, device="cuda", dtype=bf16)
+                    fn = lambda i: ops.encoder_norm_qkv_rope(x, w[i], rope, Q, Kc, Vc, xn)
+                elif name == "enc_o":
+                    fn = lambda i: ops.encoder_out_proj_residual(x, w[i], out)
+                elif name == "vis_qkv":
+                    fn = lambda i: ops.vision_norm_qkv(x.view(3, 256, K), nw, nb, w[i], bias, out.view(3, 256, N), xn.view(3, 256, K))
+                elif name == "vis_up":
+                    fn = lambda i: ops.vision_norm_ffn_up(x.view(3, 256, K), nw, nb, w[i], bias, out.view(3, 256, N), xn.view(3, 256, K))
+                else:       # vis_o, vis_down: out = x @ W + b + out, in place
+                    fn = lambda i: ops.vision_ffn_down_residual(x, w[i], bias, out, out)
+                ms = time_isolated_op(fn, layers, reps)
+                nbytes = K * N * 2 + M * K * 2 + M * N * 2 * (2 if residual else 1)
+                rows[name] = row(ms, 2.0 * M * K * N, nbytes, M=M, K=K, N=N)
+                del w
+                torch.cuda.empty_cache()
+                continue
             x32 = torch.randn(M, K, device="cuda", generator=g)
             f32_in = name in ("dec_gate", "dec_qkv")                   # the decoder's residual stream is fp32 ...
             f32_out = name in ("dec_down", "dec_o")

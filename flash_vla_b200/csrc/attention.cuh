@@ -288,6 +288,10 @@ struct DecAttnArgs {
     const bf16* q; const bf16* k; const bf16* v; bf16* out;
     int nq, nk, keys_per_split;
     int splits;                 // cluster size: CTAs sharing the keys of one 32-row query block (8..11)
+    // a batch of independent episodes (grid.z): element offsets between consecutive episodes' Q / out rows
+    // and between their K / V caches; nq and nk are per episode
+    long long q_episode_stride, kv_episode_stride;
+    int episodes;
     float scale_log2;
     int mask_rows, mask_key_le;
     int prefix_keys;            // keys [0, prefix_keys) were not written by the preceding kernel
@@ -329,10 +333,14 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
     const int OFF_LSE_IN = OFF_RED + SPL * SLICE;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    FVLA_DBG_CTA(p, blockIdx.y * gridDim.x + blockIdx.x);
+    FVLA_DBG_CTA(p, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x);
     FVLA_STAMP(0);
     uint32_t rank;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const bf16* gq = p.q + (size_t)blockIdx.z * p.q_episode_stride;
+    const bf16* gk = p.k + (size_t)blockIdx.z * p.kv_episode_stride;
+    const bf16* gv = p.v + (size_t)blockIdx.z * p.kv_episode_stride;
+    bf16* gout = p.out + (size_t)blockIdx.z * p.q_episode_stride;
     const int q0 = blockIdx.x * BQ;
     const int key_beg = (int)rank * p.keys_per_split;
     const int key_end = min(p.nk, key_beg + p.keys_per_split);
@@ -361,8 +369,8 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
     // Prefix keys were written long before the preceding kernel: fetch them while it finishes. Rows
     // past the end (keys of the ragged last split, queries of the last block) must read as zero.
     const int pre_end = min(key_end, p.prefix_keys);
-    load_rows(sK, p.k, key_beg, key_beg, pre_end, 128);
-    load_rows(sV, p.v, key_beg, key_beg, pre_end, 128);
+    load_rows(sK, gk, key_beg, key_beg, pre_end, 128);
+    load_rows(sV, gv, key_beg, key_beg, pre_end, 128);
     cp_async_commit();
     for (int idx = tid; idx < 128 * CH; idx += THREADS) {
         int r = idx / CH, c = idx % CH;
@@ -375,9 +383,9 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     FVLA_STAMP(1);
-    load_rows(sQ, p.q, q0, q0, p.nq, BQ);
-    load_rows(sK, p.k, key_beg, max(key_beg, pre_end), key_end, 128);
-    load_rows(sV, p.v, key_beg, max(key_beg, pre_end), key_end, 128);
+    load_rows(sQ, gq, q0, q0, p.nq, BQ);
+    load_rows(sK, gk, key_beg, max(key_beg, pre_end), key_end, 128);
+    load_rows(sV, gv, key_beg, max(key_beg, pre_end), key_end, 128);
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
@@ -564,7 +572,7 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
                 acc[0] += w * v0.x; acc[1] += w * v0.y; acc[2] += w * v0.z; acc[3] += w * v0.w;
             }
             const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
-            *reinterpret_cast<uint2*>(p.out + (size_t)row * HD + c4) =
+            *reinterpret_cast<uint2*>(gout + (size_t)row * HD + c4) =
                 make_uint2(pack_bf16x2(acc[0] * inv, acc[1] * inv), pack_bf16x2(acc[2] * inv, acc[3] * inv));
         }
     }
@@ -590,7 +598,7 @@ inline int launch_decoder_attention_cluster(const DecAttnArgs& a, bool pdl, cuda
         set_error("decoder attention: %d keys do not fit %d splits of %d", a.nk, a.splits, a.keys_per_split);
         return FVLA_ERR_UNSUPPORTED;
     }
-    cfg.gridDim = dim3((a.nq + decattn::BQ - 1) / decattn::BQ, a.splits, 1);
+    cfg.gridDim = dim3((a.nq + decattn::BQ - 1) / decattn::BQ, a.splits, a.episodes > 1 ? a.episodes : 1);
     cfg.blockDim = dim3(decattn::THREADS, 1, 1);
     cfg.dynamicSmemBytes = decattn::smem_bytes(a.splits);
     cfg.stream = st;

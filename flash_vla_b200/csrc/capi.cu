@@ -490,9 +490,11 @@ static int decoder_norm_front(const void* x, int x_is_f32, void* norm_factor, in
 
 int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* x_shadow, const void* weight_qkv, const void* rope, void* Q,
                                void* K, void* V, void* norm_factor, int M, int Kdim, int heads, int head_dim,
-                               void* ws, size_t ws_bytes, void* stream) {
+                               int group_rows, int kv_group_pitch, void* ws, size_t ws_bytes, void* stream) {
     const int N = (heads + 2) * head_dim;
-    if (tc5_enabled() && skinny::plan_skinny(M, N, Kdim, false).ok && aligned16(x) && aligned16(weight_qkv) &&
+    FVLA_REQUIRE(group_rows >= 0 && (group_rows == 0 || (M % group_rows == 0 && kv_group_pitch >= group_rows)),
+                 "decoder_norm_qkv_rope: M=%d is not a whole number of sequences of %d rows (K/V pitch %d rows)", M, group_rows, kv_group_pitch);
+    if (group_rows == 0 && tc5_enabled() && skinny::plan_skinny(M, N, Kdim, false).ok && aligned16(x) && aligned16(weight_qkv) &&
         head_dim % 2 == 0) {
         skinny::SkinnyArgs sa{};
         sa.x = x; sa.x_f32 = x_is_f32; sa.x_shadow = B(x_shadow); sa.ldx = Kdim; sa.M = M; sa.N = N; sa.K = Kdim; sa.need_factor = 1;
@@ -505,15 +507,20 @@ int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* x_shadow
     if (rc) return rc;
     a.B = B(weight_qkv); a.ldb = N;
     a.rope = B(rope); a.q = Bm(Q); a.k = Bm(K); a.v = Bm(V); a.heads = heads; a.head_dim = head_dim;
+    a.group_rows = group_rows; a.kv_group_pitch = kv_group_pitch;
     void* gws; size_t gn;
     gemm_ws(ws, ws_bytes, M, Kdim, &gws, &gn);
     return launch_gemm(a, gws, gn, S(stream));
 }
 
 int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* out, int queries, int keys,
-                           int head_dim, int heads, int encoder_seq_len, void* ws, size_t ws_bytes,
-                           void* stream) {
-    FVLA_REQUIRE(queries > 0 && keys > 0, "decoder_attention: bad shape");
+                           int head_dim, int heads, int encoder_seq_len, int episodes, long long q_episode_stride,
+                           long long kv_episode_stride, void* ws, size_t ws_bytes, void* stream) {
+    FVLA_REQUIRE(queries > 0 && keys > 0 && episodes >= 1, "decoder_attention: bad shape");
+    FVLA_REQUIRE(episodes == 1 || (tc5_enabled() && keys <= decattn::MAX_SPL * 128 && q_episode_stride >= (long long)queries * head_dim &&
+                                   kv_episode_stride >= (long long)keys * head_dim && q_episode_stride % 8 == 0 && kv_episode_stride % 8 == 0),
+                 "decoder_attention: a batch of episodes needs the cluster kernel (at most %d keys) and 16-byte aligned episode strides",
+                 decattn::MAX_SPL * 128);
     if (head_dim != 256) { set_error("decoder_attention: head_dim %d not built (256 only)", head_dim); return FVLA_ERR_UNSUPPORTED; }
     if (ws == nullptr || ws_bytes < fvla_decoder_attention_workspace_bytes(queries, keys)) {
         set_error("decoder_attention: workspace of %zu bytes needed", fvla_decoder_attention_workspace_bytes(queries, keys));
@@ -526,6 +533,7 @@ int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* ou
         d.nq = queries; d.nk = keys; d.keys_per_split = ((keys + d.splits - 1) / d.splits + 7) / 8 * 8;
         d.scale_log2 = kLog2e / sqrtf((float)head_dim);
         d.mask_rows = heads; d.mask_key_le = encoder_seq_len; d.prefix_keys = encoder_seq_len;
+        d.episodes = episodes; d.q_episode_stride = q_episode_stride; d.kv_episode_stride = kv_episode_stride;
         d.status = device_status_ptr(); FVLA_DBG_ATTACH(d);
         return launch_decoder_attention_cluster(d, pdl_enabled(), S(stream));
     }

@@ -762,10 +762,13 @@ inline int launch_gemm_tc5(GemmArgs g, int* status, cudaStream_t st, void* ws = 
     if (g.Kb == 0) g.Kb = g.K;
     if (g.B2 != nullptr) return launch_tc5_cfg<128, true, 4>(g, status, st);
     if (g.rope != nullptr) return launch_tc5_cfg<128, false, 6, true>(g, status, st);
-    Tc5Plan pl = plan_tc5(g.M, g.N, g.K, ws != nullptr);
+    // an fp32 destination cannot take the split through global scratch, so it is planned without one
+    Tc5Plan pl = plan_tc5(g.M, g.N, g.K, ws != nullptr && !g.c_f32);
     // Split-K reduced inside clusters (128-wide tiles, one work item per CTA, no scratch): taken when its
-    // estimate (mainloop + epilogue + one 64 KB push per extra split) beats the plan above.
-    if (g.rope == nullptr && !g.c_f32) {
+    // estimate (mainloop + epilogue + one 64 KB push per extra split) beats the plan above. An fp32
+    // destination (the decoder's residual stream at M > 64) takes it as well: the split-0 CTA sums the
+    // partials before either epilogue form runs.
+    if (g.rope == nullptr) {
         const int tiles = ((g.M + BM - 1) / BM) * ((g.N + 127) / 128), k_iters = (g.K + BK - 1) / BK;
         int best_s = 0;
         float best_t = pl.est_us;

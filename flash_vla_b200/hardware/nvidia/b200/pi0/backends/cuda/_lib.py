@@ -27,8 +27,8 @@ SIGNATURES: dict[str, list] = {
     "fvla_linear_residual": [_P, _P, _P, _I, _P, _I, _I, _I, _P, _Z, _P],
     "fvla_encoder_norm_gated_ffn": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fvla_decoder_small_proj": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _Z, _P],
-    "fvla_decoder_norm_qkv_rope": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P],
-    "fvla_decoder_attention": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _Z, _P],
+    "fvla_decoder_norm_qkv_rope": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _Z, _P],
+    "fvla_decoder_attention": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.c_longlong, ctypes.c_longlong, _P, _Z, _P],
     "fvla_decoder_norm_gated_ffn": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _Z, _P],
     "fvla_decoder_action_out_proj": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
     "fvla_embed_rows": [_P, _P, _P, _I, _I, ctypes.c_longlong, _P],

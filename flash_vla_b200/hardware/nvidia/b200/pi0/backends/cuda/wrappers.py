@@ -330,32 +330,56 @@ def decoder_action_mlp(x, weight, bias, out):
 
 def decoder_norm_qkv_rope(x, weight_qkv, rope, Q, K, V, norm_factor):
     """RMS factor, QKV projection, RoPE in fp32, scatter into Q and the KV-cache tail
-    (wrappers.py:131-144). `norm_factor[:M]` receives the bf16 factor."""
+    (wrappers.py:131-144). `norm_factor[:M]` receives the bf16 factor.
+
+    Extension for batches of episodes: with K and V 3-D views (episodes, D, hd) of the tails of the
+    episodes' caches, x holds the episodes' D rows end to end and `rope` is the table of one episode."""
     M, Kdim = x.shape
-    hd = V.shape[1]
+    hd = V.shape[-1]
     heads = Q.shape[0] // M
     N = (heads + 2) * hd
     lib = _lib.load()
+    k_ptr, group, pitch = _kv_destination("K", K, M, hd)
+    v_ptr, group_v, pitch_v = _kv_destination("V", V, M, hd)
+    if (group, pitch) != (group_v, pitch_v):
+        raise ValueError("decoder_norm_qkv_rope: K and V must have the same layout")
+    rope_rows = group or M
     ws, nb = _ws("dec_qkv_ws", lib.fvla_gemm_workspace_bytes(M, N, Kdim, 0), x.device)
     _lib.call("fvla_decoder_norm_qkv_rope", _chk("x", x, dtype=None), _is_f32("x", x), _shadow_of(x),
               _chk("weight_qkv", weight_qkv, (Kdim, N)),
-              _chk("rope", rope[:M], (M, hd)), _chk("Q", Q, (M * heads, hd)), _chk("K", K, (M, hd)),
-              _chk("V", V, (M, hd)), _chk("norm_factor", norm_factor[:M], (M,)), M, Kdim, heads, hd,
+              _chk("rope", rope[:rope_rows], (rope_rows, hd)), _chk("Q", Q, (M * heads, hd)), k_ptr, v_ptr,
+              _chk("norm_factor", norm_factor[:M], (M,)), M, Kdim, heads, hd, group, pitch,
               ws, nb, _stream())
 
 
 def decoder_attention(Q, K, V, scores, out, encoder_seq_len):
     """softmax(Q K^T / sqrt(hd)) V with the Pi0 mask, keys split across CTAs. `scores` is
     accepted for signature parity and left untouched, as in the reference's fused wrapper
-    (fused_wrappers.py:88-115); `out` may be Q."""
+    (fused_wrappers.py:88-115); `out` may be Q.
+
+    Extension for batches of episodes: K and V as 3-D views (episodes, keys, hd) of the episodes' caches
+    (evenly spaced), Q and out holding the episodes' flat query rows end to end."""
     del scores
-    queries, hd = Q.shape
-    keys = K.shape[0]
     lib = _lib.load()
+    hd = Q.shape[1]
+    if K.ndim == 3:
+        episodes, keys = K.shape[0], K.shape[1]
+        if K.shape != V.shape or K.stride() != V.stride() or K.stride(2) != 1 or K.stride(1) != hd or K.shape[2] != hd:
+            raise ValueError("decoder_attention: batched K / V must be equally laid out (episodes, keys, hd) views")
+        if Q.shape[0] % episodes:
+            raise ValueError("decoder_attention: Q rows are not a whole number of episodes")
+        for name, t in (("K", K), ("V", V)):
+            if not t.is_cuda or t.dtype != torch.bfloat16:
+                raise ValueError(f"{name}: expected a bf16 CUDA tensor")
+        queries = Q.shape[0] // episodes
+        k_ptr, v_ptr, kv_stride = K.data_ptr(), V.data_ptr(), K.stride(0)
+    else:
+        episodes, keys, queries = 1, K.shape[0], Q.shape[0]
+        k_ptr, v_ptr, kv_stride = _chk("K", K, (keys, hd)), _chk("V", V, (keys, hd)), 0
     ws, nb = _ws("dec_attn_ws", lib.fvla_decoder_attention_workspace_bytes(queries, keys), Q.device)
-    _lib.call("fvla_decoder_attention", _chk("Q", Q), _chk("K", K, (keys, hd)), _chk("V", V, (keys, hd)),
-              _chk("out", out, (queries, hd)), queries, keys, hd, DECODER_HEADS, int(encoder_seq_len),
-              ws, nb, _stream())
+    _lib.call("fvla_decoder_attention", _chk("Q", Q), k_ptr, v_ptr,
+              _chk("out", out, (queries * episodes, hd)), queries, keys, hd, DECODER_HEADS, int(encoder_seq_len),
+              episodes, queries * hd, kv_stride, ws, nb, _stream())
     return out
 
 

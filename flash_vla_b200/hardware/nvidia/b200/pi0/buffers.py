@@ -79,6 +79,35 @@ def _materialise(plan, device):
     return {name: torch.zeros(shape, dtype=dtype, device=device) for name, (shape, dtype) in plan.items()}
 
 
+def allocate_batched_decoder_buffers(chunk_size: int, episodes: int, encoder_seq_len: int, device: str):
+    """Decoder buffers of the throughput profile when the action-expert decoder, too, runs once over all
+    episodes' rows (M = episodes x (chunk + 1)): the residual stream, Q, the FFN hidden state and the noise
+    hold the episodes end to end; K / V stay in the per-episode caches. `decoder_mlp_out` and
+    `decoder_x_rows` are staging rows for the two places where an op's contiguous (episodes x chunk) rows
+    meet the (episodes, chunk + 1) layout of the residual stream."""
+    E, D = episodes, chunk_size + 1
+    plan: dict[str, tuple[tuple[int, ...], torch.dtype]] = {}
+
+    def add(name, *shape, dtype=torch.bfloat16):
+        plan[name] = (shape, dtype)
+
+    add("observation_state_normalized", E, ACTION_DIM)
+    add("diffusion_noise", E, chunk_size, ACTION_DIM)
+    add("diffusion_noise_f32", E * chunk_size, ACTION_DIM, dtype=torch.float32)
+    add("decoder_rope_weights", D, HEAD_DIM)
+    add("decoder_x", E * D, DECODER_DIM, dtype=torch.float32)
+    add("decoder_x_buf", E * chunk_size, DECODER_DIM)
+    add("decoder_mlp_out", E * chunk_size, DECODER_DIM, dtype=torch.float32)
+    add("decoder_x_rows", E * chunk_size, DECODER_DIM, dtype=torch.float32)
+    add("decoder_state_buf", E, DECODER_DIM)
+    add("decoder_norm_factor_buf", E * D)
+    add("decoder_q_buf", E * D * DECODER_HEADS, HEAD_DIM)
+    add("decoder_hidden", E * D, DECODER_FFN)
+    b = _materialise(plan, device)
+    b["decoder_rope_weights"].copy_(rope_table(D, encoder_seq_len, HEAD_DIM, device))
+    return b
+
+
 def allocate_batched_buffers(num_views: int, chunk_size: int, prompt_len: int, episodes: int, device: str):
     """Buffer plan of the throughput profile: `episodes` independent episodes whose SigLIP tower and prefix
     encoder run as ONE pass over all episodes' tokens (M = episodes x S rows, so every vision and prefix

@@ -11,10 +11,11 @@ episodes that share the weights:
   * SigLIP and the prefix encoder run ONCE over all episodes' tokens (M = E x S rows): every vision and
     prefix weight (4.8 of the 5.4 GB) is streamed once for the whole batch and the GEMMs have E times
     the tiles to fill the GPU with; only the attention kernels, which mix tokens, run per episode;
-  * each episode has its own KV cache and decoder buffers, and the E action-expert decoders run on E
-    streams inside the captured graph, side by side: their kernels are latency-bound at batch 1 and
-    leave SMs idle, which concurrent episodes fill. Decoder layer L of every episode starts as soon as
-    the batched encoder has produced layer L's prefix K/V.
+  * each episode has its own KV cache; the action-expert decoder also runs ONCE over all episodes' rows
+    (M = E x 51), its weights streamed once per layer-step for the whole batch, with attention per
+    episode inside one launch (`batch_decoder=False`: E single-episode decoders on E streams instead,
+    which fill each other's idle SMs but stream the weights E times). Decoder layer L starts as soon
+    as the batched encoder has produced layer L's prefix K/V.
 `batch_prefix=False` keeps the older form (E complete single-episode passes on E streams), whose
 per-episode results are bit-identical to the single-episode engine; the batched form runs the same
 per-row arithmetic but through differently shaped GEMM launches, so it agrees to rounding.
@@ -28,7 +29,7 @@ from flash_vla_b200.runtime.cuda import ScratchPool
 
 from . import pipeline
 from .backends.cuda import wrappers
-from .buffers import allocate_batched_buffers, allocate_static_buffers
+from .buffers import allocate_batched_buffers, allocate_batched_decoder_buffers, allocate_static_buffers
 from .ops import op_table
 
 
@@ -43,7 +44,7 @@ class Pi0Inference:
     def __init__(self, checkpoint, num_views: int, chunk_size: int, steps: int = 10,
                  layers: int = 18, fused: bool = True, device: str = "cuda", plan=None,
                  capture: bool = True, episodes: int = 1, overlap: bool = True, embedding_table=None,
-                 batch_prefix: bool = True):
+                 batch_prefix: bool = True, batch_decoder: bool = False):
         if not torch.cuda.is_available():
             raise RuntimeError("Pi0Inference needs a CUDA device; the B200 target has no CPU path")
         if episodes < 1:
@@ -79,11 +80,22 @@ class Pi0Inference:
             self.weights[name] = value.to(device=device, dtype=torch.bfloat16).contiguous()
         self.episode_buffers, self.pools = [], []
         self.batch_prefix = bool(batch_prefix) and episodes > 1
-        self.prefix_buffers, self.prefix_pool = None, None
+        self.batch_decoder = self.batch_prefix and bool(batch_decoder)
+        self.prefix_buffers, self.prefix_pool, self.decoder_buffers = None, None, None
         if self.batch_prefix:
             self.prefix_buffers, self.episode_buffers, self.encoder_seq_len = allocate_batched_buffers(
                 num_views, chunk_size, self.prompt_len, episodes, device)
             self.prefix_pool = ScratchPool()
+        if self.batch_decoder:
+            self.decoder_buffers = allocate_batched_decoder_buffers(chunk_size, episodes, self.encoder_seq_len, device)
+            self.decoder_pool = ScratchPool()
+            self.pools = [self.decoder_pool]
+            self._batched_observation_state_normalized = self.decoder_buffers["observation_state_normalized"]
+            self._batched_diffusion_noise = self.decoder_buffers["diffusion_noise"]
+            self._batched_observation_images_normalized = self.prefix_buffers["observation_images_normalized"].view(
+                episodes, num_views, 224, 224, 3)
+            self.streams = [torch.cuda.Stream(device=device)]
+        elif self.batch_prefix:
             for buffers in self.episode_buffers:
                 wrappers.register_bf16_shadow(buffers["decoder_x"], buffers["decoder_x_bf16"])
                 self.pools.append(ScratchPool())
@@ -143,18 +155,49 @@ class Pi0Inference:
             pipeline.transformer_decoder(self.ops, self.weights, b, self.encoder_seq_len,
                                          steps=self.steps, layers=self.layers, first_step=1)
 
+    def _run_fully_batched(self):
+        """Throughput plan with the decoder batched as well: prefix pass on the current stream, the one
+        batched decoder on a second stream, its first step one layer behind the encoder."""
+        E, S, p, d = self.episodes, self.encoder_seq_len, self.prefix_buffers, self.decoder_buffers
+        main, side = torch.cuda.current_stream(), self.streams[0]
+        self._write_prompt_rows()
+        side.wait_stream(main)
+        with torch.cuda.stream(side), wrappers.use_pool(self.decoder_pool):
+            pipeline.decoder_prologue_batched(self.ops, self.weights, d)
+        kv_ready = [torch.cuda.Event() for _ in range(pipeline.ENCODER_LAYERS)]
+        with wrappers.use_pool(self.prefix_pool):
+            pipeline.vision_encoder(self.ops, self.weights, p, self.num_views)
+            pipeline.transformer_encoder_batched(self.ops, self.weights, p, S, self.num_views, E,
+                                                 after_qkv=lambda layer: kv_ready[layer].record(main))
+        with torch.cuda.stream(side), wrappers.use_pool(self.decoder_pool):
+            if self.steps == 0:
+                side.wait_event(kv_ready[-1])
+            for step in range(self.steps):
+                gate = (lambda layer: side.wait_event(kv_ready[layer])) if step == 0 else None
+                pipeline.decoder_step_batched(self.ops, self.weights, p, d, S, step, E, self.layers, before_layer=gate)
+            pipeline.decoder_epilogue_batched(d)
+        main.wait_stream(side)
+
+    def _write_prompt_rows(self):
+        E, S, p = self.episodes, self.encoder_seq_len, self.prefix_buffers
+        if not self.prompt_len:
+            return
+        for e in range(E):
+            rows = p["encoder_x"][e * S + self.num_views * 256:(e + 1) * S]
+            if self.embedding_table is not None:
+                self.ops.embed_prompt(self.embedding_table, self.prompt_ids, rows)
+            else:
+                rows.copy_(self.weights["language_embeds"])
+
     def _run_batched(self):
         """The throughput plan: one SigLIP + prefix-encoder pass over all episodes' rows on the current stream,
         the episodes' decoders on one stream each, every decoder layer gated on the batched encoder's K/V."""
+        if self.batch_decoder:
+            self._run_fully_batched()
+            return
         E, S, p = self.episodes, self.encoder_seq_len, self.prefix_buffers
         main = torch.cuda.current_stream()
-        if self.prompt_len:
-            for e in range(E):
-                rows = p["encoder_x"][e * S + self.num_views * 256:(e + 1) * S]
-                if self.embedding_table is not None:
-                    self.ops.embed_prompt(self.embedding_table, self.prompt_ids, rows)
-                else:
-                    rows.copy_(self.weights["language_embeds"])
+        self._write_prompt_rows()
         for e, stream in enumerate(self.streams):               # what the decoders can do before any K/V exists
             stream.wait_stream(main)
             with torch.cuda.stream(stream), wrappers.use_pool(self.pools[e]):

@@ -128,6 +128,47 @@ def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LA
                                 w["decoder_action_fused_out_proj_b"], noise, nf)
 
 
+def decoder_prologue_batched(ops, weights, dec):
+    """`decoder_prologue` for the batched decoder buffers: all episodes' state tokens in one projection."""
+    ops.decoder_state_proj(dec["observation_state_normalized"], weights["decoder_state_in_proj_w"],
+                           weights["decoder_state_in_proj_b"], dec["decoder_state_buf"])
+    dec["diffusion_noise_f32"].copy_(dec["diffusion_noise"].view(-1, dec["diffusion_noise"].shape[-1]))
+
+
+def decoder_step_batched(ops, weights, prefix, dec, encoder_seq_len, step, episodes, layers=ENCODER_LAYERS,
+                         before_layer=None):
+    """One Euler step of ALL episodes at once: every projection of the action expert runs over the
+    episodes' rows laid end to end (M = episodes x (chunk + 1)), so the decoder's weights are streamed once
+    per layer-step for the whole batch; attention runs per episode inside one launch, each episode against
+    its own KV cache. Same ops and order per layer as `decoder_step`."""
+    w, S, E = weights, encoder_seq_len, episodes
+    x, nf, q = dec["decoder_x"], dec["decoder_norm_factor_buf"], dec["decoder_q_buf"]
+    D = x.shape[0] // E
+    x3 = x.view(E, D, x.shape[1])
+    x3[:, 0].copy_(dec["decoder_state_buf"])
+    ops.decoder_action_in_proj(dec["diffusion_noise_f32"], w["decoder_action_fused_in_proj_w"],
+                               w["decoder_action_fused_time_biases"][step % DIFFUSION_STEPS], dec["decoder_x_buf"])
+    ops.decoder_action_mlp(dec["decoder_x_buf"], w["decoder_action_mlp_w"], w["decoder_action_mlp_b"], dec["decoder_mlp_out"])
+    x3[:, 1:].copy_(dec["decoder_mlp_out"].view(E, D - 1, x.shape[1]))
+    for layer in range(layers):
+        k_all, v_all = prefix["encoder_K"][:, layer], prefix["encoder_V"][:, layer]      # (E, S + D, 256) views
+        if before_layer is not None:
+            before_layer(layer)
+        ops.decoder_norm_qkv_rope(x, w["decoder_attn_qkv_w"][layer], dec["decoder_rope_weights"], q,
+                                  k_all[:, S:], v_all[:, S:], nf)
+        ops.decoder_attention(q, k_all, v_all, None, q, S)
+        ops.decoder_out_proj_residual(q.view(-1, DECODER_HEADS * HEAD_DIM), w["decoder_attn_o_w"][layer], x)
+        ops.decoder_norm_gated_ffn(x, w["decoder_ffn_gate_w"][layer], w["decoder_ffn_up_w"][layer], dec["decoder_hidden"], nf)
+        ops.decoder_ffn_down_residual(dec["decoder_hidden"], w["decoder_ffn_down_w"][layer], x)
+    dec["decoder_x_rows"].view(E, D - 1, x.shape[1]).copy_(x3[:, 1:])
+    ops.decoder_action_out_proj(dec["decoder_x_rows"], w["decoder_action_fused_out_proj_w"],
+                                w["decoder_action_fused_out_proj_b"], dec["diffusion_noise_f32"], nf)
+
+
+def decoder_epilogue_batched(dec):
+    dec["diffusion_noise"].view(-1, dec["diffusion_noise"].shape[-1]).copy_(dec["diffusion_noise_f32"])
+
+
 def decoder_prologue(ops, weights, buffers):
     """What the decoder needs before its first step and that does not depend on the encoder: the state
     token's projection and the fp32 master copy of the noise."""

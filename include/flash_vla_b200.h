@@ -136,10 +136,15 @@ int fvla_decoder_small_proj(const void* x, int x_is_f32, const void* weight, con
 /* wrappers.py:131-144: factor = rsqrt(mean(x^2)+1e-6) (also stored, bf16, in norm_factor when
  * not NULL); projection scaled by it, RoPE in fp32, single rounding, scatter to Q / K / V.
  * x is the bf16 residual stream, or an fp32 one when x_is_f32 != 0; x_shadow (may be NULL) is a
- * current bf16 copy of an fp32 x, which spares the kernel the conversion. */
+ * current bf16 copy of an fp32 x, which spares the kernel the conversion.
+ * group_rows > 0 (an extension for batches of episodes): the M rows are M / group_rows episodes of
+ * group_rows tokens each; rope is (group_rows, hd), indexed by the token's position inside its episode,
+ * and episode g's K / V rows go to rows [g * kv_group_pitch, + group_rows) of K / V (the tail of that
+ * episode's cache). group_rows = 0: one episode, contiguous K / V. */
 int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* x_shadow, const void* weight_qkv, const void* rope, void* Q,
                                void* K, void* V, void* norm_factor, int M, int Kdim, int heads,
-                               int head_dim, void* ws, size_t ws_bytes, void* stream);
+                               int head_dim, int group_rows, int kv_group_pitch, void* ws, size_t ws_bytes,
+                               void* stream);
 /* fused_wrappers.py:88-115 (and the unfused chain wrappers.py:147-173): softmax(Q K^T / sqrt(hd))
  * V over all `keys`, with rows < heads (the state token) limited to keys j <= encoder_seq_len.
  * out may alias Q.
@@ -147,9 +152,13 @@ int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* x_shadow
  * kernel that precedes this call in `stream` STARTS, not merely before it ends. The kernel fetches those
  * rows while its predecessor is still finishing (programmatic dependent launch) and only waits for the
  * predecessor before reading Q and the rows from encoder_seq_len on. A caller whose previous kernel in
- * the stream writes the prefix rows must put an event or another kernel between the two. */
+ * the stream writes the prefix rows must put an event or another kernel between the two.
+ * episodes > 1 (an extension): that many independent episodes in one launch; `queries` and `keys` are
+ * per episode, episode e reads Q + e * q_episode_stride and K / V + e * kv_episode_stride (strides in
+ * elements, multiples of 8) and writes out + e * q_episode_stride. Needs keys <= 1408. */
 int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* out, int queries,
-                           int keys, int head_dim, int heads, int encoder_seq_len, void* ws,
+                           int keys, int head_dim, int heads, int encoder_seq_len, int episodes,
+                           long long q_episode_stride, long long kv_episode_stride, void* ws,
                            size_t ws_bytes, void* stream);
 /* fused_wrappers.py:45-54 / wrappers.py:192-198: out = gelu(rms(x) @ Wg) * (rms(x) @ Wu). When
  * norm_factor is not NULL the bf16 factor is also stored there (the unfused side effect). */

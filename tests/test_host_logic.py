@@ -203,6 +203,46 @@ def test_batched_prefix_pipeline_equals_independent_episodes(monkeypatch):
         pipeline.transformer_decoder(ops, w, b, S, steps=2, layers=L)
         assert torch.allclose(b["diffusion_noise"], want[e], atol=1e-5), f"episode {e}"
 
+    # the decoder batched as well: one pass over all episodes' rows, K / V in the per-episode caches
+    def dec_qkv(x, weight, rope, Q, K, V, nf):
+        if K.ndim == 2:
+            return base.decoder_norm_qkv_rope(x, weight, rope, Q, K, V, nf)
+        n, Dr = K.shape[0], K.shape[1]
+        for e in range(n):
+            rows = slice(e * Dr, (e + 1) * Dr)
+            base.decoder_norm_qkv_rope(x[rows], weight, rope, Q[e * Dr * 8:(e + 1) * Dr * 8], K[e], V[e], nf[rows])
+
+    def dec_attn(Q, K, V, scores, out, S_):
+        if K.ndim == 2:
+            return base.decoder_attention(Q, K, V, scores, out, S_)
+        n = K.shape[0]
+        per = Q.shape[0] // n
+        for e in range(n):
+            rows = slice(e * per, (e + 1) * per)
+            base.decoder_attention(Q[rows], K[e], V[e], torch.zeros(per, K.shape[1]), out[rows], S_)
+
+    def state_proj(x, weight, bias, out):           # the oracle's form takes one state vector
+        for e in range(x.shape[0]):
+            base.decoder_state_proj(x[e], weight, bias, out[e:e + 1])
+
+    ops2 = SimpleNamespace(**{**vars(ops), "decoder_norm_qkv_rope": dec_qkv, "decoder_attention": dec_attn,
+                              "decoder_state_proj": state_proj})
+    dec = {"observation_state_normalized": torch.stack([i[1] for i in inputs]),
+           "diffusion_noise": torch.stack([i[2] for i in inputs]).clone(),
+           "diffusion_noise_f32": torch.zeros(E * 50, 32), "decoder_rope_weights": ref_b["decoder_rope_weights"],
+           "decoder_x": torch.zeros(E * D, 1024), "decoder_x_buf": torch.zeros(E * 50, 1024),
+           "decoder_mlp_out": torch.zeros(E * 50, 1024), "decoder_x_rows": torch.zeros(E * 50, 1024),
+           "decoder_state_buf": torch.zeros(E, 1024), "decoder_norm_factor_buf": torch.zeros(E * D),
+           "decoder_q_buf": torch.zeros(E * D * 8, 256), "decoder_hidden": torch.zeros(E * D, 4096)}
+    prefix["encoder_K"][:, :, S:] = 0
+    prefix["encoder_V"][:, :, S:] = 0
+    pipeline.decoder_prologue_batched(ops2, w, dec)
+    for step in range(2):
+        pipeline.decoder_step_batched(ops2, w, prefix, dec, S, step, E, layers=L)
+    pipeline.decoder_epilogue_batched(dec)
+    for e in range(E):
+        assert torch.allclose(dec["diffusion_noise"][e], want[e], atol=1e-5), f"batched decoder, episode {e}"
+
 
 def test_engine_refuses_to_run_without_cuda():
     if torch.cuda.is_available():

@@ -159,14 +159,16 @@ def test_frozen_pool_refuses_new_scratch(full_checkpoint):
         pool.get("a", (8,), torch.float32, "cuda")
 
 
-@pytest.mark.parametrize("batch_prefix", [False, True])
-def test_concurrent_episodes_match_the_single_episode_engine(full_checkpoint, batch_prefix):
+@pytest.mark.parametrize("batch_prefix,batch_decoder", [(False, False), (True, False), (True, True)],
+                         ids=["streams", "batched-prefix", "batched-prefix-and-decoder"])
+def test_concurrent_episodes_match_the_single_episode_engine(full_checkpoint, batch_prefix, batch_decoder):
     """The throughput profile: E episodes inside one graph, shared weights, own KV caches and decoder buffers.
     batch_prefix=False runs E complete single-episode passes on E streams, the same kernels per episode as
     the single-episode engine: results must be bit-identical to it. batch_prefix=True runs SigLIP and the
     prefix encoder once over all episodes' rows (differently shaped launches of the same kernels, so the
-    results agree to rounding, not bit for bit). Either way every episode is checked against the oracle's
-    result for its own inputs."""
+    results agree to rounding, not bit for bit); batch_decoder=True also runs the action expert once over
+    all episodes' rows (M = 153 here), on the general GEMM kernels with per-episode attention inside one
+    launch. Either way every episode is checked against the oracle's result for its own inputs."""
     from flash_vla_b200 import Pi0Inference
 
     E = 3
@@ -175,8 +177,9 @@ def test_concurrent_episodes_match_the_single_episode_engine(full_checkpoint, ba
     want = [single.forward(*s).clone() for s in sets]
     del single
     torch.cuda.empty_cache()
-    multi = Pi0Inference(full_checkpoint, num_views=3, chunk_size=50, episodes=E, batch_prefix=batch_prefix)
-    assert multi.batch_prefix == batch_prefix
+    multi = Pi0Inference(full_checkpoint, num_views=3, chunk_size=50, episodes=E, batch_prefix=batch_prefix,
+                         batch_decoder=batch_decoder)
+    assert multi.batch_prefix == batch_prefix and multi.batch_decoder == batch_decoder
     batched = [torch.stack([s[i] for s in sets]) for i in range(3)]
     got = multi.forward(*batched).clone()
     got2 = multi.forward(*batched).clone()
