@@ -395,6 +395,7 @@ def run_ours(args):
                 "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (images, state, noise)),
                 "d2h_bytes_per_step": host_out.numel() * host_out.element_size()},
         "gpu_launches": int(per_forward * K * E), "gpu_launches_per_forward": int(per_forward),
+        "tuned_plans": int(engine.tuned_plans),
         "clocks": clock_summary,
         "published_h100_ms_per_forward": H100_PUBLISHED_MS,
     }
@@ -597,8 +598,16 @@ def main():
     p.add_argument("--sweep-layers", type=int, default=0, help="cap on distinct weight copies (small profiler runs)")
     p.add_argument("--sweep-reps", type=int, default=20)
     p.add_argument("--profile-pass", action="store_true", help="two eager forwards only (for ncu launch lists)")
+    p.add_argument("--autotune", action="store_true",
+                   help="sweep the launch plans of every GEMM call site and write the winners to the tuned-plan file")
+    p.add_argument("--autotune-sites", default="", help="comma-separated call sites (default: all)")
     args = p.parse_args()
-    if args.profile_pass:
+    if args.autotune:
+        from flash_vla_b200.hardware.nvidia.b200.pi0 import autotune
+        table = autotune.tune([x for x in args.autotune_sites.split(",") if x] or None, reps=args.sweep_reps)
+        autotune.save_plans(table)
+        print(json.dumps({"metric": "autotune", "plans": table["plans"], "report": table["report"]}))
+    elif args.profile_pass:
         run_profile_pass()
     elif args.sweep:
         run_sweep(args)

@@ -1,6 +1,8 @@
 // extern "C" surface of libfvla_b200: argument validation, kernel selection, launches.
 // Nothing here allocates, frees or synchronises.
 #include <atomic>
+#include <mutex>
+#include <vector>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -38,6 +40,20 @@ int check_launch(const char* what) {
     return FVLA_OK;
 }
 
+// ---- pinned launch plans (filled by the tuning harness or from a tuned-plan file) -----------------
+struct PlanEntry { int M, N, K, kind; PlanChoice choice; };
+static std::mutex g_plan_mutex;
+static std::vector<PlanEntry> g_plans;
+static std::atomic<int> g_plan_count{0};
+
+bool plan_lookup(int M, int N, int K, int kind, PlanChoice* out) {
+    if (g_plan_count.load(std::memory_order_acquire) == 0) return false;      // the common case: nothing pinned
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    for (const PlanEntry& e : g_plans)
+        if (e.M == M && e.N == N && e.K == K && e.kind == kind) { *out = e.choice; return true; }
+    return false;
+}
+
 static inline size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 static inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 static inline const bf16* B(const void* p) { return reinterpret_cast<const bf16*>(p); }
@@ -69,9 +85,13 @@ static size_t ws_factor_bytes(int M) { return align256((size_t)M * sizeof(float)
 static size_t ws_xnorm_bytes(int M, int K) { return align256((size_t)M * K * sizeof(bf16)); }
 static size_t op_ws_bytes(int M, int N, int K, bool dual) {
     size_t gemm = plan_gemm_mma(M, N, K, dual).ws_bytes;
-    if (!dual && M > 64) {                      // the tcgen05 kernel may split K through scratch
-        size_t t = tc5::plan_tc5(M, N, K, true).ws_bytes;
-        size_t t2 = tc5x2::plan_pair_plain(M, N, K, true).ws_bytes;
+    if (!dual && M > 64) {
+        // the tcgen05 kernels may split K through scratch: room for the widest plan either family can be
+        // given (4 splits at any tile width on the one-SM kernel, 6 on the pair kernel), so that a plan
+        // pinned later never finds the scratch too small
+        size_t t = 0;
+        for (int bn = 128; bn <= 256; bn += 64) { size_t v = tc5::scratch_split_bytes(M, N, bn, 4); if (v > t) t = v; }
+        size_t t2 = tc5x2::pair_split_bytes(M, N, 6);
         if (t2 > t) t = t2;
         if (t > gemm) gemm = t;
     }
@@ -139,6 +159,18 @@ static bool pair_enabled() {
 }
 
 static int launch_gemm(const GemmArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
+    PlanChoice pinned;
+    if (tc5_enabled() && tc5::tc5_supports(a) &&
+        plan_lookup(a.M, a.N, a.K, a.B2 != nullptr ? PLAN_DUAL : (a.rope != nullptr ? PLAN_ROPE : PLAN_PLAIN), &pinned)) {
+        GemmArgs g = a;
+        if (g.Kb == 0) g.Kb = g.K;
+        if (a.B2 != nullptr) {          // gated FFN: the only choice is the kernel family
+            if (pinned.engine == ENGINE_PAIR) return tc5x2::launch_geglu_pair(g, device_status_ptr(), st);
+            return tc5::launch_gemm_tc5(g, device_status_ptr(), st, ws, ws_bytes);
+        }
+        if (pinned.engine == ENGINE_PAIR) return tc5x2::launch_plain_pair_pinned(g, pinned.splits, ws, ws_bytes, device_status_ptr(), st);
+        return tc5::launch_gemm_tc5_pinned(g, pinned, device_status_ptr(), st, ws, ws_bytes);
+    }
     if (tc5_enabled() && pair_enabled() && a.B2 != nullptr && tc5::tc5_supports(a)) {
         GemmArgs g = a;
         if (g.Kb == 0) g.Kb = g.K;
@@ -166,7 +198,7 @@ using namespace fvla;
 extern "C" {
 
 const char* fvla_last_error(void) { return g_error; }
-int fvla_abi_version(void) { return 2; }
+int fvla_abi_version(void) { return 3; }
 unsigned long long fvla_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int fvla_device_status(void* stream) {
@@ -597,6 +629,38 @@ int fvla_embed_rows(const void* table, const long long* ids, void* out, int rows
     if (e != cudaSuccess) { set_error("embed_rows_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("embed_rows_kernel");
 }
+
+// ---- pinned launch plans -----------------------------------------------------------------------
+int fvla_gemm_plan_set(int M, int N, int K, int kind, int engine, int bn, int splits) {
+    FVLA_REQUIRE(M > 0 && N > 0 && K > 0 && kind >= PLAN_PLAIN && kind <= PLAN_SKINNY_DUAL, "gemm_plan_set: bad shape or kind");
+    bool ok = false;
+    switch (engine) {
+        case ENGINE_TC5_SCRATCH: ok = (kind == PLAN_PLAIN && (bn == 128 || bn == 192 || bn == 256) && splits >= 1 && splits <= 4) ||
+                                      (kind == PLAN_DUAL && splits == 1); break;
+        case ENGINE_TC5_CLUSTER: ok = kind == PLAN_PLAIN && splits >= 2 && splits <= 4; break;
+        case ENGINE_PAIR: ok = (kind == PLAN_PLAIN && splits >= 1 && splits <= 6) || (kind == PLAN_DUAL && splits == 1); break;
+        case ENGINE_SKINNY: ok = (kind == PLAN_SKINNY || kind == PLAN_SKINNY_DUAL) && (splits == 1 || splits == 2 || splits == 4 || splits == 8); break;
+        default: ok = false;
+    }
+    FVLA_REQUIRE(ok, "gemm_plan_set: engine %d with tile width %d and %d splits is not a plan for kind %d", engine, bn, splits, kind);
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    for (PlanEntry& e : g_plans)
+        if (e.M == M && e.N == N && e.K == K && e.kind == kind) { e.choice.engine = engine; e.choice.bn = bn; e.choice.splits = splits; return FVLA_OK; }
+    PlanEntry e{M, N, K, kind, {}};
+    e.choice.engine = engine; e.choice.bn = bn; e.choice.splits = splits;
+    g_plans.push_back(e);
+    g_plan_count.store((int)g_plans.size(), std::memory_order_release);
+    return FVLA_OK;
+}
+
+int fvla_gemm_plan_clear(void) {
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    g_plans.clear();
+    g_plan_count.store(0, std::memory_order_release);
+    return FVLA_OK;
+}
+
+int fvla_gemm_plan_count(void) { return g_plan_count.load(std::memory_order_acquire); }
 
 // ---- failure-detection self-test ---------------------------------------------------------------
 int fvla_selftest_wait_timeout(const void* x, const void* weight, void* out, int M, int N, int K,

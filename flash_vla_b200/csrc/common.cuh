@@ -154,6 +154,15 @@ unsigned long long* debug_next_slot();
 #define FVLA_STAMP(i) ((void)0)
 #endif
 
+// Tuned launch plans. The kernels choose tile width, K split and kernel family from cost models; a tuning
+// run (the sweep harness on the Python side) may pin a measured-best choice per GEMM shape instead. A
+// pinned plan that a launch cannot honour (scratch too small, an epilogue the family lacks) is an error
+// for that launch, never a silent substitute, so that a sweep sees which candidates are real.
+enum PlanKind { PLAN_PLAIN = 0, PLAN_ROPE = 1, PLAN_DUAL = 2, PLAN_SKINNY = 3, PLAN_SKINNY_DUAL = 4 };
+enum PlanEngine { ENGINE_AUTO = 0, ENGINE_TC5_SCRATCH = 1, ENGINE_TC5_CLUSTER = 2, ENGINE_PAIR = 3, ENGINE_SKINNY = 4 };
+struct PlanChoice { int engine = ENGINE_AUTO, bn = 0, splits = 0; };
+bool plan_lookup(int M, int N, int K, int kind, PlanChoice* out);
+
 // Host-side: record the message of the last failing call on this thread.
 void set_error(const char* fmt, ...);
 int check_launch(const char* what);

@@ -418,6 +418,18 @@ inline SkinnyPlan plan_skinny(int M, int N, int K, bool geglu) {
     if (M <= 0 || M > TOK || N % tile_n || K % 64) return pl;
     pl.tiles = N / tile_n;
     const int kb_total = K / 64;
+    PlanChoice pinned;
+    if (plan_lookup(M, N, K, geglu ? PLAN_SKINNY_DUAL : PLAN_SKINNY, &pinned)) {
+        // a pinned cluster size: 1, 2, 4 or 8 CTAs along K, at most 8 k-blocks each
+        const int s = pinned.splits;
+        if (s < 1 || s > 8 || (s & (s - 1)) || kb_total % s || kb_total / s > MAX_KB || ((kb_total / s) & (kb_total / s - 1))) return pl;
+        pl.splits = s;
+        pl.kblocks = kb_total / s;
+        pl.smem = 1024 + (size_t)(pl.kblocks < 2 ? 2 : pl.kblocks) * 16384 + 1024 + (size_t)pl.kblocks * 8192 + 32768 + 256 + 512 +
+                  (MAX_KB + 2) * 8 + 32;
+        pl.ok = true;
+        return pl;
+    }
     // largest cluster (<= 8) that divides the k-blocks, keeps <= 8 k-blocks per CTA and stays near one wave
     int best = 0;
     for (int s = 1; s <= 8; s *= 2) {       // 8 = largest portable cluster; larger ones schedule in waves

@@ -758,6 +758,43 @@ inline bool tc5_supports(const GemmArgs& g) {
            aligned16(g.A) && aligned16(g.B) && (g.B2 == nullptr || aligned16(g.B2));
 }
 
+// Scratch bytes of a split through global partials at tile width bn.
+inline size_t scratch_split_bytes(int M, int N, int bn, int splits) {
+    const size_t tiles = (size_t)((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+    return splits > 1 ? ((tiles * sizeof(int) + 255) / 256) * 256 + (size_t)splits * tiles * BM * bn * sizeof(float) : 0;
+}
+
+// A pinned plan for a plain GEMM on the one-SM kernel: `engine` ENGINE_TC5_SCRATCH (tile width bn, K split
+// through caller scratch) or ENGINE_TC5_CLUSTER (128-wide tiles, K split inside a cluster). Errors out when
+// the launch cannot honour it.
+inline int launch_gemm_tc5_pinned(GemmArgs g, const PlanChoice& pc, int* status, cudaStream_t st, void* ws, size_t ws_bytes) {
+    if (g.Kb == 0) g.Kb = g.K;
+    if (g.B2 != nullptr || g.rope != nullptr) { set_error("pinned plan: only plain GEMMs take a tile / split choice"); return FVLA_ERR_UNSUPPORTED; }
+    const int k_iters = (g.K + BK - 1) / BK;
+    if (pc.engine == ENGINE_TC5_CLUSTER) {
+        const int tiles = ((g.M + BM - 1) / BM) * ((g.N + 127) / 128);
+        if (pc.splits < 2 || pc.splits > 4 || tiles * pc.splits > num_sms() || k_iters / pc.splits < 2) {
+            set_error("pinned plan: cluster split %d does not fit %d tiles / %d k steps", pc.splits, tiles, k_iters);
+            return FVLA_ERR_UNSUPPORTED;
+        }
+        return launch_tc5_cfg<128, false, 6, false, true>(g, status, st, pc.splits, nullptr);
+    }
+    if (pc.splits < 1 || pc.splits > 4 || (pc.splits > 1 && (g.c_f32 || k_iters / pc.splits < 2))) {
+        set_error("pinned plan: scratch split %d not possible here", pc.splits);
+        return FVLA_ERR_UNSUPPORTED;
+    }
+    if (pc.splits > 1 && (ws == nullptr || ws_bytes < scratch_split_bytes(g.M, g.N, pc.bn, pc.splits))) {
+        set_error("pinned plan: scratch of %zu bytes needed", scratch_split_bytes(g.M, g.N, pc.bn, pc.splits));
+        return FVLA_ERR_WORKSPACE;
+    }
+    switch (pc.bn) {
+        case 256: return launch_tc5_cfg<256, false, 4>(g, status, st, pc.splits, ws);
+        case 192: return launch_tc5_cfg<192, false, 5>(g, status, st, pc.splits, ws);
+        case 128: return launch_tc5_cfg<128, false, 6>(g, status, st, pc.splits, ws);
+        default: set_error("pinned plan: tile width %d (128, 192 or 256)", pc.bn); return FVLA_ERR_ARG;
+    }
+}
+
 inline int launch_gemm_tc5(GemmArgs g, int* status, cudaStream_t st, void* ws = nullptr, size_t ws_bytes = 0) {
     if (g.Kb == 0) g.Kb = g.K;
     if (g.B2 != nullptr) return launch_tc5_cfg<128, true, 4>(g, status, st);

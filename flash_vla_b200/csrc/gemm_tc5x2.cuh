@@ -416,5 +416,27 @@ inline int launch_plain_pair(const GemmArgs& g, void* ws, size_t ws_bytes, int* 
     return launch_pair<false>(g, pl.splits, ws, status, st);
 }
 
+// Scratch bytes of the pair kernel's K split.
+inline size_t pair_split_bytes(int M, int N, int splits) {
+    const size_t tiles = (size_t)((M + 255) / 256) * ((N + 255) / 256);
+    return splits > 1 ? ((tiles * 2 * sizeof(int) + 255) / 256) * 256 + tiles * splits * 2 * 128 * 256 * sizeof(float) : 0;
+}
+
+// A pinned K split (1..6) for the plain form of the pair kernel; errors out when it cannot be honoured.
+inline int launch_plain_pair_pinned(const GemmArgs& g, int splits, void* ws, size_t ws_bytes, int* status, cudaStream_t st) {
+    if (g.B2 != nullptr || g.rope != nullptr || g.c_f32 || g.bias != nullptr || g.act != 0 || g.res_mod != 0 || g.row_scale != nullptr ||
+        (g.R != nullptr && g.ldr != g.ldc) || g.M <= 128 || g.N % 8 || g.K % 8) {
+        set_error("pinned plan: the pair kernel's plain form takes bf16 out (+ bf16 residual) only");
+        return FVLA_ERR_UNSUPPORTED;
+    }
+    const int k_iters = (g.K + BK - 1) / BK;
+    if (splits < 1 || splits > 6 || (splits > 1 && k_iters / splits < 2)) { set_error("pinned plan: pair split %d", splits); return FVLA_ERR_UNSUPPORTED; }
+    if (splits > 1 && (ws == nullptr || ws_bytes < pair_split_bytes(g.M, g.N, splits))) {
+        set_error("pinned plan: scratch of %zu bytes needed", pair_split_bytes(g.M, g.N, splits));
+        return FVLA_ERR_WORKSPACE;
+    }
+    return launch_pair<false>(g, splits, ws, status, st);
+}
+
 }  // namespace tc5x2
 }  // namespace fvla

@@ -33,10 +33,13 @@ SIGNATURES: dict[str, list] = {
     "fvla_decoder_action_out_proj": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
     "fvla_embed_rows": [_P, _P, _P, _I, _I, ctypes.c_longlong, _P],
     "fvla_selftest_wait_timeout": [_P, _P, _P, _I, _I, _I, ctypes.c_uint, _P],
+    "fvla_gemm_plan_set": [_I, _I, _I, _I, _I, _I, _I],
+    "fvla_gemm_plan_clear": [],
 }
 QUERIES: dict[str, tuple] = {
     "fvla_last_error": ([], c_char_p),
     "fvla_abi_version": ([], c_int),
+    "fvla_gemm_plan_count": ([], c_int),
     "fvla_launch_count": ([], ctypes.c_ulonglong),
     "fvla_device_status": ([_P], c_int),
     "fvla_gemm_workspace_bytes": ([_I, _I, _I, _I], c_size_t),

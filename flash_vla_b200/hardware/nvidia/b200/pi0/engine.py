@@ -44,7 +44,7 @@ class Pi0Inference:
     def __init__(self, checkpoint, num_views: int, chunk_size: int, steps: int = 10,
                  layers: int = 18, fused: bool = True, device: str = "cuda", plan=None,
                  capture: bool = True, episodes: int = 1, overlap: bool = True, embedding_table=None,
-                 batch_prefix: bool = True, batch_decoder: bool = False):
+                 batch_prefix: bool = True, batch_decoder: bool = False, tuned_plans="default"):
         if not torch.cuda.is_available():
             raise RuntimeError("Pi0Inference needs a CUDA device; the B200 target has no CPU path")
         if episodes < 1:
@@ -56,6 +56,12 @@ class Pi0Inference:
         # (decoder layer L only needs the prefix K/V of encoder layer L); same kernels, same results
         self.overlap = bool(overlap) and steps >= 1
         self.ops = op_table(fused, plan=plan)
+        # measured-best launch plans per GEMM shape (process-wide): "default" = the table shipped next to the
+        # sweep harness, if any; a dict or a path = that table; None = leave the library's cost models alone
+        from . import autotune
+        table = autotune.load_plans() if tuned_plans == "default" else (
+            tuned_plans if isinstance(tuned_plans, dict) or tuned_plans is None else autotune.load_plans(tuned_plans))
+        self.tuned_plans = autotune.apply_plans(table) if table is not None else 0
         self.prompt_len = int(checkpoint["language_embeds"].shape[0])
         # With an embedding table the prompt lookup is part of the captured pass: the graph gathers
         # table[prompt_ids] straight into the prefix rows, and `set_prompt(ids)` only rewrites the ids.

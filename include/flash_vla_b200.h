@@ -54,6 +54,22 @@ int fvla_device_status(void* stream);
 int fvla_selftest_wait_timeout(const void* x, const void* weight, void* out, int M, int N, int K,
                                unsigned spin_limit, void* stream);
 
+/* ---- Tuned launch plans ----------------------------------------------------------------------
+ * Counterpart of the reference's per-kernel configuration sweep (benchmarks/autotune.py), whose winners the
+ * reference writes into its TileLang kernel definitions. Here a measured-best launch plan can be pinned
+ * per GEMM shape at run time; unpinned shapes use the library's cost models. `kind`: 0 plain (bias /
+ * activation / residual epilogues), 1 QKV + RoPE, 2 gated FFN, 3 decoder cluster GEMM (M <= 64), 4 its
+ * gated form. `engine`: 1 one-SM tcgen05 kernel with tile width bn (128, 192, 256) and K split `splits`
+ * (1..4) through caller scratch; 2 the same kernel, 128-wide tiles, K split (2..4) inside a thread-block
+ * cluster; 3 the two-SM kernel, K split 1..6 through scratch (gated FFN: 1); 4 the decoder cluster GEMM
+ * with `splits` (1, 2, 4, 8) CTAs along K. A launch that cannot honour its pinned plan fails with an
+ * error instead of choosing another plan. Process-wide; set plans before capturing graphs and before the
+ * scratch of the affected ops is first used: split-K scratch holds tile counters whose layout depends on
+ * the plan, so one scratch buffer must not serve two plans. */
+int fvla_gemm_plan_set(int M, int N, int K, int kind, int engine, int bn, int splits);
+int fvla_gemm_plan_clear(void);
+int fvla_gemm_plan_count(void);
+
 /* Scratch needed by a GEMM-shaped op of the given logical size. `dual` = 1 for gated FFNs. */
 size_t fvla_gemm_workspace_bytes(int M, int N, int K, int dual);
 /* Scratch for the decoder's split-key attention with `queries` flat rows and `keys` keys. */

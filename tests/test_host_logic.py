@@ -299,3 +299,34 @@ def test_graft_entry_build_passes():
         sys.path.insert(0, root)
     entry = importlib.import_module("__graft_entry__")
     entry.build()
+
+
+def test_pinned_plan_table_validates_on_the_host():
+    """fvla_gemm_plan_set accepts only (kind, engine, tile width, split) combinations that exist; the table
+    is process-wide, replaceable and clearable. Pure host logic: no launch is made."""
+    from flash_vla_b200.hardware.nvidia.b200.pi0 import autotune
+    from flash_vla_b200.hardware.nvidia.b200.pi0.backends.cuda import _lib
+    lib = _lib.load()
+    K, E = autotune.KIND, autotune.ENGINE
+    assert lib.fvla_gemm_plan_clear() == 0 and lib.fvla_gemm_plan_count() == 0
+    assert lib.fvla_gemm_plan_set(768, 1152, 4304, K["plain"], E["tc5_scratch"], 192, 2) == 0
+    assert lib.fvla_gemm_plan_set(768, 1152, 4304, K["plain"], E["tc5_cluster"], 128, 3) == 0      # replaces, not adds
+    assert lib.fvla_gemm_plan_count() == 1
+    assert lib.fvla_gemm_plan_set(51, 4096, 1024, K["skinny_dual"], E["skinny"], 128, 2) == 0
+    assert lib.fvla_gemm_plan_count() == 2
+    for bad in ((768, 1152, 4304, K["plain"], E["tc5_scratch"], 160, 2),      # no such tile width
+                (768, 1152, 4304, K["plain"], E["tc5_cluster"], 128, 5),      # clusters split K at most 4 ways
+                (768, 1152, 4304, K["rope"], E["pair"], 256, 1),              # the RoPE epilogue has one kernel only
+                (51, 4096, 1024, K["skinny"], E["skinny"], 128, 3),           # cluster sizes are powers of two
+                (0, 1152, 4304, K["plain"], E["pair"], 256, 1)):
+        assert lib.fvla_gemm_plan_set(*bad) == -1, bad
+        assert b"gemm_plan_set" in lib.fvla_last_error()
+    assert lib.fvla_gemm_plan_count() == 2
+    assert lib.fvla_gemm_plan_clear() == 0 and lib.fvla_gemm_plan_count() == 0
+    # the sweep's candidate lists only name plans the table accepts
+    for site in autotune.SITES.values():
+        for cand in autotune.candidates(site):
+            assert lib.fvla_gemm_plan_set(*site.key(), E[cand["engine"]], cand["bn"], cand["splits"]) == 0, (site.name, cand)
+    lib.fvla_gemm_plan_clear()
+    assert autotune.grid(bn=[128, 256], splits=[1, 2]) == [{"bn": 128, "splits": 1}, {"bn": 128, "splits": 2},
+                                                            {"bn": 256, "splits": 1}, {"bn": 256, "splits": 2}]
