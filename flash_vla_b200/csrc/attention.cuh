@@ -348,30 +348,46 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
     const int owners = (rows_here + 3) / 4;                  // at most 8: ranks beyond that only send
     const bool i_own = (int)rank < owners;
 
+    // Prefix keys were written long before the preceding kernel: fetch them while it finishes. Rows
+    // past the end (keys of the ragged last split, queries of the last block) must read as zero.
+    const int pre_end = min(key_end, p.prefix_keys);
+    const uint32_t pre_bar = sbase + OFF_BAR + 24;
     if (tid == 0) {
+        const int n_pre = max(0, min(pre_end - key_beg, 128));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(in_bar) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pre_bar) : "memory");
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         if (i_own)
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(in_bar), "r"(SPL * (SLICE + 16)) : "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pre_bar), "r"(n_pre * 2 * HD * 2) : "memory");
     }
     // relaxed: the fence above already published the barrier to the cluster
     asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
-    auto load_rows = [&](uint32_t dst, const bf16* src, int row0, int row_lo, int row_hi, int nrows) {
-        // rows [row0, row0 + nrows) of `src` into dst; only rows in [row_lo, row_hi) are fetched now
-        for (int idx = tid; idx < nrows * CH; idx += THREADS) {
-            int r = idx / CH, c = idx % CH;
-            int g = row0 + r;
-            if (g >= row_lo && g < row_hi) cp_async16(dst + r * PITCH + c * 16, src + (size_t)g * HD + c * 8, 16);
-        }
+    // The prefix K and V rows (almost all of the tile) arrive as one 512-byte bulk copy per row (a row of the
+    // padded shared-memory tile is 16-byte aligned): thread t < 128 owns K row t, thread t >= 128 owns V row
+    // t - 128. About two hundred copy instructions per CTA instead of several thousand 16-byte ones, which
+    // is what a CTA that could only start after the previous kernel left its SM was waiting on.
+    auto bulk_row = [&](uint32_t dst, const bf16* src, uint32_t bar) {
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(dst), "l"(src), "r"(HD * 2), "r"(bar) : "memory");
     };
-    // Prefix keys were written long before the preceding kernel: fetch them while it finishes. Rows
-    // past the end (keys of the ragged last split, queries of the last block) must read as zero.
-    const int pre_end = min(key_end, p.prefix_keys);
-    load_rows(sK, gk, key_beg, key_beg, pre_end, 128);
-    load_rows(sV, gv, key_beg, key_beg, pre_end, 128);
-    cp_async_commit();
+    auto bounded_wait = [&](uint32_t bar) {
+        for (uint32_t i = 0; i < (1u << 22); ++i) {
+            uint32_t done;
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                         : "=r"(done) : "r"(bar), "r"(0) : "memory");
+            if (done) return;
+            if ((i & 1023u) == 1023u && *abort_flag) return;
+        }
+        *abort_flag = 1;
+    };
+    const int my_row = tid & 127;                              // row of this thread's K (tid < 128) or V tile
+    const uint32_t my_tile = tid < 128 ? sK : sV;
+    const bf16* my_src = tid < 128 ? gk : gv;
+    __syncthreads();                                           // the barriers are initialised
+    if (key_beg + my_row < pre_end) bulk_row(my_tile + my_row * PITCH, my_src + (size_t)(key_beg + my_row) * HD, pre_bar);
     for (int idx = tid; idx < 128 * CH; idx += THREADS) {
         int r = idx / CH, c = idx % CH;
         if (key_beg + r >= key_end) {
@@ -383,11 +399,28 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     FVLA_STAMP(1);
-    load_rows(sQ, gq, q0, q0, p.nq, BQ);
-    load_rows(sK, gk, key_beg, max(key_beg, pre_end), key_end, 128);
-    load_rows(sV, gv, key_beg, max(key_beg, pre_end), key_end, 128);
-    cp_async_commit();
-    cp_async_wait<0>();
+    // What the preceding kernel wrote (Q, and the new keys in the last split) is small and is what every CTA
+    // waits for next: 16-byte async copies reach shared memory sooner than a bulk copy does (about 1.0 us
+    // against 1.4 us from request to data), so they keep the old path.
+    {
+        const int post_lo = max(key_beg, pre_end);
+        for (int idx = tid; idx < BQ * CH; idx += THREADS) {
+            const int r = idx / CH, c = idx % CH;
+            if (q0 + r < p.nq) cp_async16(sQ + r * PITCH + c * 16, gq + (size_t)(q0 + r) * HD + c * 8, 16);
+        }
+        if (post_lo < key_end) {
+            for (int idx = tid; idx < 128 * CH; idx += THREADS) {
+                const int r = idx / CH, c = idx % CH, g = key_beg + r;
+                if (g >= post_lo && g < key_end) {
+                    cp_async16(sK + r * PITCH + c * 16, gk + (size_t)g * HD + c * 8, 16);
+                    cp_async16(sV + r * PITCH + c * 16, gv + (size_t)g * HD + c * 8, 16);
+                }
+            }
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+    }
+    bounded_wait(pre_bar);
     __syncthreads();
     FVLA_STAMP(2);
 

@@ -177,8 +177,11 @@ static int launch_gemm(const GemmArgs& a, void* ws, size_t ws_bytes, cudaStream_
         int rc = tc5x2::launch_geglu_pair(g, device_status_ptr(), st);
         if (rc != FVLA_ERR_UNSUPPORTED) return rc;
     }
-    if (tc5_enabled() && pair_enabled() && a.B2 == nullptr && tc5::tc5_supports(a)) {
-        // residual projections: take the CTA-pair kernel when its estimate beats the one-SM plan
+    if (tc5_enabled() && pair_enabled() && a.B2 == nullptr && a.bias == nullptr && a.act == 0 && tc5::tc5_supports(a)) {
+        // residual projections without bias: take the CTA-pair kernel when its estimate beats the one-SM plan.
+        // (With a bias or GELU epilogue, i.e. at the SigLIP call sites, the pair kernel measured slower than
+        // the one-SM plans at every site, 15.5 - 18.9 us against 10.9 - 17.0 us; it is reachable there
+        // through a pinned plan only.)
         GemmArgs g = a;
         if (g.Kb == 0) g.Kb = g.K;
         tc5x2::PairPlan pp = tc5x2::plan_pair_plain(g.M, g.N, g.K, ws != nullptr);
@@ -558,7 +561,7 @@ int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* ou
         set_error("decoder_attention: workspace of %zu bytes needed", fvla_decoder_attention_workspace_bytes(queries, keys));
         return FVLA_ERR_WORKSPACE;
     }
-    if (tc5_enabled() && keys <= decattn::MAX_SPL * 128) {        // cluster kernel: 8..11 key splits of at most 128 keys
+    if (tc5_enabled() && keys <= decattn::MAX_SPL * 128 && aligned16(Q) && aligned16(K) && aligned16(V)) {        // cluster kernel: 8..11 key splits of at most 128 keys
         DecAttnArgs d{};
         d.q = B(Q); d.k = B(K); d.v = B(V); d.out = Bm(out);
         d.splits = (keys + 127) / 128 < decattn::MIN_SPL ? decattn::MIN_SPL : (keys + 127) / 128;

@@ -274,6 +274,22 @@ tc5x2_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, c
                 } else {
                     tmem_ld32(t_row + c * 32, a);
                 }
+                if (!DUAL && p.bias) {
+                    // bias of this chunk's 32 columns (the same for every row: broadcast loads)
+                    const int col0 = n0 + c * 32;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8)
+                        if (col0 + j + 8 <= p.N) {
+                            const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + j));
+                            const float2 b0 = unpack_bf16x2(bv.x), b1 = unpack_bf16x2(bv.y), b2 = unpack_bf16x2(bv.z), b3 = unpack_bf16x2(bv.w);
+                            a[j] += b0.x; a[j + 1] += b0.y; a[j + 2] += b1.x; a[j + 3] += b1.y;
+                            a[j + 4] += b2.x; a[j + 5] += b2.y; a[j + 6] += b3.x; a[j + 7] += b3.y;
+                        }
+                }
+                if (!DUAL && p.act == 1) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) a[j] = gelu_f(a[j]);
+                }
                 if (DUAL) {
                     float u[32];
                     tmem_ld32(t_row + 128 + c * 32, u);      // matching up columns
@@ -405,11 +421,16 @@ inline int launch_geglu_pair(const GemmArgs& g, int* status, cudaStream_t st) {
     return launch_pair<true>(g, 1, nullptr, status, st);
 }
 
-// out = A @ W (+ bf16 residual), bf16 destination, no bias / activation / RoPE: FVLA_ERR_UNSUPPORTED otherwise.
+// What the plain form of the pair kernel can take: out = act(A @ W + bias) + bf16 residual, bf16 destination,
+// act none or GELU, no RoPE, no per-row scale, residual laid out like the destination.
+inline bool pair_plain_supports(const GemmArgs& g) {
+    return g.B2 == nullptr && g.rope == nullptr && !g.c_f32 && (g.act == 0 || g.act == 1) && g.res_mod == 0 && g.row_scale == nullptr &&
+           (g.bias == nullptr || aligned16(g.bias)) && (g.R == nullptr || g.ldr == g.ldc) && g.M > 128 && g.N % 8 == 0 && g.K % 8 == 0;
+}
+
+// FVLA_ERR_UNSUPPORTED when the epilogue is outside `pair_plain_supports`.
 inline int launch_plain_pair(const GemmArgs& g, void* ws, size_t ws_bytes, int* status, cudaStream_t st) {
-    if (g.B2 != nullptr || g.rope != nullptr || g.c_f32 || g.bias != nullptr || g.act != 0 || g.res_mod != 0 || g.row_scale != nullptr ||
-        (g.R != nullptr && g.ldr != g.ldc))
-        return FVLA_ERR_UNSUPPORTED;
+    if (!pair_plain_supports(g)) return FVLA_ERR_UNSUPPORTED;
     PairPlan pl = plan_pair_plain(g.M, g.N, g.K, ws != nullptr);
     if (pl.ok && pl.splits > 1 && ws_bytes < pl.ws_bytes) pl = plan_pair_plain(g.M, g.N, g.K, false);
     if (!pl.ok) return FVLA_ERR_UNSUPPORTED;
@@ -424,9 +445,8 @@ inline size_t pair_split_bytes(int M, int N, int splits) {
 
 // A pinned K split (1..6) for the plain form of the pair kernel; errors out when it cannot be honoured.
 inline int launch_plain_pair_pinned(const GemmArgs& g, int splits, void* ws, size_t ws_bytes, int* status, cudaStream_t st) {
-    if (g.B2 != nullptr || g.rope != nullptr || g.c_f32 || g.bias != nullptr || g.act != 0 || g.res_mod != 0 || g.row_scale != nullptr ||
-        (g.R != nullptr && g.ldr != g.ldc) || g.M <= 128 || g.N % 8 || g.K % 8) {
-        set_error("pinned plan: the pair kernel's plain form takes bf16 out (+ bf16 residual) only");
+    if (!pair_plain_supports(g)) {
+        set_error("pinned plan: the pair kernel's plain form takes a bf16 destination, bias, GELU and a bf16 residual only");
         return FVLA_ERR_UNSUPPORTED;
     }
     const int k_iters = (g.K + BK - 1) / BK;

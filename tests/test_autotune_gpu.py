@@ -29,7 +29,8 @@ def test_pinned_plans_reproduce_the_default_result(clean_plans):
     x, w = torch.randn(M, K, generator=g).to(bf16).cuda(), (torch.randn(K, N, generator=g) * 0.02).to(bf16).cuda()
     b, res = (torch.randn(N, generator=g) * 0.02).to(bf16).cuda(), torch.randn(M, N, generator=g).to(bf16).cuda()
     want = res.float().cpu() + x.float().cpu() @ w.float().cpu() + b.float().cpu()
-    for plan in (None, ("tc5_scratch", 192, 2), ("tc5_scratch", 256, 1), ("tc5_cluster", 128, 2), ("tc5_scratch", 128, 4)):
+    for plan in (None, ("tc5_scratch", 192, 2), ("tc5_scratch", 256, 1), ("tc5_cluster", 128, 2), ("tc5_scratch", 128, 4),
+                 ("pair", 256, 1), ("pair", 256, 3)):
         table = None if plan is None else {"plans": [{"M": M, "N": N, "K": K, "kind": "plain", "engine": plan[0],
                                                        "bn": plan[1], "splits": plan[2]}]}
         assert autotune.apply_plans(table) == (0 if plan is None else 1)
@@ -38,8 +39,8 @@ def test_pinned_plans_reproduce_the_default_result(clean_plans):
             ops.vision_ffn_down_residual(x, w, b, res, out)
         torch.cuda.synchronize()
         assert_close(out, want, what=f"vision_ffn_down_residual under plan {plan}")
-    # the two-SM kernel has no bias epilogue: pinned for this call site, the launch must fail, not fall back
-    autotune.apply_plans({"plans": [{"M": M, "N": N, "K": K, "kind": "plain", "engine": "pair", "bn": 256, "splits": 1}]})
+    # a 4-way cluster split of this shape needs 216 CTAs at once: pinned, the launch must fail, not fall back
+    autotune.apply_plans({"plans": [{"M": M, "N": N, "K": K, "kind": "plain", "engine": "tc5_cluster", "bn": 128, "splits": 4}]})
     with wrappers.use_pool(ScratchPool()), pytest.raises(_lib.FvlaError, match="pinned plan"):
         ops.vision_ffn_down_residual(x, w, b, res, torch.zeros(M, N, dtype=bf16, device="cuda"))
     torch.cuda.synchronize()
