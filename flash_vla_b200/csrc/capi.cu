@@ -625,6 +625,20 @@ int fvla_decoder_action_out_proj(const void* x, int x_is_f32, const void* weight
     return check_launch("action_out_kernel");
 }
 
+int fvla_convert_copy(const void* src, int src_is_f32, void* dst, int dst_is_f32, void* dst_shadow, size_t count, void* stream) {
+    FVLA_REQUIRE(src != nullptr && dst != nullptr && count > 0 && count <= ((size_t)1 << 31), "convert_copy: null pointer or bad count");
+    FVLA_REQUIRE(dst_shadow == nullptr || dst_is_f32, "convert_copy: a bf16 shadow only makes sense for an fp32 destination");
+    const dim3 grid((unsigned)((count + 255) / 256)), block(256);
+    cudaStream_t st = S(stream);
+    cudaError_t e;
+    if (src_is_f32 && dst_is_f32) e = launch_pdl(convert_copy_kernel<float, float>, grid, block, 0, st, (const float*)src, (float*)dst, Bm(dst_shadow), count);
+    else if (src_is_f32) e = launch_pdl(convert_copy_kernel<float, bf16>, grid, block, 0, st, (const float*)src, Bm(dst), Bm(dst_shadow), count);
+    else if (dst_is_f32) e = launch_pdl(convert_copy_kernel<bf16, float>, grid, block, 0, st, B(src), (float*)dst, Bm(dst_shadow), count);
+    else e = launch_pdl(convert_copy_kernel<bf16, bf16>, grid, block, 0, st, B(src), Bm(dst), Bm(dst_shadow), count);
+    if (e != cudaSuccess) { set_error("convert_copy_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
+    return check_launch("convert_copy_kernel");
+}
+
 int fvla_embed_rows(const void* table, const long long* ids, void* out, int rows, int dim, long long vocab, void* stream) {
     FVLA_REQUIRE(rows > 0 && dim > 0 && dim % 8 == 0 && vocab > 0, "embed_rows: bad shape rows=%d dim=%d (dim %% 8 == 0)", rows, dim);
     FVLA_REQUIRE(table != nullptr && ids != nullptr && out != nullptr && aligned16(table) && aligned16(out), "embed_rows: null or misaligned pointer");

@@ -184,6 +184,22 @@ __global__ void __launch_bounds__(256) action_out_kernel(const XT* __restrict__ 
     }
 }
 
+// dst[i] = src[i] between bf16 and fp32 buffers (any of the four combinations), optionally also writing the
+// value as bf16 to `shadow`. The small copies inside the decoder step (state token into the residual
+// stream, the action chunk to and from its fp32 master) go through this kernel instead of a framework copy
+// so that they stay inside the chain of programmatic dependent launches.
+template <typename ST, typename DT>
+__global__ void __launch_bounds__(256) convert_copy_kernel(const ST* __restrict__ src, DT* __restrict__ dst,
+                                                           bf16* __restrict__ shadow, size_t count) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const float v = static_cast<float>(src[i]);
+    dst[i] = static_cast<DT>(v);
+    if (shadow) shadow[i] = __float2bfloat16_rn(v);
+}
+
 // dst[i] = bf16(src[i]), four values per thread.
 __global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* __restrict__ src, bf16* __restrict__ dst, size_t quads) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;

@@ -32,6 +32,7 @@ SIGNATURES: dict[str, list] = {
     "fvla_decoder_norm_gated_ffn": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _Z, _P],
     "fvla_decoder_action_out_proj": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
     "fvla_embed_rows": [_P, _P, _P, _I, _I, ctypes.c_longlong, _P],
+    "fvla_convert_copy": [_P, _I, _P, _I, _P, _Z, _P],
     "fvla_selftest_wait_timeout": [_P, _P, _P, _I, _I, _I, ctypes.c_uint, _P],
     "fvla_gemm_plan_set": [_I, _I, _I, _I, _I, _I, _I],
     "fvla_gemm_plan_clear": [],

@@ -96,6 +96,18 @@ def sync_shadow(t: torch.Tensor) -> None:
         shadow.view(-1)[first:first + t.numel()].copy_(t.reshape(-1))
 
 
+def copy_rows(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    """dst.copy_(src) for contiguous bf16 / fp32 CUDA tensors of equal size, as one kernel of this library
+    (it also refreshes the bf16 shadow of a registered fp32 `dst`). The pipeline's small copies (state token
+    into the residual stream, action chunk to and from its fp32 master) use it so that no framework kernel
+    interrupts the chain of dependent launches. Not in the reference table, where these are torch copies."""
+    if dst.numel() != src.numel():
+        raise ValueError(f"copy_rows: {src.numel()} elements into {dst.numel()}")
+    _lib.call("fvla_convert_copy", _chk("src", src, dtype=None), _is_f32("src", src), _chk("dst", dst, dtype=None),
+              _is_f32("dst", dst), _shadow_of(dst), dst.numel(), _stream())
+    return dst
+
+
 def embed_prompt(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[r] = table[ids[r]]: the prompt embedding lookup (a plain row gather, no scaling). Not in the
     reference table, which only accepts precomputed `language_embeds` (engine.py:43, :60)."""
@@ -439,4 +451,4 @@ DECODER_WRAPPERS = {f.__name__: f for f in (
 
 # `sync_shadow` rides in the table so that orchestration code can reach it through `ops`.
 ALL_WRAPPERS = {**VISION_WRAPPERS, **ENCODER_WRAPPERS, **DECODER_WRAPPERS, "sync_shadow": sync_shadow,
-                "embed_prompt": embed_prompt}
+                "embed_prompt": embed_prompt, "copy_rows": copy_rows}

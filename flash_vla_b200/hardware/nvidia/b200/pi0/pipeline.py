@@ -97,6 +97,17 @@ def transformer_encoder_batched(ops, weights, buffers, encoder_seq_len, num_view
         ops.encoder_ffn_down_residual(b["encoder_hidden"], w["encoder_ffn_down_w"][layer], x)
 
 
+def _copy(ops, dst, src):
+    """dst <- src through the table's own copy kernel when it has one (it also refreshes a bf16 shadow of
+    `dst`), else a framework copy followed by the shadow refresh."""
+    if ops is not None and hasattr(ops, "copy_rows"):
+        ops.copy_rows(dst, src)
+        return
+    dst.copy_(src)
+    if ops is not None and hasattr(ops, "sync_shadow"):
+        ops.sync_shadow(dst)
+
+
 def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LAYERS, noise=None,
                  before_layer=None):
     """One flow-matching Euler step over `noise` (default: the plan's master copy). `before_layer(layer)`,
@@ -105,9 +116,7 @@ def decoder_step(ops, weights, buffers, encoder_seq_len, step, layers=ENCODER_LA
     if noise is None:
         noise = b["diffusion_noise_f32"] if "diffusion_noise_f32" in b else b["diffusion_noise"]
     x, nf = b["decoder_x"], b["decoder_norm_factor_buf"]
-    x[:1].copy_(b["decoder_state_buf"])
-    if hasattr(ops, "sync_shadow"):          # a backend keeping a bf16 copy of x must see this write
-        ops.sync_shadow(x[:1])
+    _copy(ops, x[:1], b["decoder_state_buf"])
     ops.decoder_action_in_proj(noise, w["decoder_action_fused_in_proj_w"],
                                w["decoder_action_fused_time_biases"][step % DIFFUSION_STEPS],
                                b["decoder_x_buf"])
@@ -177,14 +186,14 @@ def decoder_prologue(ops, weights, buffers):
                            weights["decoder_state_in_proj_b"], b["decoder_state_buf"])
     master = b.get("diffusion_noise_f32")
     if master is not None:
-        master.copy_(b["diffusion_noise"])
+        _copy(ops, master, b["diffusion_noise"])
 
 
-def decoder_epilogue(buffers):
+def decoder_epilogue(buffers, ops=None):
     """Refresh the bf16 action chunk from its fp32 master."""
     master = buffers.get("diffusion_noise_f32")
     if master is not None:
-        buffers["diffusion_noise"].copy_(master)
+        _copy(ops, buffers["diffusion_noise"], master)
 
 
 def transformer_decoder(ops, weights, buffers, encoder_seq_len, steps=DIFFUSION_STEPS,
@@ -197,4 +206,4 @@ def transformer_decoder(ops, weights, buffers, encoder_seq_len, steps=DIFFUSION_
         decoder_prologue(ops, weights, b)
     for step in range(first_step, steps):
         decoder_step(ops, weights, b, encoder_seq_len, step, layers, noise=master)
-    decoder_epilogue(b)
+    decoder_epilogue(b, ops)

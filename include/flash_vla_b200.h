@@ -187,6 +187,13 @@ int fvla_decoder_action_out_proj(const void* x, int x_is_f32, const void* weight
                                  int out_is_f32, void* mirror, void* norm_factor, int M, int N,
                                  int K, void* stream);
 
+/* No counterpart in the reference, where these are torch `copy_` calls inside the pipeline (pipeline.py:103,
+ * engine.py:60): dst[i] = src[i] for `count` contiguous elements, each side bf16 or fp32; dst_shadow (may be
+ * NULL; fp32 dst only) also receives the value as bf16. Keeps the small copies of the decoder step inside the
+ * chain of programmatic dependent launches. */
+int fvla_convert_copy(const void* src, int src_is_f32, void* dst, int dst_is_f32, void* dst_shadow,
+                      size_t count, void* stream);
+
 /* No counterpart in the reference, which accepts only precomputed `language_embeds` (engine.py:43, :60):
  * out[r, :] = table[ids[r], :], bf16 rows of `dim` elements (dim % 8 == 0), ids int64 on the device. An id
  * outside [0, vocab) gives a zero row and makes fvla_device_status report 7. */

@@ -47,7 +47,7 @@ def test_op_table_contract():
         "decoder_action_mlp", "decoder_norm_qkv_rope", "decoder_attention", "decoder_out_proj_residual",
         "decoder_ffn_down_residual", "decoder_norm_gated_ffn", "decoder_action_out_proj"}
     assert reference_names <= set(cuda.ALL_WRAPPERS)
-    assert set(cuda.ALL_WRAPPERS) - reference_names == {"vision_attention", "encoder_attention", "sync_shadow", "embed_prompt"}
+    assert set(cuda.ALL_WRAPPERS) - reference_names == {"vision_attention", "encoder_attention", "sync_shadow", "embed_prompt", "copy_rows"}
     assert set(DEFAULT_FUSED_OPS) == {"decoder_norm_gated_ffn", "decoder_action_out_proj", "decoder_attention"}
     fused, unfused = op_table(True), op_table(False)
     assert fused.decoder_attention is cuda.FUSED_WRAPPERS["decoder_attention"]

@@ -325,3 +325,24 @@ def test_embed_prompt_reports_a_bad_id(ops):
     assert lib.fvla_device_status(None) == 0
     assert torch.equal(out[0], table[3]) and torch.equal(out[2], table[7])
     assert (out[1] == 0).all() and (out[3] == 0).all()
+
+
+@pytest.mark.parametrize("src_dtype,dst_dtype", [(bf16, torch.float32), (torch.float32, bf16), (torch.float32, torch.float32), (bf16, bf16)])
+def test_copy_rows_converts_and_refreshes_the_shadow(ops, src_dtype, dst_dtype):
+    """The library's own copy kernel (used for the decoder's small copies): any bf16 / fp32 pairing, a row-offset
+    view as destination, and the bf16 shadow of a registered fp32 destination kept current."""
+    from flash_vla_b200.hardware.nvidia.b200.pi0.backends.cuda import wrappers
+    g = torch.Generator().manual_seed(12)
+    src = torch.randn(3, 1024, generator=g).to(src_dtype).cuda()
+    owner = torch.zeros(7, 1024, dtype=dst_dtype, device="cuda")
+    shadow = None
+    if dst_dtype == torch.float32:
+        shadow = torch.full((7, 1024), 5.0, dtype=bf16, device="cuda")
+        wrappers.register_bf16_shadow(owner, shadow)
+    ops[1].copy_rows(owner[2:5], src)
+    torch.cuda.synchronize()
+    assert torch.equal(owner[2:5], src.to(dst_dtype)) and (owner[:2] == 0).all() and (owner[5:] == 0).all()
+    if shadow is not None:
+        assert torch.equal(shadow[2:5], src.to(bf16)) and (shadow[:2] == 0).all()
+    with pytest.raises(ValueError):
+        ops[1].copy_rows(owner[2:4], src)
