@@ -177,15 +177,16 @@ static int launch_gemm(const GemmArgs& a, void* ws, size_t ws_bytes, cudaStream_
         int rc = tc5x2::launch_geglu_pair(g, device_status_ptr(), st);
         if (rc != FVLA_ERR_UNSUPPORTED) return rc;
     }
-    if (tc5_enabled() && pair_enabled() && a.B2 == nullptr && a.bias == nullptr && a.act == 0 && tc5::tc5_supports(a)) {
+    if (tc5_enabled() && pair_enabled() && a.B2 == nullptr && a.bias == nullptr && a.act == 0 && !a.c_f32 && tc5::tc5_supports(a)) {
         // residual projections without bias: take the CTA-pair kernel when its estimate beats the one-SM plan.
         // (With a bias or GELU epilogue, i.e. at the SigLIP call sites, the pair kernel measured slower than
         // the one-SM plans at every site, 15.5 - 18.9 us against 10.9 - 17.0 us; it is reachable there
-        // through a pinned plan only.)
+        // through a pinned plan only. The same holds for an fp32 destination, the residual projections of
+        // a decoder batched over episodes: 33 - 43 us on the pair kernel against 18 - 21 us.)
         GemmArgs g = a;
         if (g.Kb == 0) g.Kb = g.K;
         tc5x2::PairPlan pp = tc5x2::plan_pair_plain(g.M, g.N, g.K, ws != nullptr);
-        if (pp.ok && pp.est_us < tc5::plan_tc5(g.M, g.N, g.K, ws != nullptr).est_us) {
+        if (pp.ok && pp.est_us < tc5::plan_tc5(g.M, g.N, g.K, ws != nullptr && !g.c_f32).est_us) {
             int rc = tc5x2::launch_plain_pair(g, ws, ws_bytes, device_status_ptr(), st);
             if (rc != FVLA_ERR_UNSUPPORTED) return rc;
         }

@@ -217,7 +217,7 @@ tc5x2_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, c
                     for (int i = 0; i < 4; ++i) {
                         rco[DUAL ? 0 : c][i] = make_uint4(0, 0, 0, 0);
                         const int grow = m0 + quad * 32 + sr + 8 * i, gcol = n0 + c * 32 + sp * 8;
-                        if (p.R && grow < p.M && gcol < p.N)
+                        if (p.R && !p.c_f32 && grow < p.M && gcol < p.N)
                             rco[DUAL ? 0 : c][i] = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.R) + (size_t)grow * p.ldr + gcol);
                     }
             }
@@ -289,6 +289,24 @@ tc5x2_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, c
                 if (!DUAL && p.act == 1) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) a[j] = gelu_f(a[j]);
+                }
+                if (!DUAL && p.c_f32) {
+                    // fp32 destination (and fp32 residual, usually the destination itself): this thread owns 32
+                    // consecutive floats of its row, 128 contiguous bytes, read and written as float4
+                    const int grow = m0 + quad * 32 + lane, col0 = n0 + c * 32;
+                    if (grow < p.M) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            if (col0 + j + 4 > p.N) break;
+                            float4 v = make_float4(a[j], a[j + 1], a[j + 2], a[j + 3]);
+                            if (p.R) {
+                                const float4 r = *reinterpret_cast<const float4*>(static_cast<const float*>(p.R) + (size_t)grow * p.ldr + col0 + j);
+                                v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+                            }
+                            *reinterpret_cast<float4*>(static_cast<float*>(p.C) + (size_t)grow * p.ldc + col0 + j) = v;
+                        }
+                    }
+                    continue;
                 }
                 if (DUAL) {
                     float u[32];
@@ -421,10 +439,11 @@ inline int launch_geglu_pair(const GemmArgs& g, int* status, cudaStream_t st) {
     return launch_pair<true>(g, 1, nullptr, status, st);
 }
 
-// What the plain form of the pair kernel can take: out = act(A @ W + bias) + bf16 residual, bf16 destination,
-// act none or GELU, no RoPE, no per-row scale, residual laid out like the destination.
+// What the plain form of the pair kernel can take: out = act(A @ W + bias) + residual, destination and residual
+// both bf16 or both fp32, act none or GELU, no RoPE, no per-row scale, residual laid out like the destination.
 inline bool pair_plain_supports(const GemmArgs& g) {
-    return g.B2 == nullptr && g.rope == nullptr && !g.c_f32 && (g.act == 0 || g.act == 1) && g.res_mod == 0 && g.row_scale == nullptr &&
+    return g.B2 == nullptr && g.rope == nullptr && (g.act == 0 || g.act == 1) && g.res_mod == 0 && g.row_scale == nullptr &&
+           (!g.c_f32 || (g.N % 4 == 0 && g.ldc % 4 == 0 && aligned16(g.C))) &&
            (g.bias == nullptr || aligned16(g.bias)) && (g.R == nullptr || g.ldr == g.ldc) && g.M > 128 && g.N % 8 == 0 && g.K % 8 == 0;
 }
 
@@ -446,7 +465,7 @@ inline size_t pair_split_bytes(int M, int N, int splits) {
 // A pinned K split (1..6) for the plain form of the pair kernel; errors out when it cannot be honoured.
 inline int launch_plain_pair_pinned(const GemmArgs& g, int splits, void* ws, size_t ws_bytes, int* status, cudaStream_t st) {
     if (!pair_plain_supports(g)) {
-        set_error("pinned plan: the pair kernel's plain form takes a bf16 destination, bias, GELU and a bf16 residual only");
+        set_error("pinned plan: the pair kernel's plain form takes bias, GELU and a residual of the destination's type only");
         return FVLA_ERR_UNSUPPORTED;
     }
     const int k_iters = (g.K + BK - 1) / BK;

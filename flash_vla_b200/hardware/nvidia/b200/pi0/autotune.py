@@ -99,6 +99,8 @@ SITES = {s.name: s for s in (
     CallSite("vis_up_x4", 3072, 4304, 1152, "plain", 6), CallSite("vis_down_x4", 3072, 1152, 4304, "plain", 6),
     CallSite("enc_o_x4", 3072, 2048, 2048, "plain", 6), CallSite("enc_down_x4", 3072, 2048, 16384, "plain", 4),
     CallSite("enc_gate_x4", 3072, 16384, 2048, "dual", 4),
+    # the residual projections of a decoder batched over 4 episodes (M = 204, fp32 residual stream, no shadow)
+    CallSite("dec_o_x4", 204, 1024, 2048, "plain", 18), CallSite("dec_down_x4", 204, 1024, 4096, "plain", 18),
 )}
 
 
@@ -165,7 +167,8 @@ def build_site(site: CallSite, ops, generator):
     if name in ("dec_o", "dec_down"):
         x = rnd(M, K)
         out = torch.zeros(M, N, device="cuda")
-        wrappers.register_bf16_shadow(out, torch.zeros(M, N, device="cuda", dtype=bf16))
+        if M <= 64:
+            wrappers.register_bf16_shadow(out, torch.zeros(M, N, device="cuda", dtype=bf16))
         return (lambda i: ops.decoder_ffn_down_residual(x, w[i], out)), out
     if name == "dec_action_mlp":
         x, bias = rnd(M, K), rnd(N, scale=0.02)
