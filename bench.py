@@ -257,8 +257,8 @@ def run_reference(args):
 def workload_config(n_gpus: int, episodes: int = 1):
     return {"workload": "Pi0 full forward: 3 views 224x224x3, empty prompt (prefix 768), chunk 50, 10 Euler steps, "
                         "27 SigLIP + 18 prefix + 18 decoder layers, batch 1, one CUDA graph" +
-                        ("" if episodes == 1 else f"; {episodes} independent episodes per GPU inside the graph (vision and prefix encoder "
-                                                  f"batched over the episodes, decoders on concurrent streams)"),
+                        ("" if episodes == 1 else f"; {episodes} independent episodes per GPU inside the graph (vision, prefix encoder "
+                                                  f"and decoder batched over the episodes)"),
             "weights": "random_checkpoint N(0, 0.02) bf16, 2.709 G params",
             "replicas": n_gpus, "episodes_per_gpu": episodes, "parallelism": f"replicas x{n_gpus} (no collective)",
             "l2": "each step streams 5.4 GB of weights, far more than the 126 MB L2; no explicit flush"}
@@ -320,8 +320,8 @@ def measure_throughput_profile(weights, rank, world, n_gpus, K, W, episodes=4):
 
 
 def engine_form(episodes):
-    return (f"{episodes} episodes per captured pass: SigLIP and the prefix encoder once over all episodes' rows "
-            f"(M = {episodes} x 768), the {episodes} action-expert decoders on {episodes} concurrent streams, shared weights")
+    return (f"{episodes} episodes per captured pass: SigLIP, the prefix encoder (M = {episodes} x 768) and the action-expert decoder "
+            f"(M = {episodes} x 51) each run once over all episodes' rows; attention per episode; shared weights")
 
 
 def run_ours(args):

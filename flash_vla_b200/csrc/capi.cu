@@ -436,10 +436,14 @@ static int refresh_shadow(const void* src, void* dst, size_t count, cudaStream_t
 }
 
 int fvla_linear_residual(const void* x, const void* weight, void* out, int out_is_f32, void* out_shadow, int M,
-                         int N, int K, void* ws, size_t ws_bytes, void* stream) {
-    if (tc5_enabled() && skinny::plan_skinny(M, N, K, false).ok && aligned16(x) && aligned16(weight)) {
+                         int N, int K, int group_rows, void* ws, size_t ws_bytes, void* stream) {
+    FVLA_REQUIRE(group_rows >= 0 && (group_rows == 0 || M % group_rows == 0), "linear_residual: M=%d is not a whole number of groups of %d rows", M, group_rows);
+    // rows as several groups of at most 64 (a batch of episodes): the decoder's cluster GEMM once per group in
+    // one launch, each group streaming the weights from L2 after the first has pulled them from HBM
+    const int rows = group_rows > 0 ? group_rows : M, groups = group_rows > 0 ? M / group_rows : 1;
+    if (tc5_enabled() && skinny::plan_skinny(rows, N, K, false).ok && aligned16(x) && aligned16(weight)) {
         skinny::SkinnyArgs sa{};
-        sa.x = x; sa.x_f32 = 0; sa.ldx = K; sa.M = M; sa.N = N; sa.K = K;
+        sa.x = x; sa.x_f32 = 0; sa.ldx = K; sa.M = rows; sa.N = N; sa.K = K; sa.groups = groups;
         sa.out = out; sa.out_f32 = out_is_f32; sa.ldo = N; sa.out_shadow = Bm(out_shadow);
         sa.status = device_status_ptr(); FVLA_DBG_ATTACH(sa);
         return skinny::launch_skinny<skinny::EPI_RESIDUAL>(sa, weight, nullptr, N, S(stream));

@@ -46,6 +46,7 @@ struct SkinnyArgs {
     const bf16* x_shadow;                     // optional bf16 copy of an fp32 x, kept current by its writers
     bf16* out_shadow;                         // optional bf16 copy of `out` to maintain (RESIDUAL / BIAS)
     int M, N, K;
+    int groups;                               // independent row groups of M rows each, laid end to end (grid.z); 0 or 1 = one
     int kblocks;                              // 64-wide k-blocks per CTA (K / 64 / splits)
     int splits;                               // cluster size along K
     int need_factor;                          // compute rsqrt(mean(x^2)+1e-6) per token
@@ -122,9 +123,10 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + off_bar + (MAX_KB + 2) * 8 + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    FVLA_DBG_CTA(p, blockIdx.y * gridDim.x + blockIdx.x);
+    FVLA_DBG_CTA(p, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x);
     FVLA_STAMP(0);
     const uint32_t rank = cluster_ctarank();                 // position along K within the cluster
+    const int row0 = blockIdx.z * p.M;                       // first row of this CTA's row group in x / out
     const int tile = blockIdx.x;
     const int k0 = (int)rank * KB * 64;
     const int owners = (p.M + TS - 1) / TS;                  // ranks that own at least one real token
@@ -169,7 +171,7 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (x_by_tma && lane == 0 && warp < KB)
-        tma_load_2d(sX + warp * 8192, &tmX, bars + warp * 8, k0 + warp * 64, 0);
+        tma_load_2d(sX + warp * 8192, &tmX, bars + warp * 8, k0 + warp * 64, row0);
     // Tell the cluster this CTA is running (barriers initialised); peers wait for that before
     // sending anything into its shared memory.
     // (the fence after the barrier initialisation already published it cluster-wide, so a relaxed
@@ -198,9 +200,9 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
                 }
             } else if (EPI == EPI_RESIDUAL) {
                 if (p.out_f32) {
-                    pre[j] = *reinterpret_cast<const uint4*>(static_cast<const float*>(p.out) + (size_t)token * p.ldo + n);
+                    pre[j] = *reinterpret_cast<const uint4*>(static_cast<const float*>(p.out) + (size_t)(row0 + token) * p.ldo + n);
                 } else {
-                    const uint2 r = *reinterpret_cast<const uint2*>(static_cast<const bf16*>(p.out) + (size_t)token * p.ldo + n);
+                    const uint2 r = *reinterpret_cast<const uint2*>(static_cast<const bf16*>(p.out) + (size_t)(row0 + token) * p.ldo + n);
                     const float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y);
                     pre[j] = make_uint4(__float_as_uint(r0.x), __float_as_uint(r0.y), __float_as_uint(r1.x), __float_as_uint(r1.y));
                 }
@@ -227,7 +229,7 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
                 ra[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                 rb[u] = ra[u];
                 if (idx < total && t < p.M) {
-                    const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + (size_t)t * p.ldx + k0 + c * 8);
+                    const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + (size_t)(row0 + t) * p.ldx + k0 + c * 8);
                     ra[u] = src[0];
                     rb[u] = src[1];
                 }
@@ -373,7 +375,7 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
                     up.x += v.x; up.y += v.y; up.z += v.z; up.w += v.w;
                 }
                 const float f2 = factor;
-                *reinterpret_cast<uint2*>(static_cast<bf16*>(p.out) + (size_t)token * p.ldo + tile * 64 + c4) =
+                *reinterpret_cast<uint2*>(static_cast<bf16*>(p.out) + (size_t)(row0 + token) * p.ldo + tile * 64 + c4) =
                     make_uint2(pack_bf16x2(gelu_f(sum.x * f2) * (up.x * f2), gelu_f(sum.y * f2) * (up.y * f2)),
                                pack_bf16x2(gelu_f(sum.z * f2) * (up.z * f2), gelu_f(sum.w * f2) * (up.w * f2)));
             } else {
@@ -383,12 +385,12 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
                 v2 += __uint_as_float(pre[j].z); v3 += __uint_as_float(pre[j].w);
                 if (EPI == EPI_BIAS && p.act == 2) { v0 = silu_f(v0); v1 = silu_f(v1); v2 = silu_f(v2); v3 = silu_f(v3); }
                 if (p.out_shadow)
-                    *reinterpret_cast<uint2*>(p.out_shadow + (size_t)token * p.ldo + n) =
+                    *reinterpret_cast<uint2*>(p.out_shadow + (size_t)(row0 + token) * p.ldo + n) =
                         make_uint2(pack_bf16x2(v0, v1), pack_bf16x2(v2, v3));
                 if (p.out_f32)
-                    *reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)token * p.ldo + n) = make_float4(v0, v1, v2, v3);
+                    *reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)(row0 + token) * p.ldo + n) = make_float4(v0, v1, v2, v3);
                 else
-                    *reinterpret_cast<uint2*>(static_cast<bf16*>(p.out) + (size_t)token * p.ldo + n) =
+                    *reinterpret_cast<uint2*>(static_cast<bf16*>(p.out) + (size_t)(row0 + token) * p.ldo + n) =
                         make_uint2(pack_bf16x2(v0, v1), pack_bf16x2(v2, v3));
             }
         }
@@ -411,7 +413,7 @@ skinny_gemm_kernel(const SkinnyArgs p, const __grid_constant__ CUtensorMap tmW, 
 // ---- host side ---------------------------------------------------------------------------------
 struct SkinnyPlan { int splits, kblocks, tiles; size_t smem; bool ok; };
 
-inline SkinnyPlan plan_skinny(int M, int N, int K, bool geglu) {
+inline SkinnyPlan plan_skinny(int M, int N, int K, bool geglu, int groups = 1) {
     SkinnyPlan pl{};
     pl.ok = false;
     const int tile_n = geglu ? 64 : TN;
@@ -440,6 +442,17 @@ inline SkinnyPlan plan_skinny(int M, int N, int K, bool geglu) {
         best = s;
     }
     if (!best) return pl;
+    if (groups > 1) {
+        // Several row groups in one launch multiply the CTA count. Clusters are placed GPC by GPC: about 33
+        // clusters of 4 or 15 of 8 are resident at once, so prefer the largest split whose clusters of all
+        // groups are resident together (one wave) over the single-group choice.
+        for (int s = best; s >= 1; s /= 2) {
+            const int kb = kb_total / s;
+            if (kb_total % s || kb > MAX_KB) break;
+            const int resident = s >= 8 ? 15 * 8 : (s == 4 ? 33 * 4 : 148);
+            if (pl.tiles * s * groups <= resident) { best = s; break; }
+        }
+    }
     pl.splits = best;
     pl.kblocks = kb_total / best;
     pl.smem = 1024 + (size_t)(pl.kblocks < 2 ? 2 : pl.kblocks) * 16384 + 1024 + (size_t)pl.kblocks * 8192 + 32768 + 256 + 512 +
@@ -450,9 +463,14 @@ inline SkinnyPlan plan_skinny(int M, int N, int K, bool geglu) {
 
 template <int EPI>
 inline int launch_skinny(SkinnyArgs a, const void* W, const void* W2, int ldw, cudaStream_t st) {
-    SkinnyPlan pl = plan_skinny(a.M, a.N, a.K, EPI == EPI_GEGLU);
+    SkinnyPlan pl = plan_skinny(a.M, a.N, a.K, EPI == EPI_GEGLU, a.groups > 1 ? a.groups : 1);
     if (!pl.ok) { set_error("skinny gemm: shape %dx%dx%d not supported", a.M, a.N, a.K); return FVLA_ERR_UNSUPPORTED; }
     a.splits = pl.splits; a.kblocks = pl.kblocks;
+    const int groups = a.groups > 1 ? a.groups : 1;
+    if (groups > 1 && (EPI == EPI_QKV_ROPE || a.need_factor || (a.x_f32 && a.x_shadow == nullptr))) {
+        set_error("skinny gemm: row groups are only built for the bias / residual forms with a bf16 operand");
+        return FVLA_ERR_UNSUPPORTED;
+    }
     auto kern = skinny_gemm_kernel<EPI>;
     static PerDeviceFlag configured;
     if (!configured.get()) {
@@ -467,10 +485,10 @@ inline int launch_skinny(SkinnyArgs a, const void* W, const void* W2, int ldw, c
     rc = tc5::make_map(&tmW2, W2 ? W2 : W, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)ldw, 64, 64);
     if (rc) return rc;
     if (a.x_f32 && a.x_shadow == nullptr) tmX = tmW;         // unused by the kernel in this case
-    else rc = tc5::make_map(&tmX, a.x_f32 ? (const void*)a.x_shadow : a.x, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.ldx, 64, 64);
+    else rc = tc5::make_map(&tmX, a.x_f32 ? (const void*)a.x_shadow : a.x, (uint64_t)a.K, (uint64_t)a.M * groups, (uint64_t)a.ldx, 64, 64);
     if (rc) return rc;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(pl.tiles, pl.splits, 1);
+    cfg.gridDim = dim3(pl.tiles, pl.splits, groups);
     cfg.blockDim = dim3(THREADS, 1, 1);
     cfg.dynamicSmemBytes = pl.smem;
     cfg.stream = st;

@@ -24,7 +24,7 @@ SIGNATURES: dict[str, list] = {
     "fvla_encoder_projector": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fvla_encoder_norm_qkv_rope": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "fvla_encoder_attention": [_P, _P, _P, _P, _I, _I, _I, _F, _P, _Z, _P],
-    "fvla_linear_residual": [_P, _P, _P, _I, _P, _I, _I, _I, _P, _Z, _P],
+    "fvla_linear_residual": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _Z, _P],
     "fvla_encoder_norm_gated_ffn": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fvla_decoder_small_proj": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _Z, _P],
     "fvla_decoder_norm_qkv_rope": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _Z, _P],

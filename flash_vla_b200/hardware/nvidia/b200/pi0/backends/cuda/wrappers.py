@@ -281,12 +281,21 @@ def encoder_attention(Q, K, V, scale, out):
 
 
 def _linear_residual(role, x, weight, out):
+    """out += x @ weight. Extension for batches of episodes: 3-D `x` (episodes, rows, K) and `out` (episodes,
+    rows, N), contiguous, mean that many independent row groups; with at most 64 rows per group the
+    decoder's weight-streaming kernel serves every group inside one launch."""
+    group_rows = 0
+    if x.ndim == 3:
+        if out.ndim != 3 or out.shape[:2] != x.shape[:2]:
+            raise ValueError("linear_residual: batched x and out must agree in their leading dimensions")
+        group_rows = x.shape[1]
+        x, out = x.reshape(-1, x.shape[2]), out.reshape(-1, out.shape[2])
     M, K = x.shape
     N = weight.shape[1]
     lib = _lib.load()
     ws, nb = _ws(role, lib.fvla_gemm_workspace_bytes(M, N, K, 0), x.device)
     _lib.call("fvla_linear_residual", _chk("x", x), _chk("weight", weight, (K, N)),
-              _chk("out", out, (M, N), dtype=None), _is_f32("out", out), _shadow_of(out), M, N, K, ws, nb,
+              _chk("out", out, (M, N), dtype=None), _is_f32("out", out), _shadow_of(out), M, N, K, group_rows, ws, nb,
               _stream())
     return out
 

@@ -166,9 +166,11 @@ def decoder_step_batched(ops, weights, prefix, dec, encoder_seq_len, step, episo
         ops.decoder_norm_qkv_rope(x, w["decoder_attn_qkv_w"][layer], dec["decoder_rope_weights"], q,
                                   k_all[:, S:], v_all[:, S:], nf)
         ops.decoder_attention(q, k_all, v_all, None, q, S)
-        ops.decoder_out_proj_residual(q.view(-1, DECODER_HEADS * HEAD_DIM), w["decoder_attn_o_w"][layer], x)
+        # the two residual projections see the rows as E groups of D (3-D operands): with D <= 64 the backend
+        # runs its weight-streaming decoder kernel once per episode inside one launch
+        ops.decoder_out_proj_residual(q.view(E, D, DECODER_HEADS * HEAD_DIM), w["decoder_attn_o_w"][layer], x3)
         ops.decoder_norm_gated_ffn(x, w["decoder_ffn_gate_w"][layer], w["decoder_ffn_up_w"][layer], dec["decoder_hidden"], nf)
-        ops.decoder_ffn_down_residual(dec["decoder_hidden"], w["decoder_ffn_down_w"][layer], x)
+        ops.decoder_ffn_down_residual(dec["decoder_hidden"].view(E, D, -1), w["decoder_ffn_down_w"][layer], x3)
     dec["decoder_x_rows"].view(E, D - 1, x.shape[1]).copy_(x3[:, 1:])
     ops.decoder_action_out_proj(dec["decoder_x_rows"], w["decoder_action_fused_out_proj_w"],
                                 w["decoder_action_fused_out_proj_b"], dec["diffusion_noise_f32"], nf)

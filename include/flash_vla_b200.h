@@ -136,9 +136,11 @@ int fvla_encoder_attention(const void* Q, const void* K, const void* V, void* ou
 /* wrappers.py:366-371, :383-392 (encoder) and :176-189 (decoder): out += x(M,K) @ W(K,N). out is
  * bf16, or an fp32 residual stream when out_is_f32 != 0. out_shadow (may be NULL; fp32 out only) is a
  * bf16 tensor of out's shape that receives the rounded new value, for a later GEMM to read: written by
- * the GEMM's own epilogue for M <= 64, by a small conversion kernel after it otherwise. */
+ * the GEMM's own epilogue for M <= 64, by a small conversion kernel after it otherwise.
+ * group_rows > 0 (an extension for batches of episodes): the M rows are M / group_rows groups of at most
+ * 64 rows; the decoder's weight-streaming kernel then runs once per group inside one launch. 0: one group. */
 int fvla_linear_residual(const void* x, const void* weight, void* out, int out_is_f32, void* out_shadow,
-                         int M, int N, int K, void* ws, size_t ws_bytes, void* stream);
+                         int M, int N, int K, int group_rows, void* ws, size_t ws_bytes, void* stream);
 /* wrappers.py:374-380: x_norm = rms(x); out = gelu(x_norm @ Wg) * (x_norm @ Wu). */
 int fvla_encoder_norm_gated_ffn(const void* x, const void* gate_w, const void* up_w, void* out,
                                 void* x_norm, int M, int N, int K, void* stream);
