@@ -446,6 +446,21 @@ int fvla_linear_residual(const void* x, const void* weight, void* out, int out_i
         sa.x = x; sa.x_f32 = 0; sa.ldx = K; sa.M = rows; sa.N = N; sa.K = K; sa.groups = groups;
         sa.out = out; sa.out_f32 = out_is_f32; sa.ldo = N; sa.out_shadow = Bm(out_shadow);
         sa.status = device_status_ptr(); FVLA_DBG_ATTACH(sa);
+        // With several row groups a long K (the down projection: 64 k-blocks, 8-way split, 256 CTAs for four
+        // groups, three waves of clusters) is better taken as two launches over half of K each: each half
+        // splits 4 ways and all its clusters are resident at once. The second launch accumulates onto the first.
+        const skinny::SkinnyPlan whole = skinny::plan_skinny(rows, N, K, false, groups);
+        if (groups > 1 && whole.splits == 8 && whole.tiles * whole.splits * groups > 15 * 8 && (K / 2) % 64 == 0 &&
+            skinny::plan_skinny(rows, N, K / 2, false, groups).ok) {
+            const skinny::SkinnyPlan half = skinny::plan_skinny(rows, N, K / 2, false, groups);
+            if (half.tiles * half.splits * groups <= (half.splits >= 8 ? 15 * 8 : 33 * 4)) {
+                sa.K = K / 2;
+                int rc = skinny::launch_skinny<skinny::EPI_RESIDUAL>(sa, weight, nullptr, N, S(stream));
+                if (rc) return rc;
+                sa.x = B(x) + K / 2;
+                return skinny::launch_skinny<skinny::EPI_RESIDUAL>(sa, B(weight) + (size_t)(K / 2) * N, nullptr, N, S(stream));
+            }
+        }
         return skinny::launch_skinny<skinny::EPI_RESIDUAL>(sa, weight, nullptr, N, S(stream));
     }
     FVLA_REQUIRE(out_shadow == nullptr || out_is_f32, "linear_residual: a bf16 shadow only makes sense for an fp32 `out`");

@@ -179,7 +179,8 @@ class Pi0Inference:
         with wrappers.use_pool(self.prefix_pool):
             pipeline.vision_encoder(self.ops, self.weights, p, self.num_views)
             pipeline.transformer_encoder_batched(self.ops, self.weights, p, S, self.num_views, E,
-                                                 after_qkv=lambda layer: kv_ready[layer].record(main))
+                                                 after_qkv=lambda layer: kv_ready[layer].record(main),
+                                                 per_episode=self._attention_fork())
         with torch.cuda.stream(side), wrappers.use_pool(self.decoder_pool):
             if self.steps == 0:
                 side.wait_event(kv_ready[-1])
@@ -188,6 +189,35 @@ class Pi0Inference:
                 pipeline.decoder_step_batched(self.ops, self.weights, p, d, S, step, E, self.layers, before_layer=gate)
             pipeline.decoder_epilogue_batched(d)
         main.wait_stream(side)
+
+    def _attention_fork(self):
+        """`per_episode` hook of the batched prefix encoder: episode e's attention goes to a stream of its own,
+        forked from the current stream; the call with None joins them all back."""
+        import contextlib
+        import os
+        if "mma" in (os.environ.get("FVLA_ATTN"), os.environ.get("FVLA_GEMM")):
+            return None      # the warp-level fallback shares one split-K scratch between the episodes: keep it serial
+        main = torch.cuda.current_stream()
+        if not hasattr(self, "_attn_streams"):
+            self._attn_streams = [torch.cuda.Stream(device=main.device) for _ in range(self.episodes)]
+        used = []
+
+        @contextlib.contextmanager
+        def on_stream(e):
+            stream = self._attn_streams[e]
+            stream.wait_stream(main)
+            used.append(stream)
+            with torch.cuda.stream(stream):
+                yield
+
+        def hook(e):
+            if e is None:
+                for stream in used:
+                    main.wait_stream(stream)
+                used.clear()
+                return None
+            return on_stream(e)
+        return hook
 
     def _write_prompt_rows(self):
         E, S, p = self.episodes, self.encoder_seq_len, self.prefix_buffers
@@ -217,7 +247,8 @@ class Pi0Inference:
         with wrappers.use_pool(self.prefix_pool):
             pipeline.vision_encoder(self.ops, self.weights, p, self.num_views)
             pipeline.transformer_encoder_batched(self.ops, self.weights, p, S, self.num_views, E,
-                                                 after_qkv=lambda layer: kv_ready[layer].record(main))
+                                                 after_qkv=lambda layer: kv_ready[layer].record(main),
+                                                 per_episode=self._attention_fork())
         for e, stream in enumerate(self.streams):
             b = self.episode_buffers[e]
             with torch.cuda.stream(stream), wrappers.use_pool(self.pools[e]):

@@ -66,12 +66,16 @@ def transformer_encoder(ops, weights, buffers, encoder_seq_len, after_qkv=None):
         ops.encoder_ffn_down_residual(b["encoder_hidden"], w["encoder_ffn_down_w"][layer], x)
 
 
-def transformer_encoder_batched(ops, weights, buffers, encoder_seq_len, num_views, episodes, after_qkv=None):
+def transformer_encoder_batched(ops, weights, buffers, encoder_seq_len, num_views, episodes, after_qkv=None,
+                                per_episode=None):
     """The prefix encoder over `episodes` sequences of `encoder_seq_len` tokens laid end to end in the batched
     buffers (`allocate_batched_buffers`): every projection runs once over all rows, so its weights are
     streamed once for the whole batch; attention, which mixes tokens, runs per episode. K / V of layer L go
     straight into rows [0, S) of every episode's cache. Same ops and call order per layer as
-    `transformer_encoder`."""
+    `transformer_encoder`. `per_episode(e)`, if given, returns a context manager under which episode e's
+    attention is enqueued (the engine uses it to put the episodes' attention launches, 48 CTAs each, side by
+    side on streams of their own) and `per_episode(None)` is called once after the last episode to join."""
+    import contextlib
     w, b, S, E = weights, buffers, encoder_seq_len, episodes
     x = b["encoder_x"]
     for e in range(E):
@@ -89,8 +93,11 @@ def transformer_encoder_batched(ops, weights, buffers, encoder_seq_len, num_view
             return
         for e in range(E):
             rows = slice(e * S, (e + 1) * S)
-            ops.encoder_attention(b["encoder_Q"][e * S * DECODER_HEADS:(e + 1) * S * DECODER_HEADS], k_prefix[e], v_prefix[e],
-                                  HEAD_DIM ** -0.5, b["encoder_attn"][rows])
+            with (per_episode(e) if per_episode is not None else contextlib.nullcontext()):
+                ops.encoder_attention(b["encoder_Q"][e * S * DECODER_HEADS:(e + 1) * S * DECODER_HEADS], k_prefix[e], v_prefix[e],
+                                      HEAD_DIM ** -0.5, b["encoder_attn"][rows])
+        if per_episode is not None:
+            per_episode(None)
         ops.encoder_out_proj_residual(b["encoder_attn"], w["encoder_attn_o_w"][layer], x)
         ops.encoder_norm_gated_ffn(x, w["encoder_ffn_gate_w"][layer], w["encoder_ffn_up_w"][layer],
                                    b["encoder_hidden"], b["encoder_x_norm"])
