@@ -412,8 +412,7 @@ inline int launch_pair(const GemmArgs& g, int splits, void* ws, int* status, cud
     }
     a.status = status;
     const int items = a.tiles_m * a.tiles_n * splits;
-    const int max_pairs = num_sms() / 2;
-    const int pairs = items < max_pairs ? items : max_pairs;
+    const int pairs = balanced_grid(items, num_sms() / 2);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     cfg.blockDim = dim3(320, 1, 1);
