@@ -195,6 +195,32 @@ static int launch_gemm(const GemmArgs& a, void* ws, size_t ws_bytes, cudaStream_
     return launch_gemm_mma(a, ws, ws_bytes, st);
 }
 
+// RMS norm + QKV projection + RoPE + scatter of the prefix encoder. fuse_norm: let the GEMM take the raw rows and
+// apply the norm to its accumulators when the shape allows (x_norm is then left alone); otherwise x_norm receives
+// the normalised rows from a kernel of its own.
+static int encoder_qkv_rope(const void* x, const void* weight_qkv, const void* rope, void* Q, void* K, void* V, void* x_norm,
+                            int M, int Kdim, int heads, int head_dim, int group_rows, int kv_group_pitch, int fuse_norm,
+                            void* stream) {
+    GemmArgs a;
+    a.lda = Kdim; a.B = B(weight_qkv); a.ldb = (heads + 2) * head_dim;
+    a.M = M; a.N = (heads + 2) * head_dim; a.K = Kdim;
+    a.rope = B(rope); a.q = Bm(Q); a.k = Bm(K); a.v = Bm(V); a.heads = heads; a.head_dim = head_dim;
+    a.round_first = 1;
+    a.group_rows = group_rows; a.kv_group_pitch = kv_group_pitch;
+    a.trigger_early = 1;      // the next kernel (prefix attention / down projection) runs one CTA per SM
+    if (fuse_norm && tc5_enabled()) {
+        a.A = B(x); a.norm_mode = 1;
+        const int rc = tc5::launch_gemm_tc5_normed(a, device_status_ptr(), S(stream));
+        if (rc != FVLA_ERR_UNSUPPORTED) return rc;
+        a.norm_mode = 0;
+    }
+    if (x_norm == nullptr) { set_error("encoder QKV: M=%d needs the x_norm scratch", M); return FVLA_ERR_ARG; }
+    int rc = rownorm(x, 0, nullptr, nullptr, x_norm, nullptr, nullptr, M, Kdim, 1, S(stream));
+    if (rc) return rc;
+    a.A = B(x_norm);
+    return launch_gemm(a, nullptr, 0, S(stream));
+}
+
 }  // namespace fvla
 
 using namespace fvla;
@@ -202,7 +228,7 @@ using namespace fvla;
 extern "C" {
 
 const char* fvla_last_error(void) { return g_error; }
-int fvla_abi_version(void) { return 3; }
+int fvla_abi_version(void) { return 4; }
 unsigned long long fvla_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int fvla_device_status(void* stream) {
@@ -331,6 +357,32 @@ int fvla_vision_norm_ffn_up(const void* x, const void* norm_w, const void* norm_
     return norm_linear(x, norm_w, norm_b, weight, bias, out, x_norm, M, N, K, 1, stream, 1);      // the down GEMM follows
 }
 
+int fvla_fold_layernorm(const void* norm_w, const void* norm_b, const void* weight, const void* bias, void* weight_folded,
+                        float* colsum, float* bias_folded, int N, int K, void* stream) {
+    FVLA_REQUIRE(norm_w && norm_b && weight && weight_folded && colsum && bias_folded && N > 0 && K > 0, "fold_layernorm: bad arguments");
+    fold_layernorm_kernel<<<(N + 127) / 128, 128, 0, S(stream)>>>(B(norm_w), B(norm_b), B(weight), B(bias), Bm(weight_folded), colsum,
+                                                                 bias_folded, N, K);
+    return check_launch("fold_layernorm_kernel");
+}
+
+int fvla_fused_norm_supported(int M, int N, int K, int rope) {
+    return tc5_enabled() && tc5::normed_tile_width(M, N, K, rope != 0) != 0 ? 1 : 0;
+}
+
+int fvla_vision_folded_norm_linear(const void* x, const void* weight_folded, const float* colsum, const float* bias_folded,
+                                   void* out, int M, int N, int K, int act, void* stream) {
+    FVLA_REQUIRE(x && weight_folded && colsum && bias_folded && out && M > 0 && N > 0 && K > 0 && (act == 0 || act == 1),
+                 "vision_folded_norm_linear: bad arguments");
+    GemmArgs a;
+    a.A = B(x); a.lda = K; a.B = B(weight_folded); a.ldb = N; a.C = out; a.ldc = N;
+    a.act = act; a.M = M; a.N = N; a.K = K; a.trigger_early = act;      // after the up projection the down GEMM follows
+    a.norm_mode = 2; a.colsum = colsum; a.bias_f32 = bias_folded;
+    const int rc = tc5_enabled() ? tc5::launch_gemm_tc5_normed(a, device_status_ptr(), S(stream)) : FVLA_ERR_UNSUPPORTED;
+    if (rc == FVLA_ERR_UNSUPPORTED)
+        set_error("vision_folded_norm_linear: M=%d N=%d K=%d is outside the fused form (see fvla_fused_norm_supported)", M, N, K);
+    return rc;
+}
+
 int fvla_encoder_projector(const void* x, const void* norm_w, const void* norm_b, const void* proj_w,
                            const void* proj_b, void* out, void* x_norm, int M, int N, int K, void* stream) {
     return norm_linear(x, norm_w, norm_b, proj_w, proj_b, out, x_norm, M, N, K, 0, stream, 0);
@@ -373,16 +425,16 @@ int fvla_encoder_norm_qkv_rope(const void* x, const void* weight_qkv, const void
     FVLA_REQUIRE(M > 64, "encoder_norm_qkv_rope: M=%d must exceed 64 (no split-K scratch is taken)", M);
     FVLA_REQUIRE(group_rows >= 0 && (group_rows == 0 || (M % group_rows == 0 && kv_group_pitch >= group_rows)),
                  "encoder_norm_qkv_rope: M=%d is not a whole number of sequences of %d rows (K/V pitch %d rows)", M, group_rows, kv_group_pitch);
-    int rc = rownorm(x, 0, nullptr, nullptr, x_norm, nullptr, nullptr, M, Kdim, 1, S(stream));
-    if (rc) return rc;
-    GemmArgs a;
-    a.A = B(x_norm); a.lda = Kdim; a.B = B(weight_qkv); a.ldb = (heads + 2) * head_dim;
-    a.M = M; a.N = (heads + 2) * head_dim; a.K = Kdim;
-    a.rope = B(rope); a.q = Bm(Q); a.k = Bm(K); a.v = Bm(V); a.heads = heads; a.head_dim = head_dim;
-    a.round_first = 1;
-    a.group_rows = group_rows; a.kv_group_pitch = kv_group_pitch;
-    a.trigger_early = 1;      // the next kernel (prefix attention / down projection) runs one CTA per SM
-    return launch_gemm(a, nullptr, 0, S(stream));
+    return encoder_qkv_rope(x, weight_qkv, rope, Q, K, V, x_norm, M, Kdim, heads, head_dim, group_rows, kv_group_pitch, 0, stream);
+}
+
+int fvla_encoder_qkv_rope_fused_norm(const void* x, const void* weight_qkv, const void* rope, void* Q, void* K,
+                                     void* V, void* x_norm, int M, int Kdim, int heads, int head_dim, int group_rows,
+                                     int kv_group_pitch, void* stream) {
+    FVLA_REQUIRE(M > 64, "encoder_qkv_rope_fused_norm: M=%d must exceed 64 (no split-K scratch is taken)", M);
+    FVLA_REQUIRE(group_rows >= 0 && (group_rows == 0 || (M % group_rows == 0 && kv_group_pitch >= group_rows)),
+                 "encoder_qkv_rope_fused_norm: M=%d is not a whole number of sequences of %d rows (K/V pitch %d rows)", M, group_rows, kv_group_pitch);
+    return encoder_qkv_rope(x, weight_qkv, rope, Q, K, V, x_norm, M, Kdim, heads, head_dim, group_rows, kv_group_pitch, 1, stream);
 }
 
 size_t fvla_encoder_attention_workspace_bytes(int queries, int keys) {

@@ -38,6 +38,14 @@ struct GemmArgs {
     // only when the next kernel runs one CTA per SM: a kernel with several small CTAs per SM (row
     // norm, SigLIP attention) would be packed onto the few SMs that are idle at that moment.
     int trigger_early = 0;
+    // Row norm of A folded into the GEMM (tcgen05 one-SM kernel only, one tile per CTA): A holds the raw rows, the
+    // epilogue warps add up each row's sum and sum of squares from the operand stages while the MMAs run, and the
+    // accumulator is corrected before bias / activation / RoPE. 1: RMS norm, acc * rstd (eps 1e-6). 2: LayerNorm
+    // whose scale and shift were folded into B, colsum and bias_f32 beforehand: rstd * (acc - mean * colsum[n])
+    // (eps 1e-5). bias_f32, when set, replaces `bias`.
+    int norm_mode = 0;
+    const float* colsum = nullptr;
+    const float* bias_f32 = nullptr;
 };
 
 __device__ __forceinline__ int rope_row(const GemmArgs& p, int row) { return p.group_rows > 0 ? row % p.group_rows : row; }

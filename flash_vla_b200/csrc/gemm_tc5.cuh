@@ -159,7 +159,10 @@ __device__ __forceinline__ void epilogue8(const GemmArgs& p, int row, int col, f
 #pragma unroll
         for (int i = 0; i < 8; ++i) a[i] = gelu_f(a[i]) * u[i];
     }
-    if (p.bias) {
+    if (p.bias_f32) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] += __ldg(p.bias_f32 + col + i);
+    } else if (p.bias) {
         uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
         float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
         a[0] += b0.x; a[1] += b0.y; a[2] += b1.x; a[3] += b1.y; a[4] += b2.x; a[5] += b2.y; a[6] += b3.x; a[7] += b3.y;
@@ -226,8 +229,11 @@ struct Tc5Cfg {
     static constexpr int EPI_WARPS = 8;                         // two warps per TMEM lane quadrant, half the columns each
     static constexpr int EPI_STAGE_BYTES = 32 * 80;             // per warp: 32 rows x (64 B + 16 B pad)
     static constexpr int THREADS = 64 + 32 * EPI_WARPS;
-    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BAR_BYTES + EPI_WARPS * EPI_STAGE_BYTES;
+    static constexpr int NORM_BYTES = 2 * BM * 2 * 4;           // fused row norm: (sum, sum of squares) of each row from each of its two threads
+    static constexpr int COLC_BYTES = 2 * 2 * BN * 4;           // per-column epilogue constants (bias, column sums) as fp32, one set per accumulator stage
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BAR_BYTES + EPI_WARPS * EPI_STAGE_BYTES + NORM_BYTES + COLC_BYTES;
     static_assert(2 * ACC_COLS <= 512, "two accumulator stages must fit in TMEM");
+    static_assert(SMEM_BYTES <= 232448, "shared memory of one CTA");
     static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN");
 };
 
@@ -237,7 +243,10 @@ struct Tc5Cfg {
 // with split > 0 stage their fp32 partial tile in their own (by then idle) pipeline shared memory and push
 // it with one bulk copy into the idle pipeline memory of the split-0 CTA, which adds the partials in
 // split order and runs the epilogue. No global scratch, no semaphore; needs one work item per CTA.
-template <int BN, bool DUAL, int STAGES, bool ROPE = false, bool CLUSTER = false>
+// NORM: the row norm of A is folded in (GemmArgs::norm_mode): the epilogue warps also consume every operand stage,
+// so a stage returns to the producer after the MMAs AND the eight epilogue warps have read it. Meant for one tile
+// per CTA; with more, a tile's statistics wait for the previous tile's epilogue (correct, but the overlap is lost).
+template <int BN, bool DUAL, int STAGES, bool ROPE = false, bool CLUSTER = false, bool NORM = false>
 __global__ void __launch_bounds__(320, 1)
 tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                 const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2) {
@@ -262,7 +271,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
     if (threadIdx.x == 0) FVLA_STAMP_ANY(0);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), NORM ? 1 + Cfg::EPI_WARPS : 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), Cfg::EPI_WARPS); }
         mbar_init(bars + (2 * STAGES + 4) * 8 + 16, 1);          // cluster split-K: "the leader's pipeline memory is free"
         mbar_init(bars + (2 * STAGES + 4) * 8 + 24, 1);          // cluster split-K: "the peers' partial tiles have arrived"
@@ -384,6 +393,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
         const int rope_qd = p.heads * p.head_dim;            // RoPE epilogue: columns [0, qd) are Q, then K, then V
         const int sr = lane >> 2, sp = lane & 3;              // staged access: row sr + 8 i, 16-byte piece sp
         uint32_t tcount = 0;
+        uint32_t nit = 0;                                     // fused row norm: stages consumed so far
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
             const int acc = tcount & 1;
             const uint32_t acc_ph = (tcount >> 1) & 1u;
@@ -391,12 +401,26 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
             const int m0 = (t_idx % args.tiles_m) * BM, n0 = (t_idx / args.tiles_m) * BN + chalf * HALF;
             const int row = m0 + quad * 32 + lane;
             // operands that do not depend on the accumulator, fetched while the MMAs still run
-            float bias_lane[CHUNKS];
+            // Per-column constants of this tile (bias; column sums for the folded LayerNorm) go to shared memory
+            // as fp32, one column per thread; the chunk loop reads them back as broadcast 16-byte loads. Two sets,
+            // alternating with the accumulator stage, so a warp that runs ahead never overwrites values in use.
+            const bool has_bias = p.bias != nullptr || p.bias_f32 != nullptr;
+            float* colc = reinterpret_cast<float*>(smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES + Cfg::EPI_WARPS * Cfg::EPI_STAGE_BYTES + Cfg::NORM_BYTES) + acc * 2 * BN;
+            {
+                const int t = (int)threadIdx.x - 64, col = (t_idx / args.tiles_m) * BN + t;
+                if (t < BN && (has_bias || NORM)) {
+                    float bv = 0.f, cv = 0.f;
+                    if (col < p.N) {
+                        bv = p.bias_f32 ? __ldg(p.bias_f32 + col) : (p.bias ? __bfloat162float(__ldg(p.bias + col)) : 0.f);
+                        if (NORM && p.colsum) cv = __ldg(p.colsum + col);
+                    }
+                    colc[t] = bv;
+                    if (NORM) colc[BN + t] = cv;
+                }
+            }
             uint4 rco[CHUNKS][4];
 #pragma unroll
             for (int c = 0; c < CHUNKS; ++c) {
-                const int col = n0 + c * 32 + lane;
-                bias_lane[c] = (p.bias && col < p.N) ? __bfloat162float(__ldg(p.bias + col)) : 0.f;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     rco[c][i] = make_uint4(0, 0, 0, 0);
@@ -409,6 +433,47 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                         rco[c][i] = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.R) + (size_t)rr * p.ldr + gcol);
                     }
                 }
+            }
+            float nrm_mean = 0.f, nrm_rstd = 1.f;
+            if (NORM) {
+                // This thread adds up half of its row: four of the eight 16-byte pieces of each 128-byte operand
+                // row. Sums do not depend on the order of the pieces, so the 128-byte swizzle needs no undoing;
+                // the piece index rotates with the lane so that a quarter warp touches eight different bank groups.
+                float s1 = 0.f, s2 = 0.f;
+                const int kt_beg = split * args.k_per_split, kt_end = min(args.k_iters, kt_beg + args.k_per_split);
+                bool alive = true;
+                for (int kt = kt_beg; kt < kt_end; ++kt, ++nit) {
+                    const int s = nit % STAGES;
+                    const uint32_t ph = (nit / STAGES) & 1u;
+                    if (!mbar_wait(full_bar(s), ph, abort_flag)) { alive = false; break; }
+                    const uint8_t* arow = smem_gen + s * Cfg::STAGE_BYTES + (quad * 32 + lane) * 128;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(arow + (((lane + 2 * j + chalf) & 7) << 4));
+                        const float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+                        s1 += (f0.x + f0.y) + (f1.x + f1.y) + (f2.x + f2.y) + (f3.x + f3.y);
+                        s2 += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y + f2.x * f2.x + f2.y * f2.y + f3.x * f3.x + f3.y * f3.y;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty_bar(s));      // this warp has read the stage
+                }
+                if (!alive) break;
+                float2* nstat = reinterpret_cast<float2*>(smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES + Cfg::EPI_WARPS * Cfg::EPI_STAGE_BYTES);
+                nstat[chalf * BM + quad * 32 + lane] = make_float2(s1, s2);
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * Cfg::EPI_WARPS) : "memory");
+                const float2 other = nstat[(chalf ^ 1) * BM + quad * 32 + lane];
+                // both threads of a row add the two halves in the same order
+                const float t1 = chalf == 0 ? s1 + other.x : other.x + s1, t2 = chalf == 0 ? s2 + other.y : other.y + s2;
+                const float invk = 1.f / (float)p.K;
+                if (p.norm_mode == 2) {
+                    nrm_mean = t1 * invk;
+                    nrm_rstd = rsqrtf(t2 * invk - nrm_mean * nrm_mean + 1e-5f);
+                } else {
+                    nrm_rstd = rsqrtf(t2 * invk + 1e-6f);
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * Cfg::EPI_WARPS) : "memory");      // the statistics area may be rewritten for the next tile
+            } else if (has_bias) {
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * Cfg::EPI_WARPS) : "memory");      // the column constants are in place
             }
             if (!mbar_wait(accfull_bar(acc), acc_ph, abort_flag)) break;
             if (tile + (int)gridDim.x >= num_tiles) { if (p.trigger_early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }      // last accumulator complete
@@ -542,11 +607,36 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                     }
                     // the activation is chosen once per chunk, outside the element loop: inside it the compiler
                     // evaluates every branch for every element and selects
+                    const float* colc_chunk = colc + chalf * HALF + c * 32;
+                    if (NORM) {
+                        // the norm of this thread's row, applied to the raw product
+                        if (p.norm_mode == 2) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 cs = *reinterpret_cast<const float4*>(colc_chunk + BN + j);
+                                a[j] = nrm_rstd * (a[j] - nrm_mean * cs.x); a[j + 1] = nrm_rstd * (a[j + 1] - nrm_mean * cs.y);
+                                a[j + 2] = nrm_rstd * (a[j + 2] - nrm_mean * cs.z); a[j + 3] = nrm_rstd * (a[j + 3] - nrm_mean * cs.w);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) a[j] *= nrm_rstd;
+                        }
+                    }
                     auto finish = [&](auto act) {
+                        if (DUAL) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) a[j] = gelu_f(a[j]) * u[j];
+                        }
+                        if (has_bias) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 b4 = *reinterpret_cast<const float4*>(colc_chunk + j);
+                                a[j] += b4.x; a[j + 1] += b4.y; a[j + 2] += b4.z; a[j + 3] += b4.w;
+                            }
+                        }
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
-                            float v = (DUAL ? gelu_f(a[j]) * u[j] : a[j]) + __shfl_sync(0xffffffffu, bias_lane[c], j);
-                            v = act(v);
+                            const float v = act(a[j]);
                             a[j] = p.R ? v + res[j] : v;
                         }
                     };
@@ -706,10 +796,10 @@ inline Tc5Plan plan_tc5(int M, int N, int K, bool ws_ok) {
     return best;
 }
 
-template <int BN, bool DUAL, int STAGES, bool ROPE = false, bool CLUSTER = false>
+template <int BN, bool DUAL, int STAGES, bool ROPE = false, bool CLUSTER = false, bool NORM = false>
 inline int launch_tc5_cfg(const GemmArgs& g, int* status, cudaStream_t st, int splits = 1, void* ws = nullptr) {
     using Cfg = Tc5Cfg<BN, DUAL, STAGES>;
-    auto kern = tc5_gemm_kernel<BN, DUAL, STAGES, ROPE, CLUSTER>;
+    auto kern = tc5_gemm_kernel<BN, DUAL, STAGES, ROPE, CLUSTER, NORM>;
     static PerDeviceFlag configured;
     if (!configured.get()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
@@ -829,6 +919,37 @@ inline int launch_gemm_tc5(GemmArgs g, int* status, cudaStream_t st, void* ws = 
         case 256: return launch_tc5_cfg<256, false, 4>(g, status, st, pl.splits, ws);
         case 192: return launch_tc5_cfg<192, false, 5>(g, status, st, pl.splits, ws);
         default: return launch_tc5_cfg<128, false, 6>(g, status, st, pl.splits, ws);
+    }
+}
+
+// GEMM with the row norm of A folded in (GemmArgs::norm_mode != 0): one tile per CTA, no K split, bf16 destination,
+// and either the RoPE + scatter epilogue alone or the plain one. FVLA_ERR_UNSUPPORTED otherwise; the caller then
+// normalises A with a kernel of its own and calls the plain GEMM.
+// Tile width at which the fused-norm GEMM takes an M x N x K problem (0: it does not): every CTA gets one tile.
+inline int normed_tile_width(int M, int N, int K, bool rope) {
+    if (M <= 64 || N % 8 != 0 || K % BK != 0) return 0;
+    const int tiles_m = (M + BM - 1) / BM, sms = num_sms();
+    if (rope) return tiles_m * ((N + 127) / 128) <= sms ? 128 : 0;
+    int bn = plan_tc5(M, N, K, false).bn;      // the widest tile that still gives every CTA exactly one, starting from the plain kernel's plan
+    while (bn < 256 && tiles_m * ((N + bn - 1) / bn) > sms) bn += 64;
+    return tiles_m * ((N + bn - 1) / bn) <= sms ? bn : 0;
+}
+
+inline int launch_gemm_tc5_normed(GemmArgs g, int* status, cudaStream_t st) {
+    if (g.Kb == 0) g.Kb = g.K;
+    if (!tc5_supports(g) || g.B2 != nullptr || g.c_f32 || g.norm_mode < 1 || g.norm_mode > 2 || g.K % BK != 0 ||
+        (g.norm_mode == 2 && g.colsum == nullptr))
+        return FVLA_ERR_UNSUPPORTED;
+    const int bn = normed_tile_width(g.M, g.N, g.K, g.rope != nullptr);
+    if (bn == 0) return FVLA_ERR_UNSUPPORTED;
+    if (g.rope != nullptr) {
+        if (g.R != nullptr || g.bias != nullptr || g.bias_f32 != nullptr || g.act != 0) return FVLA_ERR_UNSUPPORTED;
+        return launch_tc5_cfg<128, false, 6, true, false, true>(g, status, st);
+    }
+    switch (bn) {
+        case 256: return launch_tc5_cfg<256, false, 4, false, false, true>(g, status, st);
+        case 192: return launch_tc5_cfg<192, false, 5, false, false, true>(g, status, st);
+        default: return launch_tc5_cfg<128, false, 6, false, false, true>(g, status, st);
     }
 }
 

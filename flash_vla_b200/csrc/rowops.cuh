@@ -85,6 +85,28 @@ __global__ void __launch_bounds__(128) rownorm_kernel(const XT* __restrict__ x, 
     }
 }
 
+// Folds a LayerNorm's scale g and shift s into the linear layer that follows it, y = LN(x) W + b:
+//   W'[k][n] = bf16(g[k] W[k][n]),  colsum[n] = sum_k W'[k][n],  bias'[n] = sum_k s[k] W[k][n] + b[n]
+// so that y = rstd (x W' - mean colsum) + bias'. colsum is taken over the ROUNDED W', the matrix the GEMM
+// multiplies by, so a constant row still maps to bias' exactly. One thread per output column; a set-up kernel.
+__global__ void __launch_bounds__(128) fold_layernorm_kernel(const bf16* __restrict__ g, const bf16* __restrict__ s,
+                                                             const bf16* __restrict__ W, const bf16* __restrict__ b,
+                                                             bf16* __restrict__ Wf, float* __restrict__ colsum,
+                                                             float* __restrict__ biasf, int N, int K) {
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    float cs = 0.f, bs = 0.f;
+    for (int k = 0; k < K; ++k) {
+        const float wv = __bfloat162float(W[(size_t)k * N + n]);
+        const bf16 f = __float2bfloat16_rn(__bfloat162float(g[k]) * wv);
+        Wf[(size_t)k * N + n] = f;
+        cs += __bfloat162float(f);
+        bs += __bfloat162float(s[k]) * wv;
+    }
+    colsum[n] = cs;
+    biasf[n] = bs + (b != nullptr ? __bfloat162float(b[n]) : 0.f);
+}
+
 // images (views, 224, 224, 3) -> patches (views * 256, ld) with feature order (iy, ix, c); columns
 // [588, ld) are written as zero so the GEMM may read whole 16-byte chunks.
 __global__ void __launch_bounds__(256) patchify_kernel(const bf16* __restrict__ img, bf16* __restrict__ out,

@@ -21,6 +21,9 @@ SIGNATURES: dict[str, list] = {
     "fvla_vision_attention": [_P, _P, _I, _I, _I, _I, _P],
     "fvla_vision_linear_bias_residual": [_P, _P, _P, _P, _P, _I, _I, _I, _P, _Z, _P],
     "fvla_vision_norm_ffn_up": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "fvla_fold_layernorm": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P],
+    "fvla_vision_folded_norm_linear": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "fvla_encoder_qkv_rope_fused_norm": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "fvla_encoder_projector": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fvla_encoder_norm_qkv_rope": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "fvla_encoder_attention": [_P, _P, _P, _P, _I, _I, _I, _F, _P, _Z, _P],
@@ -40,6 +43,7 @@ SIGNATURES: dict[str, list] = {
 QUERIES: dict[str, tuple] = {
     "fvla_last_error": ([], c_char_p),
     "fvla_abi_version": ([], c_int),
+    "fvla_fused_norm_supported": ([_I, _I, _I, _I], c_int),
     "fvla_gemm_plan_count": ([], c_int),
     "fvla_launch_count": ([], ctypes.c_ulonglong),
     "fvla_device_status": ([_P], c_int),

@@ -1,10 +1,16 @@
 """Fused overlays of the CUDA backend, same names and signatures as the reference's
 (`.../backends/tilelang/fused_wrappers.py:45-122`).
 
-In the reference the fused table differs from the unfused one in three decoder ops. Here the
-arithmetic of the two tables is the same kernel; what differs is the reference-visible side
-effect: the fused forms never write `norm_factor` (fused_wrappers.py:45-50, :57-62) and the
-fused attention never writes `scores` (fused_wrappers.py:88-94).
+In the reference the fused table differs from the unfused one in three decoder ops. Here those three
+run the same kernel in both tables; what differs is the reference-visible side effect: the fused forms
+never write `norm_factor` (fused_wrappers.py:45-50, :57-62) and the fused attention never writes
+`scores` (fused_wrappers.py:88-94).
+
+Three prefix ops are fused here beyond the reference's table: the LayerNorm of the two SigLIP
+projections and the RMS norm of the prefix encoder's QKV projection move into the GEMM (row statistics
+taken from the operand stages, correction applied to the accumulators), which removes one kernel per
+call site. Like `norm_factor` above, their scratch output `x_norm` is then not written. The unfused
+table keeps the two-kernel forms, so comparing the two tables compares two implementations.
 """
 from __future__ import annotations
 
@@ -32,4 +38,7 @@ FUSED_WRAPPERS = {
     "decoder_norm_gated_ffn": decoder_norm_gated_ffn,
     "decoder_action_out_proj": decoder_action_out_proj,
     "decoder_attention": decoder_attention,
+    "vision_norm_qkv": _w.vision_norm_qkv_fused,
+    "vision_norm_ffn_up": _w.vision_norm_ffn_up_fused,
+    "encoder_norm_qkv_rope": _w.encoder_norm_qkv_rope_fused,
 }

@@ -188,6 +188,64 @@ def vision_norm_qkv(x, norm_w, norm_b, qkv_w, qkv_b, out, x_norm):
     return _norm_linear("fvla_vision_norm_qkv", x, norm_w, norm_b, qkv_w, qkv_b, out, x_norm)
 
 
+_FOLDED_ATTR = "_fvla_folded_layernorm"
+
+
+def _folded_layernorm(weight, norm_w, norm_b, bias):
+    """(weight_folded, colsum, bias_folded) of `fvla_fold_layernorm` for this LayerNorm + linear pair, made on first
+    use and kept ON the tensor that owns `weight`'s storage (found again through `view._base`, gone with it).
+    The entry also remembers the versions of the four tensors: an in-place update of any of them refolds.
+    None while a CUDA graph is being captured and nothing has been folded yet (folding allocates)."""
+    owner = weight if weight._base is None else weight._base
+    table = getattr(owner, _FOLDED_ATTR, None)
+    if table is None:
+        table = {}
+        setattr(owner, _FOLDED_ATTR, table)
+    key = (weight.data_ptr(), norm_w.data_ptr(), norm_b.data_ptr(), bias.data_ptr())
+    versions = (weight._version, norm_w._version, norm_b._version, bias._version)
+    entry = table.get(key)
+    if entry is not None and entry[0] == versions:
+        return entry[1]
+    if torch.cuda.is_current_stream_capturing():
+        return None
+    K, N = weight.shape
+    folded = (torch.empty_like(weight, memory_format=torch.contiguous_format),
+              torch.empty(N, dtype=torch.float32, device=weight.device),
+              torch.empty(N, dtype=torch.float32, device=weight.device))
+    _lib.call("fvla_fold_layernorm", _chk("norm_w", norm_w, (K,)), _chk("norm_b", norm_b, (K,)), _chk("weight", weight),
+              _chk("bias", bias, (N,)), folded[0].data_ptr(), folded[1].data_ptr(), folded[2].data_ptr(), N, K, _stream())
+    table[key] = (versions, folded)
+    return folded
+
+
+def _folded_norm_linear(entry, act, x, norm_w, norm_b, weight, bias, out, x_norm):
+    """The fused table's LayerNorm + linear: the norm happens inside the GEMM and `x_norm` stays untouched. Shapes
+    outside the fused form (a CTA would own several tiles) and calls that would have to fold weights during
+    graph capture take the two-kernel form of the unfused table."""
+    M = x.shape[0] * VISION_TOKENS
+    K, N = weight.shape
+    folded = _folded_layernorm(weight, norm_w, norm_b, bias) if _lib.load().fvla_fused_norm_supported(M, N, K, 0) else None
+    if folded is None:
+        return _norm_linear(entry, x, norm_w, norm_b, weight, bias, out, x_norm)
+    _lib.call("fvla_vision_folded_norm_linear", _chk("x", x, (x.shape[0], VISION_TOKENS, K)), folded[0].data_ptr(),
+              folded[1].data_ptr(), folded[2].data_ptr(), _chk("out", out), M, N, K, act, _stream())
+    return out
+
+
+def vision_norm_qkv_fused(x, norm_w, norm_b, qkv_w, qkv_b, out, x_norm):
+    """out = LayerNorm(x) @ qkv_w + qkv_b with the norm folded into the GEMM; `x_norm` is not written."""
+    if out.numel() != x.shape[0] * VISION_TOKENS * qkv_w.shape[1]:
+        raise ValueError("vision_norm_qkv: out has the wrong size")
+    return _folded_norm_linear("fvla_vision_norm_qkv", 0, x, norm_w, norm_b, qkv_w, qkv_b, out, x_norm)
+
+
+def vision_norm_ffn_up_fused(x, norm_w, norm_b, weight, bias, out, x_norm):
+    """out = gelu(LayerNorm(x) @ weight + bias) with the norm folded into the GEMM; `x_norm` is not written."""
+    if out.numel() != x.shape[0] * VISION_TOKENS * weight.shape[1]:
+        raise ValueError("vision_norm_ffn_up: out has the wrong size")
+    return _folded_norm_linear("fvla_vision_norm_ffn_up", 1, x, norm_w, norm_b, weight, bias, out, x_norm)
+
+
 def vision_attention(QKV, out):
     """Per-view 16-head attention over the packed QKV buffer (kernels/attention.py:20-26)."""
     views = QKV.shape[0]
@@ -249,7 +307,7 @@ def _kv_destination(name: str, t: torch.Tensor, M: int, hd: int):
     return t.data_ptr(), t.shape[1], t.stride(0) // hd
 
 
-def encoder_norm_qkv_rope(x, weight_qkv, rope, Q, K, V, x_norm):
+def encoder_norm_qkv_rope(x, weight_qkv, rope, Q, K, V, x_norm, _entry="fvla_encoder_norm_qkv_rope"):
     """RMS norm, QKV projection rounded to bf16, RoPE, scatter to Q/K/V (wrappers.py:347-363).
 
     Extension for batches of episodes: when K and V are 3-D views (episodes, S, hd) of the episodes' caches,
@@ -263,9 +321,15 @@ def encoder_norm_qkv_rope(x, weight_qkv, rope, Q, K, V, x_norm):
     if (group, pitch) != (group_v, pitch_v):
         raise ValueError("encoder_norm_qkv_rope: K and V must have the same layout")
     rope_rows = group or M
-    _lib.call("fvla_encoder_norm_qkv_rope", _chk("x", x), _chk("weight_qkv", weight_qkv, (Kdim, (heads + 2) * hd)),
+    _lib.call(_entry, _chk("x", x), _chk("weight_qkv", weight_qkv, (Kdim, (heads + 2) * hd)),
               _chk("rope", rope[:rope_rows], (rope_rows, hd)), _chk("Q", Q, (M * heads, hd)), k_ptr, v_ptr,
               _chk("x_norm", x_norm[:M], (M, Kdim)), M, Kdim, heads, hd, group, pitch, _stream())
+
+
+def encoder_norm_qkv_rope_fused(x, weight_qkv, rope, Q, K, V, x_norm):
+    """The same op with the RMS norm applied to the GEMM's accumulators; `x_norm` is not written (unless the
+    shape gives a CTA several tiles, where the library falls back to the two-kernel form)."""
+    return encoder_norm_qkv_rope(x, weight_qkv, rope, Q, K, V, x_norm, _entry="fvla_encoder_qkv_rope_fused_norm")
 
 
 def encoder_attention(Q, K, V, scale, out):

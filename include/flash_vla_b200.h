@@ -111,6 +111,22 @@ int fvla_vision_linear_bias_residual(const void* x, const void* weight, const vo
 int fvla_vision_norm_ffn_up(const void* x, const void* norm_w, const void* norm_b,
                             const void* weight, const void* bias, void* out, void* x_norm, int M,
                             int N, int K, void* stream);
+/* LayerNorm folded into the linear layer behind it (the fused table's form of wrappers.py:268-276 and :291-298;
+ * no counterpart in the reference). Set-up, once per weight: fvla_fold_layernorm writes
+ *   weight_folded[k][n] = bf16(norm_w[k] * weight[k][n])   (K x N bf16)
+ *   colsum[n]           = sum_k weight_folded[k][n]         (N fp32)
+ *   bias_folded[n]      = sum_k norm_b[k] * weight[k][n] + bias[n]   (N fp32; bias may be NULL)
+ * Per call: out = act(rstd * (x @ weight_folded - mean * colsum) + bias_folded), act 0 none / 1 gelu_tanh, with
+ * each row's mean and rstd (eps 1e-5) taken inside the GEMM from its operand stages; no x_norm exists. The form
+ * needs every CTA to own exactly one output tile: fvla_fused_norm_supported(M, N, K, rope) says whether a shape
+ * qualifies (rope 1: the QKV + RoPE epilogue below); otherwise the call returns FVLA_ERR_UNSUPPORTED and the
+ * caller uses fvla_vision_norm_qkv / fvla_vision_norm_ffn_up. */
+int fvla_fold_layernorm(const void* norm_w, const void* norm_b, const void* weight, const void* bias,
+                        void* weight_folded, float* colsum, float* bias_folded, int N, int K, void* stream);
+int fvla_fused_norm_supported(int M, int N, int K, int rope);
+int fvla_vision_folded_norm_linear(const void* x, const void* weight_folded, const float* colsum,
+                                   const float* bias_folded, void* out, int M, int N, int K, int act,
+                                   void* stream);
 
 /* ---- Prefix encoder (M = S tokens, width 2048) ------------------------------------------ */
 /* wrappers.py:336-344: x_norm = LayerNorm(x); out = x_norm @ W + b. */
@@ -127,6 +143,14 @@ int fvla_encoder_projector(const void* x, const void* norm_w, const void* norm_b
 int fvla_encoder_norm_qkv_rope(const void* x, const void* weight_qkv, const void* rope, void* Q,
                                void* K, void* V, void* x_norm, int M, int Kdim, int heads,
                                int head_dim, int group_rows, int kv_group_pitch, void* stream);
+/* The same op with the RMS norm folded into the GEMM (the fused table's form; no counterpart in the reference,
+ * whose fused table leaves the prefix encoder alone): the GEMM reads the raw rows of x, adds up each row's sum
+ * of squares from its operand stages while the tensor cores run, and scales the accumulators before rounding
+ * and RoPE. x_norm is NOT written then. Shapes that give a CTA more than one tile (M beyond 768 or so) fall
+ * back to the two-kernel form and do write x_norm, which may only be NULL when that cannot happen. */
+int fvla_encoder_qkv_rope_fused_norm(const void* x, const void* weight_qkv, const void* rope, void* Q,
+                                     void* K, void* V, void* x_norm, int M, int Kdim, int heads,
+                                     int head_dim, int group_rows, int kv_group_pitch, void* stream);
 /* kernels/attention.py:29-34: unmasked multi-query attention, Q flat (tokens*heads, hd). With `ws`
  * (fvla_encoder_attention_workspace_bytes; contents need no initialisation) the keys are split over
  * twice as many CTAs and a second kernel merges the halves; NULL keeps the single-kernel form. */

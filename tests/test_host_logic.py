@@ -48,11 +48,14 @@ def test_op_table_contract():
         "decoder_ffn_down_residual", "decoder_norm_gated_ffn", "decoder_action_out_proj"}
     assert reference_names <= set(cuda.ALL_WRAPPERS)
     assert set(cuda.ALL_WRAPPERS) - reference_names == {"vision_attention", "encoder_attention", "sync_shadow", "embed_prompt", "copy_rows"}
-    assert set(DEFAULT_FUSED_OPS) == {"decoder_norm_gated_ffn", "decoder_action_out_proj", "decoder_attention"}
+    # the reference's three fused decoder ops, plus three prefix ops whose row norm this backend folds into the GEMM
+    reference_fused = {"decoder_norm_gated_ffn", "decoder_action_out_proj", "decoder_attention"}
+    assert set(DEFAULT_FUSED_OPS) == reference_fused | {"vision_norm_qkv", "vision_norm_ffn_up", "encoder_norm_qkv_rope"}
     fused, unfused = op_table(True), op_table(False)
     assert fused.decoder_attention is cuda.FUSED_WRAPPERS["decoder_attention"]
     assert unfused.decoder_attention is cuda.ALL_WRAPPERS["decoder_attention"]
-    assert fused.vision_norm_qkv is unfused.vision_norm_qkv
+    assert fused.vision_norm_qkv is not unfused.vision_norm_qkv
+    assert fused.vision_patch_embed is unfused.vision_patch_embed
     planned = op_table(True, plan={"decoder_attention": "cuda"})
     assert set(vars(planned)) == set(op_names(True))
     with pytest.raises(KeyError):

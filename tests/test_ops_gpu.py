@@ -67,6 +67,42 @@ def test_vision_norm_linear(ops, ref_ops, name, N, act):
     assert_close(out, ref, what=name)
 
 
+@pytest.mark.parametrize("views", [1, 3, 12])
+@pytest.mark.parametrize("name,N,act", [("vision_norm_qkv", 3456, 0), ("vision_norm_ffn_up", 4304, 1)])
+def test_vision_norm_linear_fused_table(ops, ref_ops, name, N, act, views):
+    """The fused table folds the LayerNorm into the GEMM (row statistics inside the kernel, scale and shift folded
+    into the weights once): same result as the oracle's op, `x_norm` left alone. 12 views give a CTA several
+    tiles, where the library centres the rows with a kernel of its own and does write `x_norm`. Rows with a
+    large common offset check the variance taken as E[x^2] - mean^2 in fp32."""
+    g = torch.Generator().manual_seed(2)
+    x = rnd(g, views, 256, 1152)
+    x[0, :32] += 6.0                                      # mean several times the spread
+    nw, nb = rnd(g, 1152, scale=0.5) + 1, rnd(g, 1152, scale=0.1)
+    w, b = rnd(g, 1152, N, scale=0.02), rnd(g, N, scale=0.02)
+    ref, ref_n = torch.zeros(views, 256, N), torch.zeros(views, 256, 1152)
+    getattr(ref_ops[1], name)(*f32(x, nw, nb, w, b), ref, ref_n)
+    out = torch.zeros(views, 256, N, dtype=bf16, device="cuda")
+    xn = torch.full((views, 256, 1152), 5.0, dtype=bf16, device="cuda")
+    args = dev(x, nw, nb, w, b)
+    getattr(ops[1], name)(*args, out, xn)
+    assert_close(out, ref, what=name + " (fused table)")
+    if views <= 3:
+        assert (xn == 5.0).all(), "the fused form must not write x_norm"
+    # a second call reuses the folded operands; an in-place weight update refolds them
+    out2 = torch.zeros_like(out)
+    getattr(ops[1], name)(*args, out2, xn)
+    assert torch.equal(out, out2)
+    args[3].mul_(2.0)
+    getattr(ref_ops[1], name)(*f32(x, nw, nb, w * 2, b), ref, ref_n)
+    getattr(ops[1], name)(*args, out2, xn)
+    assert_close(out2, ref, what=name + " (fused table, updated weight)")
+    # and the two tables agree with each other to rounding
+    args[3].div_(2.0)
+    getattr(ops[0], name)(*args, out2, xn)
+    # (both are bf16 roundings of nearly the same fp32 value: they may land on neighbouring bf16 numbers)
+    assert_close(out, out2.float().cpu(), rtol=2e-2, what=name + " fused vs unfused table")
+
+
 def test_vision_attention(ops, ref_ops):
     g = torch.Generator().manual_seed(3)
     qkv = rnd(g, 3, 256, 3456)
@@ -134,6 +170,20 @@ def test_encoder_norm_qkv_rope(ops, ref_ops, S):
             assert outliers <= 2e-3, f"encoder_norm_qkv_rope.{what} vs {tag}: {outliers:.2e} of the elements outside the default bound"
         assert_close(got, ref, rtol=2e-2, atol_rms=4e-2, what=f"encoder_norm_qkv_rope.{what} vs fp32")
         assert_close(got, fa, rtol=1e-2, atol_rms=3e-2, what=f"encoder_norm_qkv_rope.{what} vs bf16-faithful")
+    # The fused table applies the RMS factor to the GEMM's accumulators instead of normalising the rows first:
+    # same bounds against the oracle, x_norm left alone.
+    Qf, kf, vf = torch.zeros_like(Q), torch.zeros_like(cache_k), torch.zeros_like(cache_v)
+    xnf = torch.full((S, 2048), 5.0, dtype=bf16, device="cuda")
+    ops[1].encoder_norm_qkv_rope(*dev(x, w, rope), Qf, kf[:S], vf[:S], xnf)
+    assert (xnf == 5.0).all(), "the fused form must not write x_norm"
+    assert (kf[S:] == 0).all() and (vf[S:] == 0).all()
+    for got, ref, what in zip((Qf, kf[:S], vf[:S]), refs, "Q K V".split()):
+        o = ref.float()
+        err = (got.float().cpu() - o).abs()
+        outliers = (err > 1e-2 * o.pow(2).mean().sqrt() + 1e-2 * o.abs()).float().mean().item()
+        print(f"\n[S={S}] fused table {what} vs fp32: fraction outside the default bound {outliers:.2e}, max-abs {err.max().item():.4g}")
+        assert outliers <= 2e-3, f"encoder_norm_qkv_rope (fused table).{what}: {outliers:.2e} of the elements outside the default bound"
+        assert_close(got, ref, rtol=2e-2, atol_rms=4e-2, what=f"encoder_norm_qkv_rope (fused table).{what} vs fp32")
     assert (cache_k[S:] == 0).all() and (cache_v[S:] == 0).all()
 
 
