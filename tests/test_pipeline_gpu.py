@@ -148,6 +148,37 @@ def test_full_forward(full_checkpoint, prompt_len):
     torch.cuda.empty_cache()
 
 
+def test_fused_and_unfused_tables_agree(full_checkpoint):
+    """The reference's bisection gate (eval/correctness/pi0/fused_vs_unfused.py:34-60): the same forward through
+    the fused and the unfused op table. Here the two tables differ in how three prefix ops apply their row norm
+    (inside the GEMM against a kernel of its own), so this compares two implementations; both are also held to
+    the oracle's actions."""
+    from flash_vla_b200 import Pi0Inference
+
+    gold = torch.load(GOLDEN / "forward_p0.pt")
+    images, state, noise = bench_inputs()
+    outs, probes = {}, {}
+    for fused in (True, False):
+        engine = Pi0Inference(full_checkpoint, num_views=3, chunk_size=50, fused=fused)
+        outs[fused] = engine.forward(images, state, noise).float().cpu()
+        b = engine.buffers
+        probes[fused] = {k: b[k].float().cpu().clone() for k in ("vision_x", "encoder_x")}
+        # the fused table leaves the row-norm scratch of the prefix ops it fuses untouched
+        touched = b["vision_x_norm"].abs().sum().item() != 0
+        assert touched, "encoder_projector (unfused in both tables) writes vision_x_norm"
+        del engine
+    for name in ("vision_x", "encoder_x"):
+        f, u = probes[True][name], probes[False][name]
+        rel_rms = ((f - u).pow(2).mean().sqrt() / u.pow(2).mean().sqrt()).item()
+        print(f"\n{name}: fused vs unfused table rel-rms {rel_rms:.4g}, cos {cosine(f, u):.6f}")
+        assert rel_rms <= 2e-2 and cosine(f, u) >= 0.9995, name
+    diff = (outs[True] - outs[False]).abs().max().item()
+    print(f"\nactions: fused vs unfused table max-abs {diff:.4g}, cosine {cosine(outs[True], outs[False]):.6f}")
+    assert cosine(outs[True], outs[False]) >= FINAL_COSINE
+    for fused in (True, False):
+        assert cosine(outs[fused], gold["actions"]) >= FINAL_COSINE, fused
+
+
 def test_frozen_pool_refuses_new_scratch(full_checkpoint):
     """After capture a scratch request that warm-up never made raises instead of allocating."""
     from flash_vla_b200.runtime.cuda import ScratchPool
