@@ -458,7 +458,7 @@ SWEEP = {   # name: (M, K, N, gated, residual, layers cycled)
 }
 
 
-def sweep_rows(names, layers_cap: int, reps: int):
+def sweep_rows(names, layers_cap: int, reps: int, fused: bool = True):
     """Isolated kernel timings: bf16 weights ~ N(0, 0.02), activations ~ N(0, 1), fp32 accumulate, distinct
     weight copies cycled inside one CUDA graph so every launch streams its weights cold. Returns
     {name: {ms_per_launch, tflops, gbs, algorithmic_bytes, flops, frac_of_hbm, frac_of_bf16, ...}}."""
@@ -466,7 +466,7 @@ def sweep_rows(names, layers_cap: int, reps: int):
     from flash_vla_b200.hardware.nvidia.b200.pi0.backends.cuda import wrappers
     from flash_vla_b200.hardware.nvidia.b200.pi0.buffers import rope_table
     from flash_vla_b200.runtime.cuda import ScratchPool
-    ops, peaks, bf16 = op_table(True), measured_peaks(), torch.bfloat16
+    ops, peaks, bf16 = op_table(fused), measured_peaks(), torch.bfloat16
     g = torch.Generator(device="cuda").manual_seed(0)
     rows = {}
 
@@ -565,7 +565,7 @@ def run_sweep(args):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py --sweep needs a CUDA device")
     names = [args.sweep_only] if args.sweep_only else list(SWEEP)
-    rows = sweep_rows(names, args.sweep_layers, args.sweep_reps)
+    rows = sweep_rows(names, args.sweep_layers, args.sweep_reps, fused=not args.sweep_unfused)
     print(json.dumps({"metric": "isolated_gemm_roofline", "peaks": measured_peaks(), "kernels": rows,
                       "note": "fractions are of the measured copy bandwidth and measured cuBLAS bf16 burst rate"}))
 
@@ -597,6 +597,8 @@ def main():
     p.add_argument("--sweep-only", choices=list(SWEEP), default=None)
     p.add_argument("--sweep-layers", type=int, default=0, help="cap on distinct weight copies (small profiler runs)")
     p.add_argument("--sweep-reps", type=int, default=20)
+    p.add_argument("--sweep-unfused", action="store_true",
+                   help="sweep the unfused op table (row norm as a kernel of its own in front of the prefix GEMMs)")
     p.add_argument("--profile-pass", action="store_true", help="two eager forwards only (for ncu launch lists)")
     p.add_argument("--autotune", action="store_true",
                    help="sweep the launch plans of every GEMM call site and write the winners to the tuned-plan file")
