@@ -90,7 +90,7 @@ static size_t op_ws_bytes(int M, int N, int K, bool dual) {
         // given (4 splits at any tile width on the one-SM kernel, 6 on the pair kernel), so that a plan
         // pinned later never finds the scratch too small
         size_t t = 0;
-        for (int bn = 128; bn <= 256; bn += 64) { size_t v = tc5::scratch_split_bytes(M, N, bn, 4); if (v > t) t = v; }
+        for (int bn = 64; bn <= 256; bn += 64) { size_t v = tc5::scratch_split_bytes(M, N, bn, 4); if (v > t) t = v; }
         size_t t2 = tc5x2::pair_split_bytes(M, N, 6);
         if (t2 > t) t = t2;
         if (t > gemm) gemm = t;
@@ -724,7 +724,7 @@ int fvla_gemm_plan_set(int M, int N, int K, int kind, int engine, int bn, int sp
     FVLA_REQUIRE(M > 0 && N > 0 && K > 0 && kind >= PLAN_PLAIN && kind <= PLAN_SKINNY_DUAL, "gemm_plan_set: bad shape or kind");
     bool ok = false;
     switch (engine) {
-        case ENGINE_TC5_SCRATCH: ok = (kind == PLAN_PLAIN && (bn == 128 || bn == 192 || bn == 256) && splits >= 1 && splits <= 4) ||
+        case ENGINE_TC5_SCRATCH: ok = (kind == PLAN_PLAIN && (bn == 64 || bn == 128 || bn == 192 || bn == 256) && splits >= 1 && splits <= 4) ||
                                       (kind == PLAN_DUAL && splits == 1); break;
         case ENGINE_TC5_CLUSTER: ok = kind == PLAN_PLAIN && splits >= 2 && splits <= 4; break;
         case ENGINE_PAIR: ok = (kind == PLAN_PLAIN && splits >= 1 && splits <= 6) || (kind == PLAN_DUAL && splits == 1); break;

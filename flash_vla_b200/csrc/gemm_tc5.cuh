@@ -768,9 +768,10 @@ inline int balanced_grid(int items, int max_ctas) {
 
 struct Tc5Plan { int bn, splits; size_t ws_bytes; float est_us; };
 
-// Per-step times (us) of one 64-wide k step at tile width 128 / 192 / 256, as measured on B200: the
-// shared-memory fill through L2 (about 64 B/clk/SM), not the MMA, sets them.
-inline float k_step_us(int bn) { return bn == 128 ? 0.30f : (bn == 192 ? 0.37f : 0.43f); }
+// Per-step times (us) of one 64-wide k step at tile width 64 / 128 / 192 / 256, as measured on B200: the
+// shared-memory traffic of a step (every operand byte written once by TMA and read once by the tensor core, at
+// 128 B/clk), not the MMA, sets them.
+inline float k_step_us(int bn) { return bn == 64 ? 0.26f : (bn == 128 ? 0.30f : (bn == 192 ? 0.37f : 0.43f)); }
 
 // Tile width and K split for a plain (non-gated) GEMM: minimise the estimated time of the slowest SM,
 // (waves of work items) x (k steps per item) x (time per step), plus, for a split, the cost of writing
@@ -779,7 +780,7 @@ inline Tc5Plan plan_tc5(int M, int N, int K, bool ws_ok) {
     const int tiles_m = (M + BM - 1) / BM, sms = num_sms(), k_iters = (K + BK - 1) / BK;
     Tc5Plan best{128, 1, 0, 1e30f};
     float best_t = 1e30f;
-    for (int bn = 128; bn <= 256; bn += 64) {
+    for (int bn = 64; bn <= 256; bn += 64) {
         const int tiles = tiles_m * ((N + bn - 1) / bn);
         for (int s = 1; s <= (ws_ok ? 4 : 1); ++s) {
             if (s > 1 && k_iters / s < 16) break;
@@ -889,7 +890,8 @@ inline int launch_gemm_tc5_pinned(GemmArgs g, const PlanChoice& pc, int* status,
         case 256: return launch_tc5_cfg<256, false, 4>(g, status, st, pc.splits, ws);
         case 192: return launch_tc5_cfg<192, false, 5>(g, status, st, pc.splits, ws);
         case 128: return launch_tc5_cfg<128, false, 6>(g, status, st, pc.splits, ws);
-        default: set_error("pinned plan: tile width %d (128, 192 or 256)", pc.bn); return FVLA_ERR_ARG;
+        case 64: return launch_tc5_cfg<64, false, 8>(g, status, st, pc.splits, ws);
+        default: set_error("pinned plan: tile width %d (64, 128, 192 or 256)", pc.bn); return FVLA_ERR_ARG;
     }
 }
 
@@ -918,6 +920,7 @@ inline int launch_gemm_tc5(GemmArgs g, int* status, cudaStream_t st, void* ws = 
     switch (pl.bn) {
         case 256: return launch_tc5_cfg<256, false, 4>(g, status, st, pl.splits, ws);
         case 192: return launch_tc5_cfg<192, false, 5>(g, status, st, pl.splits, ws);
+        case 64: return launch_tc5_cfg<64, false, 8>(g, status, st, pl.splits, ws);
         default: return launch_tc5_cfg<128, false, 6>(g, status, st, pl.splits, ws);
     }
 }
@@ -931,6 +934,7 @@ inline int normed_tile_width(int M, int N, int K, bool rope) {
     const int tiles_m = (M + BM - 1) / BM, sms = num_sms();
     if (rope) return tiles_m * ((N + 127) / 128) <= sms ? 128 : 0;
     int bn = plan_tc5(M, N, K, false).bn;      // the widest tile that still gives every CTA exactly one, starting from the plain kernel's plan
+    if (bn < 128) bn = 128;                    // the fused-norm variants start at 128 columns
     while (bn < 256 && tiles_m * ((N + bn - 1) / bn) > sms) bn += 64;
     return tiles_m * ((N + bn - 1) / bn) <= sms ? bn : 0;
 }

@@ -107,7 +107,7 @@ SITES = {s.name: s for s in (
 def candidates(site: CallSite) -> list[dict]:
     """Every plan worth timing for a call site (the library rejects the ones a shape cannot take)."""
     if site.kind == "plain":
-        return ([{"engine": "tc5_scratch", **c} for c in grid(bn=[128, 192, 256], splits=[1, 2, 3, 4])] +
+        return ([{"engine": "tc5_scratch", **c} for c in grid(bn=[64, 128, 192, 256], splits=[1, 2, 3, 4])] +
                 [{"engine": "tc5_cluster", "bn": 128, "splits": s} for s in (2, 3, 4)] +
                 [{"engine": "pair", "bn": 256, "splits": s} for s in (1, 2, 3, 4, 6)])
     if site.kind == "dual":

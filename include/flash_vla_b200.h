@@ -59,7 +59,7 @@ int fvla_selftest_wait_timeout(const void* x, const void* weight, void* out, int
  * reference writes into its TileLang kernel definitions. Here a measured-best launch plan can be pinned
  * per GEMM shape at run time; unpinned shapes use the library's cost models. `kind`: 0 plain (bias /
  * activation / residual epilogues), 1 QKV + RoPE, 2 gated FFN, 3 decoder cluster GEMM (M <= 64), 4 its
- * gated form. `engine`: 1 one-SM tcgen05 kernel with tile width bn (128, 192, 256) and K split `splits`
+ * gated form. `engine`: 1 one-SM tcgen05 kernel with tile width bn (64, 128, 192, 256) and K split `splits`
  * (1..4) through caller scratch; 2 the same kernel, 128-wide tiles, K split (2..4) inside a thread-block
  * cluster; 3 the two-SM kernel, K split 1..6 through scratch (gated FFN: 1); 4 the decoder cluster GEMM
  * with `splits` (1, 2, 4, 8) CTAs along K. A launch that cannot honour its pinned plan fails with an
