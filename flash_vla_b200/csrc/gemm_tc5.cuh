@@ -384,7 +384,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
         // instead of 16 bytes in each of 32 rows.
         asm volatile("griddepcontrol.wait;" ::: "memory");
         if (CLUSTER) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-        const int ew = warp - 2, quad = warp & 3, chalf = ew >> 2;
+        const int ew = warp - 2, quad = warp & 3, whalf = ew >> 2;
         constexpr int HALF = BN / 2, CHUNKS = HALF / 32;
         uint8_t* stg = smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES + ew * Cfg::EPI_STAGE_BYTES;
         // staged path: bf16 destination(s); the preloaded operand is the bf16 residual or, for the RoPE +
@@ -398,6 +398,11 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
             const int acc = tcount & 1;
             const uint32_t acc_ph = (tcount >> 1) & 1u;
             const int t_idx = tile / args.splits, split = tile % args.splits;
+            // Two cluster mates that split K between them share the epilogue as well: each finishes the column half
+            // of its own rank (after receiving the other's partial sums for it), and inside that half the warp's
+            // `whalf` picks one of the two 32-column chunks. In every other case `whalf` picks the column half.
+            const bool sym = CLUSTER && CHUNKS == 2 && args.splits == 2;
+            const int chalf = sym ? split : whalf;
             const int m0 = (t_idx % args.tiles_m) * BM, n0 = (t_idx / args.tiles_m) * BN + chalf * HALF;
             const int row = m0 + quad * 32 + lane;
             // operands that do not depend on the accumulator, fetched while the MMAs still run
@@ -424,6 +429,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     rco[c][i] = make_uint4(0, 0, 0, 0);
+                    if (sym && c != whalf) continue;
                     const int grow = m0 + quad * 32 + sr + 8 * i, gcol = n0 + c * 32 + sp * 8;
                     if (ROPE && plain && p.rope) {
                         if (grow < p.M && gcol < rope_qd + p.head_dim)
@@ -449,7 +455,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                     const uint8_t* arow = smem_gen + s * Cfg::STAGE_BYTES + (quad * 32 + lane) * 128;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const uint4 v = *reinterpret_cast<const uint4*>(arow + (((lane + 2 * j + chalf) & 7) << 4));
+                        const uint4 v = *reinterpret_cast<const uint4*>(arow + (((lane + 2 * j + whalf) & 7) << 4));
                         const float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
                         s1 += (f0.x + f0.y) + (f1.x + f1.y) + (f2.x + f2.y) + (f3.x + f3.y);
                         s2 += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y + f2.x * f2.x + f2.y * f2.y + f3.x * f3.x + f3.y * f3.y;
@@ -459,11 +465,11 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                 }
                 if (!alive) break;
                 float2* nstat = reinterpret_cast<float2*>(smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES + Cfg::EPI_WARPS * Cfg::EPI_STAGE_BYTES);
-                nstat[chalf * BM + quad * 32 + lane] = make_float2(s1, s2);
+                nstat[whalf * BM + quad * 32 + lane] = make_float2(s1, s2);
                 asm volatile("bar.sync 1, %0;" ::"n"(32 * Cfg::EPI_WARPS) : "memory");
-                const float2 other = nstat[(chalf ^ 1) * BM + quad * 32 + lane];
+                const float2 other = nstat[(whalf ^ 1) * BM + quad * 32 + lane];
                 // both threads of a row add the two halves in the same order
-                const float t1 = chalf == 0 ? s1 + other.x : other.x + s1, t2 = chalf == 0 ? s2 + other.y : other.y + s2;
+                const float t1 = whalf == 0 ? s1 + other.x : other.x + s1, t2 = whalf == 0 ? s2 + other.y : other.y + s2;
                 const float invk = 1.f / (float)p.K;
                 if (p.norm_mode == 2) {
                     nrm_mean = t1 * invk;
@@ -485,7 +491,40 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
             if (CLUSTER && args.splits > 1) {
                 const uint32_t free_bar = bars + (2 * STAGES + 4) * 8 + 16, red_bar = bars + (2 * STAGES + 4) * 8 + 24;
                 constexpr uint32_t TILE_BYTES = BM * BN * 4;
-                if (split > 0) {
+                if (sym) {
+                    // Reduce-scatter between the two mates. This CTA's pipeline memory is idle (its MMAs are done):
+                    // [0, 32 KB) stages the partial sums of the MATE's column half as [column quad][row][4],
+                    // [32 KB, 64 KB) receives the mate's partial sums of THIS CTA's half in the same layout.
+                    constexpr uint32_t HALF_BYTES = BM * HALF * 4;
+                    if (ew == 0 && lane == 0) {
+                        mbar_expect_tx(red_bar, HALF_BYTES);
+                        uint32_t fb;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(fb) : "r"(free_bar), "r"(split ^ 1));
+                        asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(fb) : "memory");      // "send when ready"
+                    }
+                    {
+                        float a[32];
+                        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * Cfg::ACC_COLS + (split ^ 1) * HALF + whalf * 32, a);
+                        float* dst = reinterpret_cast<float*>(smem_gen) + (whalf * 8) * (BM * 4) + (quad * 32 + lane) * 4;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4*>(dst + (j / 4) * (BM * 4)) = make_float4(a[j], a[j + 1], a[j + 2], a[j + 3]);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // staged half -> visible to the bulk copy
+                    asm volatile("bar.sync 1, %0;" ::"n"(32 * Cfg::EPI_WARPS) : "memory");
+                    if (ew == 0 && lane == 0) {
+                        if (mbar_wait(free_bar, 0, abort_flag)) {      // the mate's pipeline memory is idle
+                            uint32_t dst0, rbar;
+                            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst0) : "r"(smem_base + HALF_BYTES), "r"(split ^ 1));
+                            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(red_bar), "r"(split ^ 1));
+#pragma unroll
+                            for (uint32_t off = 0; off < HALF_BYTES; off += 16384)
+                                asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                             ::"r"(dst0 + off), "r"(smem_base + off), "r"(16384), "r"(rbar) : "memory");
+                        }
+                    }
+                    mbar_wait(red_bar, 0, abort_flag);      // a wait that gives up sets the abort flag; the sums are then garbage and reported
+                } else if (split > 0) {
                     // stage the partial tile as [column quad][row][4] in this CTA's idle pipeline memory, then push it
 #pragma unroll
                     for (int c = 0; c < CHUNKS; ++c) {
@@ -513,7 +552,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                     }
                     continue;
                 }
-                if (ew == 0 && lane == 0) {
+                if (!sym && ew == 0 && lane == 0) {
                     mbar_expect_tx(red_bar, (uint32_t)(args.splits - 1) * TILE_BYTES);
                     for (int sp_i = 1; sp_i < args.splits; ++sp_i) {
                         uint32_t fb;
@@ -521,7 +560,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                         asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(fb) : "memory");
                     }
                 }
-                mbar_wait(red_bar, 0, abort_flag);      // a wait that gives up sets the abort flag; the sums are then garbage and reported
+                if (!sym) mbar_wait(red_bar, 0, abort_flag);      // a wait that gives up sets the abort flag; the sums are then garbage and reported
                 from_cluster = true;
             }
             if (!CLUSTER && !DUAL && args.splits > 1) {
@@ -561,6 +600,7 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
             for (int c = 0; c < CHUNKS; ++c) {
                 float a[32], u[32];
+                if (sym && c != whalf) continue;
                 if (from_partials) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) a[j] = 0.f;
@@ -577,7 +617,15 @@ tc5_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA,
                     tmem_ld32(t_row + c * 32, a);
                     if (DUAL) tmem_ld32(t_row + BN + c * 32, u);
                 }
-                if (CLUSTER && from_cluster) {
+                if (CLUSTER && from_cluster && sym) {
+                    // the mate's partial sums of this chunk (two addends: the order does not matter)
+                    const float* src = reinterpret_cast<const float*>(smem_gen + BM * HALF * 4) + (c * 8) * (BM * 4) + (quad * 32 + lane) * 4;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 v = *reinterpret_cast<const float4*>(src + (j / 4) * (BM * 4));
+                        a[j] += v.x; a[j + 1] += v.y; a[j + 2] += v.z; a[j + 3] += v.w;
+                    }
+                } else if (CLUSTER && from_cluster) {
                     // split 0 is this CTA's own accumulator; the others arrived in split order
                     for (int sp_i = 1; sp_i < args.splits; ++sp_i) {
                         const float* src = reinterpret_cast<const float*>(smem_gen + (size_t)(sp_i - 1) * (BM * BN * 4)) +
@@ -911,7 +959,8 @@ inline int launch_gemm_tc5(GemmArgs g, int* status, cudaStream_t st, void* ws = 
         float best_t = pl.est_us;
         for (int sp = 2; sp <= 4; ++sp) {
             if (tiles * sp > num_sms() || k_iters / sp < 8) break;
-            const float t = ((k_iters + sp - 1) / sp) * k_step_us(128) + 4.0f + 2.5f + (sp - 1) * 2.1f;
+            // two mates reduce-scatter their halves (about 1.5 us); more splits gather one 64 KB tile each into the split-0 CTA
+            const float t = ((k_iters + sp - 1) / sp) * k_step_us(128) + 4.0f + (sp == 2 ? 1.5f : 2.5f + (sp - 1) * 2.1f);
             if (t < best_t) { best_t = t; best_s = sp; }
         }
         if (best_s) return launch_tc5_cfg<128, false, 6, false, true>(g, status, st, best_s, nullptr);
