@@ -217,7 +217,7 @@ tc5x2_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, c
                     for (int i = 0; i < 4; ++i) {
                         rco[DUAL ? 0 : c][i] = make_uint4(0, 0, 0, 0);
                         const int grow = m0 + quad * 32 + sr + 8 * i, gcol = n0 + c * 32 + sp * 8;
-                        if (p.R && !p.c_f32 && grow < p.M && gcol < p.N)
+                        if (p.R && !p.c_f32 && grow < p.M && gcol < p.N && (chalf * CHUNKS + c) % args.splits == split)
                             rco[DUAL ? 0 : c][i] = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(p.R) + (size_t)grow * p.ldr + gcol);
                     }
             }
@@ -227,10 +227,16 @@ tc5x2_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, c
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * 256 + chalf * SPAN;
             bool from_partials = false;
             if (!DUAL && args.splits > 1) {
-                // publish this item's partial rows (layout [item][rank][column quad][row][4], coalesced), then the
-                // last-arriving split of this CTA's half tile sums all of them in split order
+                // K split over `splits` work items of one tile. The 8 chunks (32 columns each) of this CTA's 128 rows
+                // are shared out: chunk g is finished by the item whose split index is g % splits. An item publishes
+                // the partial sums of the chunks it does NOT finish (layout [item][rank][column quad][row][4],
+                // coalesced), announces itself on the tile's arrival counter, waits until all items of the tile
+                // have done so (all of them are resident or will be: items run in index order and publish before
+                // they wait), and then sums its own chunks in split order, taking its own addend from TMEM.
+                int* arrive = args.counters + (t_idx * 2 + rank) * 2;
 #pragma unroll 1
                 for (int c = 0; c < CHUNKS; ++c) {
+                    if ((chalf * CHUNKS + c) % args.splits == split) continue;
                     float a[32];
                     tmem_ld32(t_row + c * 32, a);
                     float* dst = args.partial + ((size_t)((t_idx * args.splits + split) * 2 + rank) * 64 + (chalf * CHUNKS + c) * 8) * 512 +
@@ -239,20 +245,25 @@ tc5x2_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, c
                     for (int j = 0; j < 32; j += 4)
                         __stcg(reinterpret_cast<float4*>(dst + (j / 4) * 512), make_float4(a[j], a[j + 1], a[j + 2], a[j + 3]));
                 }
-                release_acc(acc);
                 __threadfence();
                 asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
                 int* flag = reinterpret_cast<int*>(smem_gen + STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 12);
                 if (ew == 0 && lane == 0) {
-                    const int prev = atomicAdd(args.counters + t_idx * 2 + rank, 1);
-                    const int last = prev == args.splits - 1;
-                    if (last) args.counters[t_idx * 2 + rank] = 0;
-                    *flag = last;
+                    atomicAdd(arrive, 1);
+                    int ok = 0;
+                    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+                        int seen;
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(arrive) : "memory");
+                        if (seen >= args.splits) { ok = 1; break; }
+                        if ((spin & 1023u) == 1023u && *abort_flag) break;
+                    }
+                    if (!ok) *abort_flag = 1;
+                    *flag = ok;
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
-                const int last = *reinterpret_cast<volatile int*>(flag);
-                asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
-                if (!last) continue;
+                const int all_here = *reinterpret_cast<volatile int*>(flag);
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");   // flag may be rewritten by the next item
+                if (!all_here) break;
                 __threadfence();
                 from_partials = true;
             }
@@ -260,9 +271,17 @@ tc5x2_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, c
             for (int c = 0; c < CHUNKS; ++c) {
                 float a[32];
                 if (from_partials) {
+                    if ((chalf * CHUNKS + c) % args.splits != split) continue;      // another item of the tile finishes this chunk
 #pragma unroll
                     for (int j = 0; j < 32; ++j) a[j] = 0.f;
                     for (int sp_i = 0; sp_i < args.splits; ++sp_i) {
+                        if (sp_i == split) {
+                            float own[32];
+                            tmem_ld32(t_row + c * 32, own);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) a[j] += own[j];
+                            continue;
+                        }
                         const float* src = args.partial + ((size_t)((t_idx * args.splits + sp_i) * 2 + rank) * 64 + (chalf * CHUNKS + c) * 8) * 512 +
                                            (quad * 32 + lane) * 4;
 #pragma unroll
@@ -349,7 +368,16 @@ tc5x2_gemm_kernel(const Tc5Args args, const __grid_constant__ CUtensorMap tmA, c
                 }
                 __syncwarp();
             }
-            if (!from_partials) release_acc(acc);
+            release_acc(acc);
+            if (from_partials) {
+                // the last item to leave the tile zeroes both counters for the next launch: by then every item has seen
+                // the full arrival count
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
+                if (ew == 0 && lane == 0) {
+                    int* arrive = args.counters + (t_idx * 2 + rank) * 2;
+                    if (atomicAdd(arrive + 1, 1) == args.splits - 1) { arrive[1] = 0; arrive[0] = 0; __threadfence(); }
+                }
+            }
         }
     }
 
@@ -379,7 +407,7 @@ inline PairPlan plan_pair_plain(int M, int N, int K, bool ws_ok) {
         if (s > 1) t += 3.0f + (float)s * M * N * 8.0f / 4.0e6f;
         if (t < pl.est_us) { pl.est_us = t; pl.splits = s; pl.ok = true; }
     }
-    if (pl.splits > 1) pl.ws_bytes = (((size_t)tiles * 2 * sizeof(int) + 255) / 256) * 256 + (size_t)tiles * pl.splits * 2 * 128 * 256 * sizeof(float);
+    if (pl.splits > 1) pl.ws_bytes = (((size_t)tiles * 4 * sizeof(int) + 255) / 256) * 256 + (size_t)tiles * pl.splits * 2 * 128 * 256 * sizeof(float);
     return pl;
 }
 
@@ -406,7 +434,7 @@ inline int launch_pair(const GemmArgs& g, int splits, void* ws, int* status, cud
     a.k_iters = (g.K + BK - 1) / BK;
     a.splits = splits; a.k_per_split = (a.k_iters + splits - 1) / splits;
     if (splits > 1) {
-        const size_t counters = (((size_t)a.tiles_m * a.tiles_n * 2 * sizeof(int) + 255) / 256) * 256;
+        const size_t counters = (((size_t)a.tiles_m * a.tiles_n * 4 * sizeof(int) + 255) / 256) * 256;
         a.counters = reinterpret_cast<int*>(ws);
         a.partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + counters);
     }
@@ -458,7 +486,7 @@ inline int launch_plain_pair(const GemmArgs& g, void* ws, size_t ws_bytes, int* 
 // Scratch bytes of the pair kernel's K split.
 inline size_t pair_split_bytes(int M, int N, int splits) {
     const size_t tiles = (size_t)((M + 255) / 256) * ((N + 255) / 256);
-    return splits > 1 ? ((tiles * 2 * sizeof(int) + 255) / 256) * 256 + tiles * splits * 2 * 128 * 256 * sizeof(float) : 0;
+    return splits > 1 ? ((tiles * 4 * sizeof(int) + 255) / 256) * 256 + tiles * splits * 2 * 128 * 256 * sizeof(float) : 0;
 }
 
 // A pinned K split (1..6) for the plain form of the pair kernel; errors out when it cannot be honoured.
