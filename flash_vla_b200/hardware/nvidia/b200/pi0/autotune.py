@@ -192,7 +192,9 @@ def sweep(site: CallSite, reps: int = 20, verbose: bool = True, seed: int = 0) -
     from flash_vla_b200.runtime.cuda import ScratchPool
     from .backends.cuda import _lib, wrappers
     lib = _lib.load()
-    ops = op_table(True)
+    # The unfused table: a pinned plan addresses the plain GEMM of an op. (The fused table's three prefix ops that
+    # fold their row norm into the GEMM pick their tile from the shape alone and consult no plan.)
+    ops = op_table(False)
     saved = _pinned_snapshot()
     results, refused, wrong = [], 0, 0
     try:
