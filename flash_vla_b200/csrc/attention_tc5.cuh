@@ -12,6 +12,12 @@
 //     value P is expressed against (rare after the first block), so P V seldom waits for a correction.
 // All operands are used where TMA puts them (128-byte swizzle): Q and K are K-major, V is the
 // MN-major B operand exactly as the weights of the GEMM kernels.
+//
+// When one CTA per query tile would leave most SMs idle, two CTAs (a cluster) share a tile: each walks half of
+// the key blocks, then the two reduce-scatter: a CTA stages the other's half of its unnormalised accumulator
+// (128 of the 256 columns, fp32) in its idle K buffer and pushes it, with its rows' running maximum and sum,
+// into the mate's idle V buffer by bulk copy; each then merges the two partial results for its own 128
+// columns (log-sum-exp) and stores them.
 #pragma once
 
 #include "common.cuh"
@@ -39,6 +45,7 @@ struct Args {
     int nq, nk;
     float scale_log2;
     int* status;
+    int split;          // 1: launched as clusters of two CTAs per query tile, each walking half of the key blocks
 };
 
 // S = Q K^T: both operands K-major.
@@ -112,11 +119,19 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + OFF_BAR + 104);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int q0 = blockIdx.x * BQ;
-    const int nblk = (p.nk + BKEY - 1) / BKEY;
+    const int nblk_all = (p.nk + BKEY - 1) / BKEY;
+    uint32_t rank = 0;
+    if (p.split) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int q0 = (p.split ? blockIdx.x >> 1 : blockIdx.x) * BQ;
+    const int half_blks = (nblk_all + 1) / 2;
+    const int jb0 = p.split ? (int)rank * half_blks : 0;                        // first key block of this CTA
+    const int nblk = p.split ? min(half_blks, nblk_all - jb0) : nblk_all;      // and how many it walks
+    const uint32_t x_ready = bars + 112, x_recv = bars + 120;                   // key split: "mate may send", "mate's half has arrived"
 
     if (tid == 0) {
         for (int i = 0; i < 12; ++i) mbar_init(bars + i * 8, 1);
+        mbar_init(x_ready, 1);
+        mbar_init(x_recv, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -128,6 +143,7 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
     __syncthreads();
     tc5::tc_fence_after();
     const uint32_t tmem = *tmem_slot_ptr;
+    if (p.split) asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");   // the mate's barriers exist
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");       // Q, K and V come from the preceding kernel
 
@@ -144,7 +160,7 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
                 if (!mbar_wait(k_empty, (uint32_t)(j & 1) ^ 1u, abort_flag)) break;
                 mbar_expect_tx(k_full, K_BYTES);
 #pragma unroll
-                for (int a = 0; a < 4; ++a) tma_load_2d(sK + a * 16384, &tmK, k_full, a * 64, j * BKEY);
+                for (int a = 0; a < 4; ++a) tma_load_2d(sK + a * 16384, &tmK, k_full, a * 64, (jb0 + j) * BKEY);
             }
         } else if (lane == 1) {
             tc5::prefetch_tensormap(&tmV);
@@ -155,7 +171,7 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
                 for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
                     for (int a = 0; a < 4; ++a)
-                        tma_load_2d(sV + kb * 32768 + a * 8192, &tmV, v_full, a * 64, j * BKEY + kb * 64);
+                        tma_load_2d(sV + kb * 32768 + a * 8192, &tmV, v_full, a * 64, (jb0 + j) * BKEY + kb * 64);
             }
         }
     } else if (warp == 1) {
@@ -213,7 +229,8 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
             // the whole 128-key score row of this thread, read once (four loads in flight, one wait)
             float v[BKEY];
             ld_row128(t_s, v);
-            const bool ragged = (j + 1) * BKEY > p.nk;      // only the last block can hold keys past the end
+            const int key0 = (jb0 + j) * BKEY;              // first key of this block
+            const bool ragged = key0 + BKEY > p.nk;         // only the last block can hold keys past the end
             float mx = -INFINITY;
             if (!ragged) {
 #pragma unroll
@@ -221,7 +238,7 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
             } else {
 #pragma unroll
                 for (int i = 0; i < BKEY; ++i)
-                    if (j * BKEY + i < p.nk) mx = fmaxf(mx, v[i]);
+                    if (key0 + i < p.nk) mx = fmaxf(mx, v[i]);
             }
             mx *= p.scale_log2;                              // the scale is positive
             if (j == 0) {
@@ -254,7 +271,7 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
                 for (int i = 0; i < BKEY; ++i) { v[i] = fast_exp2(fmaf(v[i], p.scale_log2, -m_used)); psum += v[i]; }
             } else {
 #pragma unroll
-                for (int i = 0; i < BKEY; ++i) { v[i] = j * BKEY + i < p.nk ? fast_exp2(fmaf(v[i], p.scale_log2, -m_used)) : 0.f; psum += v[i]; }
+                for (int i = 0; i < BKEY; ++i) { v[i] = key0 + i < p.nk ? fast_exp2(fmaf(v[i], p.scale_log2, -m_used)) : 0.f; psum += v[i]; }
             }
             ok = ok && mbar_wait(p_empty, (uint32_t)(j & 1) ^ 1u, abort_flag);      // P_{j-1} has been consumed
             __syncwarp();
@@ -278,12 +295,80 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
         if (nblk > 0) ok = ok && mbar_wait(o_done, (uint32_t)((nblk - 1) & 1), abort_flag);
         __syncwarp();
         tc5::tc_fence_after();
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
         const int grow = q0 + row;
         const bool store = ok && grow < p.nq;              // the TMEM loads are warp-collective: only the stores are predicated
-        bf16* dst = p.out + (size_t)(store ? grow : 0) * HD;
+        bf16* dst = p.out + (size_t)(grow < p.nq ? grow : 0) * HD;
+        if (p.split) {
+            // Reduce-scatter with the mate. All of this CTA's MMAs are complete, so its K, V and P buffers are idle:
+            // K stages the mate's column half of the accumulator as [column quad][row][4], P holds the rows'
+            // (maximum, sum) for sending (first 1 KB) and the mate's (second 1 KB), V receives the mate's partial
+            // sums of THIS CTA's column half.
+            constexpr uint32_t HALF_BYTES = BQ * (HD / 2) * 4, STAT_BYTES = BQ * 8;
+            const int mine = (int)rank, other = mine ^ 1;
+            if (warp == 2 && lane == 0) {
+                mbar_expect_tx(x_recv, HALF_BYTES + STAT_BYTES);
+                uint32_t rb;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rb) : "r"(x_ready), "r"(other));
+                asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(rb) : "memory");
+            }
+            reinterpret_cast<float2*>(gen + OFF_P)[row] = make_float2(m_used, l);
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
+            for (int c = 0; c < HD / 64; ++c) {
+                float o[32];
+                tc5::tmem_ld32(tmem + t_lane + O_COL + other * (HD / 2) + c * 32, o);
+                float* stage = reinterpret_cast<float*>(gen + OFF_K) + (c * 8) * (BQ * 4) + row * 4;
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<float4*>(stage + (i / 4) * (BQ * 4)) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // staged values -> visible to the bulk copies
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (warp == 2 && lane == 0) {
+                if (mbar_wait(x_ready, 0, abort_flag)) {      // the mate's V and P buffers are idle
+                    uint32_t dv, dp, rb;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dv) : "r"(sV), "r"(other));
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dp) : "r"(sP + STAT_BYTES), "r"(other));
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rb) : "r"(x_recv), "r"(other));
+#pragma unroll
+                    for (uint32_t off = 0; off < HALF_BYTES; off += 16384)
+                        asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(dv + off), "r"(sK + off), "r"(16384), "r"(rb) : "memory");
+                    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(dp), "r"(sP), "r"(STAT_BYTES), "r"(rb) : "memory");
+                }
+            }
+            ok = mbar_wait(x_recv, 0, abort_flag) && ok;
+            const float2 theirs = reinterpret_cast<const float2*>(gen + OFF_P + STAT_BYTES)[row];
+            // both partial results against the larger maximum
+            const float m_all = fmaxf(m_used, theirs.x);
+            const float s_own = fast_exp2(m_used - m_all), s_their = fast_exp2(theirs.x - m_all);
+            const float l_all = l * s_own + theirs.y * s_their;
+            const float inv_all = l_all > 0.f ? 1.0f / l_all : 0.f;
+            const float w_own = s_own * inv_all, w_their = s_their * inv_all;
+            const bool st = ok && grow < p.nq;
+#pragma unroll 1
+            for (int c = 0; c < HD / 64; ++c) {
+                float o[32];
+                tc5::tmem_ld32(tmem + t_lane + O_COL + mine * (HD / 2) + c * 32, o);
+                const float* recv = reinterpret_cast<const float*>(gen + OFF_V) + (c * 8) * (BQ * 4) + row * 4;
+                if (st) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 r0 = *reinterpret_cast<const float4*>(recv + (2 * q) * (BQ * 4));
+                        const float4 r1 = *reinterpret_cast<const float4*>(recv + (2 * q + 1) * (BQ * 4));
+                        *reinterpret_cast<uint4*>(dst + mine * (HD / 2) + c * 32 + q * 8) =
+                            make_uint4(pack_bf16x2(o[8 * q] * w_own + r0.x * w_their, o[8 * q + 1] * w_own + r0.y * w_their),
+                                       pack_bf16x2(o[8 * q + 2] * w_own + r0.z * w_their, o[8 * q + 3] * w_own + r0.w * w_their),
+                                       pack_bf16x2(o[8 * q + 4] * w_own + r1.x * w_their, o[8 * q + 5] * w_own + r1.y * w_their),
+                                       pack_bf16x2(o[8 * q + 6] * w_own + r1.z * w_their, o[8 * q + 7] * w_own + r1.w * w_their));
+                    }
+                }
+                __syncwarp();
+            }
+        }
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < (p.split ? 0 : HD / 32); ++c) {
             float o[32];
             tc5::tmem_ld32(tmem + t_lane + O_COL + c * 32, o);
             if (store) {
@@ -299,6 +384,8 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
 
     tc5::tc_fence_before();
     __syncthreads();
+    // neither mate leaves while the other's bulk copies may still read its shared memory or signal its barrier
+    if (p.split) asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (warp == 1) {
         tc5::tc_fence_after();
         tc5::tmem_dealloc(tmem, 512);
@@ -322,8 +409,25 @@ inline int launch_attention_tc5(const void* Q, const void* K, const void* V, voi
     if (rc) return rc;
     rc = tc5::make_map(&tmV, V, HD, (uint64_t)nk, HD, 64, 64);
     if (rc) return rc;
-    Args a{static_cast<bf16*>(out), nq, nk, scale_log2, status};
-    cudaError_t e = launch_pdl(kern, dim3((nq + BQ - 1) / BQ), dim3(THREADS), SMEM, st, a, tmQ, tmK, tmV);
+    // Two CTAs per query tile (each half of the key blocks) when that still fits one CTA per SM and both get a block.
+    const int q_tiles = (nq + BQ - 1) / BQ;
+    const int split = (2 * q_tiles <= tc5::num_sms() && (nk + BKEY - 1) / BKEY >= 2) ? 1 : 0;
+    Args a{static_cast<bf16*>(out), nq, nk, scale_log2, status, split};
+    cudaError_t e;
+    if (split) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * q_tiles); cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = SMEM; cfg.stream = st;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled() ? 2 : 1;
+        e = cudaLaunchKernelEx(&cfg, kern, a, tmQ, tmK, tmV);
+    } else {
+        e = launch_pdl(kern, dim3(q_tiles), dim3(THREADS), SMEM, st, a, tmQ, tmK, tmV);
+    }
     if (e != cudaSuccess) { set_error("attention_tc5_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("attention_tc5_kernel");
 }
