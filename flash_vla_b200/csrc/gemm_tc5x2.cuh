@@ -446,13 +446,25 @@ inline int launch_pair(const GemmArgs& g, int splits, void* ws, int* status, cud
     cfg.blockDim = dim3(320, 1, 1);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     cfg.stream = st;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[3];
+    int n_attr = 0;
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 2; attr[n_attr].val.clusterDim.y = 1; attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+    if (splits > 1) {
+        // The items of a tile wait for one another (shared-out final sum): a cooperative launch makes the whole grid
+        // resident at once, so no item can wait for a mate that another grid keeps off the SMs.
+        attr[n_attr].id = cudaLaunchAttributeCooperative;
+        attr[n_attr].val.cooperative = 1;
+        ++n_attr;
+    }
+    if (pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cfg.numAttrs = n_attr;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, tmA, tmG, tmU);
     if (e != cudaSuccess) { set_error("tc5x2_gemm_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("tc5x2_gemm_kernel");
