@@ -30,6 +30,26 @@ def test_layer_norm_and_rms():
     assert torch.allclose(f, 1.0 / torch.sqrt(x.pow(2).mean(-1) + 1e-6))
 
 
+def test_layer_norm_folded_into_the_linear_layer_is_the_same_function():
+    """The algebra behind the CUDA backend's fused LayerNorm + linear ops, checked against the oracle's own op
+    (the reference's two-kernel form, wrappers.py:268-276) in fp64: with W' = diag(g) W, colsum = 1^T W' and
+    bias' = s^T W + b,  LN(x) W + b  ==  rstd * (x W' - mean * colsum) + bias',  also for rows whose mean is many
+    times their spread. And the RMS form: (x * rstd) W == rstd * (x W)."""
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(16, 1152, generator=g, dtype=torch.float64)
+    x[:4] += 6.0
+    gam, sh = torch.randn(1152, generator=g, dtype=torch.float64) * 0.5 + 1, torch.randn(1152, generator=g, dtype=torch.float64) * 0.1
+    W, b = torch.randn(1152, 96, generator=g, dtype=torch.float64) * 0.02, torch.randn(96, generator=g, dtype=torch.float64) * 0.02
+    ref = O.layer_norm(x.float(), gam.float(), sh.float()).double() @ W + b          # the oracle keeps fp32 inside the norm
+    mean = x.mean(-1, keepdim=True)
+    rstd = torch.rsqrt((x * x).mean(-1, keepdim=True) - mean * mean + 1e-5)
+    Wf = gam[:, None] * W
+    folded = rstd * (x @ Wf - mean * Wf.sum(0)) + (sh @ W + b)
+    assert (folded - ref).abs().max().item() <= 2e-5 * ref.abs().max().item()
+    r = O.rms_factor(x.float()).double()[:, None]
+    assert torch.allclose((x * r) @ W, r * (x @ W), rtol=1e-12, atol=1e-12)
+
+
 def test_rope_table_matches_reference_fixture():
     gold = torch.load(GOLDEN / "rope.pt")
     for S in (768, 816, 817):
