@@ -30,6 +30,7 @@ using tc5::mbar_init;
 using tc5::mbar_expect_tx;
 using tc5::mbar_wait;
 using tc5::tma_load_2d;
+using tc5::tma_load_3d;
 using tc5::smem_desc;
 
 constexpr int HD = 256, BQ = 128, BKEY = 128, THREADS = 192;
@@ -46,6 +47,11 @@ struct Args {
     float scale_log2;
     int* status;
     int split;          // 1: launched as clusters of two CTAs per query tile, each walking half of the key blocks
+    // A batch of sequences (grid.y): sequence e reads slab e of the Q / K / V tensor maps and writes `out` at
+    // e * out_stride elements. Rows below `mask_rows` only see keys up to `mask_key_le` (the action expert's
+    // state token must not see the action tokens); mask_rows = 0: no mask.
+    long long out_stride;
+    int mask_rows, mask_key_le;
 };
 
 // S = Q K^T: both operands K-major.
@@ -123,6 +129,7 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
     uint32_t rank = 0;
     if (p.split) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
     const int q0 = (p.split ? blockIdx.x >> 1 : blockIdx.x) * BQ;
+    const int seq = blockIdx.y;                                                 // which sequence of the batch
     const int half_blks = (nblk_all + 1) / 2;
     const int jb0 = p.split ? (int)rank * half_blks : 0;                        // first key block of this CTA
     const int nblk = p.split ? min(half_blks, nblk_all - jb0) : nblk_all;      // and how many it walks
@@ -155,12 +162,12 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
             tc5::prefetch_tensormap(&tmK);
             mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
-            for (int a = 0; a < 4; ++a) tma_load_2d(sQ + a * 16384, &tmQ, q_full, a * 64, q0);
+            for (int a = 0; a < 4; ++a) tma_load_3d(sQ + a * 16384, &tmQ, q_full, a * 64, q0, seq);
             for (int j = 0; j < nblk; ++j) {
                 if (!mbar_wait(k_empty, (uint32_t)(j & 1) ^ 1u, abort_flag)) break;
                 mbar_expect_tx(k_full, K_BYTES);
 #pragma unroll
-                for (int a = 0; a < 4; ++a) tma_load_2d(sK + a * 16384, &tmK, k_full, a * 64, (jb0 + j) * BKEY);
+                for (int a = 0; a < 4; ++a) tma_load_3d(sK + a * 16384, &tmK, k_full, a * 64, (jb0 + j) * BKEY, seq);
             }
         } else if (lane == 1) {
             tc5::prefetch_tensormap(&tmV);
@@ -171,7 +178,7 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
                 for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
                     for (int a = 0; a < 4; ++a)
-                        tma_load_2d(sV + kb * 32768 + a * 8192, &tmV, v_full, a * 64, (jb0 + j) * BKEY + kb * 64);
+                        tma_load_3d(sV + kb * 32768 + a * 8192, &tmV, v_full, a * 64, (jb0 + j) * BKEY + kb * 64, seq);
             }
         }
     } else if (warp == 1) {
@@ -220,6 +227,9 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
         const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
         bool ok = true;
         float m_used = 0.f, l = 0.f;
+        // keys this row may see: all of them, or (masked rows) those up to mask_key_le
+        const int key_limit = (q0 + row < p.mask_rows) ? min(p.nk, p.mask_key_le + 1) : p.nk;
+        bool seen_any = false;                               // a block with at least one visible key has been processed
         for (int j = 0; j < nblk; ++j) {
             const int b = j & 1;
             ok = ok && mbar_wait(s_full(b), (uint32_t)((j >> 1) & 1), abort_flag);
@@ -230,7 +240,7 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
             float v[BKEY];
             ld_row128(t_s, v);
             const int key0 = (jb0 + j) * BKEY;              // first key of this block
-            const bool ragged = key0 + BKEY > p.nk;         // only the last block can hold keys past the end
+            const bool ragged = key0 + BKEY > key_limit;    // a block that holds keys this row does not see (past the end, or masked)
             float mx = -INFINITY;
             if (!ragged) {
 #pragma unroll
@@ -238,13 +248,16 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
             } else {
 #pragma unroll
                 for (int i = 0; i < BKEY; ++i)
-                    if (key0 + i < p.nk) mx = fmaxf(mx, v[i]);
+                    if (key0 + i < key_limit) mx = fmaxf(mx, v[i]);
             }
             mx *= p.scale_log2;                              // the scale is positive
             if (j == 0) {
                 m_used = mx == -INFINITY ? 0.f : mx;
             } else {
-                const bool grow = mx > m_used + RESCALE_THRESHOLD;
+                // a row that has not seen a key yet (masked so far) has nothing accumulated: it adopts this block's
+                // maximum as it is; the others rescale when their maximum has grown enough
+                const bool first = !seen_any;
+                const bool grow = !first && mx > m_used + RESCALE_THRESHOLD;
                 if (__any_sync(0xffffffffu, grow)) {
                     // the accumulator must be quiet while it is rescaled: P_{j-1} V_{j-1} has to be complete
                     ok = ok && mbar_wait(o_done, (uint32_t)((j - 1) & 1), abort_flag);
@@ -263,6 +276,7 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
                     if (grow) m_used = mx;
                     tc5::tc_fence_before();
                 }
+                if (first && mx != -INFINITY) m_used = mx;
             }
             // P = 2^(scale * S - m): one fused multiply-add and one special-function op per key
             float psum = 0.f;
@@ -271,7 +285,7 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
                 for (int i = 0; i < BKEY; ++i) { v[i] = fast_exp2(fmaf(v[i], p.scale_log2, -m_used)); psum += v[i]; }
             } else {
 #pragma unroll
-                for (int i = 0; i < BKEY; ++i) { v[i] = key0 + i < p.nk ? fast_exp2(fmaf(v[i], p.scale_log2, -m_used)) : 0.f; psum += v[i]; }
+                for (int i = 0; i < BKEY; ++i) { v[i] = key0 + i < key_limit ? fast_exp2(fmaf(v[i], p.scale_log2, -m_used)) : 0.f; psum += v[i]; }
             }
             ok = ok && mbar_wait(p_empty, (uint32_t)(j & 1) ^ 1u, abort_flag);      // P_{j-1} has been consumed
             __syncwarp();
@@ -284,6 +298,7 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
                                pack_bf16x2(v[8 * piece + 4], v[8 * piece + 5]), pack_bf16x2(v[8 * piece + 6], v[8 * piece + 7]));
             }
             l += psum;
+            seen_any = seen_any || mx != -INFINITY;
             tc5::tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P stores -> visible to the MMA
             asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -297,7 +312,7 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
         tc5::tc_fence_after();
         const int grow = q0 + row;
         const bool store = ok && grow < p.nq;              // the TMEM loads are warp-collective: only the stores are predicated
-        bf16* dst = p.out + (size_t)(grow < p.nq ? grow : 0) * HD;
+        bf16* dst = p.out + (size_t)seq * p.out_stride + (size_t)(grow < p.nq ? grow : 0) * HD;
         if (p.split) {
             // Reduce-scatter with the mate. All of this CTA's MMAs are complete, so its K, V and P buffers are idle:
             // K stages the mate's column half of the accumulator as [column quad][row][4], P holds the rows'
@@ -311,7 +326,7 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
                 asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rb) : "r"(x_ready), "r"(other));
                 asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(rb) : "memory");
             }
-            reinterpret_cast<float2*>(gen + OFF_P)[row] = make_float2(m_used, l);
+            reinterpret_cast<float2*>(gen + OFF_P)[row] = make_float2(l > 0.f ? m_used : -INFINITY, l);      // a side that saw no key drops out of the merge
 #pragma unroll 1
             for (int c = 0; c < HD / 64; ++c) {
                 float o[32];
@@ -340,8 +355,9 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
             ok = mbar_wait(x_recv, 0, abort_flag) && ok;
             const float2 theirs = reinterpret_cast<const float2*>(gen + OFF_P + STAT_BYTES)[row];
             // both partial results against the larger maximum
-            const float m_all = fmaxf(m_used, theirs.x);
-            const float s_own = fast_exp2(m_used - m_all), s_their = fast_exp2(theirs.x - m_all);
+            const float m_own = l > 0.f ? m_used : -INFINITY;
+            const float m_all = fmaxf(m_own, theirs.x);
+            const float s_own = l > 0.f ? fast_exp2(m_own - m_all) : 0.f, s_their = theirs.y > 0.f ? fast_exp2(theirs.x - m_all) : 0.f;
             const float l_all = l * s_own + theirs.y * s_their;
             const float inv_all = l_all > 0.f ? 1.0f / l_all : 0.f;
             const float w_own = s_own * inv_all, w_their = s_their * inv_all;
@@ -393,8 +409,11 @@ attention_tc5_kernel(const Args p, const __grid_constant__ CUtensorMap tmQ, cons
     if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 4);
 }
 
+// `seqs` sequences of nq flat query rows x nk keys each (grid.y); Q / K / V of sequence e start q_stride / kv_stride
+// elements after those of e - 1, `out` like Q. mask_rows / mask_key_le: see Args.
 inline int launch_attention_tc5(const void* Q, const void* K, const void* V, void* out, int nq, int nk, float scale_log2,
-                                int* status, cudaStream_t st) {
+                                int* status, cudaStream_t st, int seqs = 1, long long q_stride = 0, long long kv_stride = 0,
+                                int mask_rows = 0, int mask_key_le = 0) {
     auto kern = attention_tc5_kernel;
     static PerDeviceFlag configured;
     if (!configured.get()) {
@@ -403,20 +422,20 @@ inline int launch_attention_tc5(const void* Q, const void* K, const void* V, voi
         configured.set();
     }
     CUtensorMap tmQ, tmK, tmV;
-    int rc = tc5::make_map(&tmQ, Q, HD, (uint64_t)nq, HD, 64, BQ);
+    int rc = tc5::make_map3d(&tmQ, Q, HD, (uint64_t)nq, (uint64_t)seqs, HD, (uint64_t)q_stride, 64, BQ);
     if (rc) return rc;
-    rc = tc5::make_map(&tmK, K, HD, (uint64_t)nk, HD, 64, BKEY);
+    rc = tc5::make_map3d(&tmK, K, HD, (uint64_t)nk, (uint64_t)seqs, HD, (uint64_t)kv_stride, 64, BKEY);
     if (rc) return rc;
-    rc = tc5::make_map(&tmV, V, HD, (uint64_t)nk, HD, 64, 64);
+    rc = tc5::make_map3d(&tmV, V, HD, (uint64_t)nk, (uint64_t)seqs, HD, (uint64_t)kv_stride, 64, 64);
     if (rc) return rc;
     // Two CTAs per query tile (each half of the key blocks) when that still fits one CTA per SM and both get a block.
     const int q_tiles = (nq + BQ - 1) / BQ;
-    const int split = (2 * q_tiles <= tc5::num_sms() && (nk + BKEY - 1) / BKEY >= 2) ? 1 : 0;
-    Args a{static_cast<bf16*>(out), nq, nk, scale_log2, status, split};
+    const int split = (2 * q_tiles * seqs <= tc5::num_sms() && (nk + BKEY - 1) / BKEY >= 2) ? 1 : 0;
+    Args a{static_cast<bf16*>(out), nq, nk, scale_log2, status, split, q_stride, mask_rows, mask_key_le};
     cudaError_t e;
     if (split) {
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2 * q_tiles); cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = SMEM; cfg.stream = st;
+        cfg.gridDim = dim3(2 * q_tiles, seqs); cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = SMEM; cfg.stream = st;
         cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
@@ -426,12 +445,11 @@ inline int launch_attention_tc5(const void* Q, const void* K, const void* V, voi
         cfg.numAttrs = pdl_enabled() ? 2 : 1;
         e = cudaLaunchKernelEx(&cfg, kern, a, tmQ, tmK, tmV);
     } else {
-        e = launch_pdl(kern, dim3(q_tiles), dim3(THREADS), SMEM, st, a, tmQ, tmK, tmV);
+        e = launch_pdl(kern, dim3(q_tiles, seqs), dim3(THREADS), SMEM, st, a, tmQ, tmK, tmV);
     }
     if (e != cudaSuccess) { set_error("attention_tc5_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("attention_tc5_kernel");
 }
-
 
 // ---------------------------------------------------------------------------------------------
 // SigLIP attention on tcgen05: one CTA per (view, head, half of the 256 query tokens). The whole key

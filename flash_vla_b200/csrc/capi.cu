@@ -624,11 +624,19 @@ int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* ou
                            int head_dim, int heads, int encoder_seq_len, int episodes, long long q_episode_stride,
                            long long kv_episode_stride, void* ws, size_t ws_bytes, void* stream) {
     FVLA_REQUIRE(queries > 0 && keys > 0 && episodes >= 1, "decoder_attention: bad shape");
-    FVLA_REQUIRE(episodes == 1 || (tc5_enabled() && keys <= decattn::MAX_SPL * 128 && q_episode_stride >= (long long)queries * head_dim &&
+    FVLA_REQUIRE(episodes == 1 || (tc5_enabled() && q_episode_stride >= (long long)queries * head_dim &&
                                    kv_episode_stride >= (long long)keys * head_dim && q_episode_stride % 8 == 0 && kv_episode_stride % 8 == 0),
-                 "decoder_attention: a batch of episodes needs the cluster kernel (at most %d keys) and 16-byte aligned episode strides",
-                 decattn::MAX_SPL * 128);
+                 "decoder_attention: a batch of episodes needs the tcgen05 kernels and 16-byte aligned episode strides");
     if (head_dim != 256) { set_error("decoder_attention: head_dim %d not built (256 only)", head_dim); return FVLA_ERR_UNSUPPORTED; }
+    // A batch of episodes goes to the tcgen05 flash kernel (128 flat query rows per CTA, one grid row per episode,
+    // state-token mask): at one episode its 4 query tiles would occupy 8 SMs and the cluster kernel below is faster,
+    // but the cluster kernel's 8-CTA clusters are resident 15 at a time, so E episodes take E / 1.15 rounds of it.
+    static int batched_tc5 = -1;
+    if (batched_tc5 < 0) { const char* v = getenv("FVLA_DEC_ATTN"); batched_tc5 = (v != nullptr && strcmp(v, "cluster") == 0) ? 0 : 1; }
+    if (episodes > 1 && batched_tc5 && tc5_enabled() && aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(out))
+        return attn5::launch_attention_tc5(Q, K, V, out, queries, keys, kLog2e / sqrtf((float)head_dim), device_status_ptr(), S(stream),
+                                           episodes, q_episode_stride, kv_episode_stride, heads, encoder_seq_len);
+    FVLA_REQUIRE(episodes == 1 || keys <= decattn::MAX_SPL * 128, "decoder_attention: the cluster kernel takes at most %d keys", decattn::MAX_SPL * 128);
     if (ws == nullptr || ws_bytes < fvla_decoder_attention_workspace_bytes(queries, keys)) {
         set_error("decoder_attention: workspace of %zu bytes needed", fvla_decoder_attention_workspace_bytes(queries, keys));
         return FVLA_ERR_WORKSPACE;

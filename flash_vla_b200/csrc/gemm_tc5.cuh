@@ -65,6 +65,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -812,6 +817,24 @@ inline int balanced_grid(int items, int max_ctas) {
     if (items <= max_ctas) return items;
     const int rounds = (items + max_ctas - 1) / max_ctas;
     return (items + rounds - 1) / rounds;
+}
+
+// 3-D bf16 tensor map: `inner` contiguous elements per row, `rows` rows of pitch `ld` elements, `slabs` such matrices
+// `slab_stride` elements apart (a batch of sequences, each with its own row count limit: rows past `rows` read as
+// zero instead of running into the next slab); box = box_inner x box_rows x 1, 128-byte swizzle.
+inline int make_map3d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t slabs, uint64_t ld,
+                      uint64_t slab_stride, uint32_t box_inner, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return FVLA_ERR_LAUNCH; }
+    cuuint64_t gdim[3] = {inner, rows, slabs};
+    cuuint64_t gstride[2] = {ld * sizeof(bf16), (slabs > 1 ? slab_stride : rows * ld) * sizeof(bf16)};
+    cuuint32_t box[3] = {box_inner, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), gdim, gstride, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (3-D) failed with CUresult %d", (int)r); return FVLA_ERR_ARG; }
+    return FVLA_OK;
 }
 
 struct Tc5Plan { int bn, splits; size_t ws_bytes; float est_us; };

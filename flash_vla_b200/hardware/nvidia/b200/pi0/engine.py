@@ -13,9 +13,10 @@ episodes that share the weights:
     the tiles to fill the GPU with; only the attention kernels, which mix tokens, run per episode;
   * each episode has its own KV cache; the action-expert decoder also runs ONCE over all episodes' rows
     (M = E x 51): QKV and the gated FFN as one GEMM over all rows, the two residual projections as the
-    weight-streaming cluster GEMM once per episode inside one launch, attention per episode inside one
-    launch. Below 4 episodes (or with `batch_decoder=False`) the decoders run as E single-episode
-    decoders on E streams instead, which fill each other's idle SMs and are the faster form there.
+    weight-streaming cluster GEMM once per episode inside one launch, attention for all episodes in one
+    launch of the tcgen05 flash kernel (one grid row per episode, each against its own KV cache). At 2
+    episodes (or with `batch_decoder=False`) the decoders run as E single-episode decoders on E streams
+    instead, which fill each other's idle SMs and are the faster form there.
     Decoder layer L starts as soon as the batched encoder has produced layer L's prefix K/V.
 `batch_prefix=False` keeps the older form (E complete single-episode passes on E streams), whose
 per-episode results are bit-identical to the single-episode engine; the batched form runs the same
@@ -87,10 +88,10 @@ class Pi0Inference:
             self.weights[name] = value.to(device=device, dtype=torch.bfloat16).contiguous()
         self.episode_buffers, self.pools = [], []
         self.batch_prefix = bool(batch_prefix) and episodes > 1
-        # measured on B200: the batched decoder beats concurrent single-episode decoders from 4 episodes on
-        # (E = 4: 15.6 against 17.4 ms, E = 8: 26.5 against 34.9 ms) and loses at 2 (11.7 against 9.4 ms)
+        # measured on B200: the batched decoder beats concurrent single-episode decoders from 3 episodes on
+        # (E = 3: 11.2 against 13.0 ms, E = 4: 11.7 against 17.4 ms) and loses at 2 (11.5 against 9.1 ms)
         if batch_decoder is None:
-            batch_decoder = episodes >= 4
+            batch_decoder = episodes >= 3
         self.batch_decoder = self.batch_prefix and bool(batch_decoder)
         self.prefix_buffers, self.prefix_pool, self.decoder_buffers = None, None, None
         if self.batch_prefix:

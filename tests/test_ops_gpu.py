@@ -294,6 +294,33 @@ def test_decoder_attention(ops, ref_ops, S, kv_scale, fused):
     assert torch.equal(q2[:8], q[:8])
 
 
+@pytest.mark.parametrize("S,episodes", [(768, 4), (817, 3), (1024, 2)])
+def test_decoder_attention_for_a_batch_of_episodes(ops, ref_ops, S, episodes):
+    """The batched decoder's attention: E episodes in one call (3-D Q, K / V views of per-episode caches that also
+    hold other rows), each against its own keys, the state token's mask included. Every episode is compared with
+    the oracle's single-episode op; 1 075 keys (S = 1024) go beyond what the cluster kernel takes for a batch."""
+    g = torch.Generator().manual_seed(31)
+    keys = S + 51
+    Q = rnd(g, episodes, 408, 256)
+    cache_k = rnd(g, episodes, keys + 13, 256)             # each episode's cache holds rows that are not keys of this call
+    cache_v = rnd(g, episodes, keys + 13, 256)
+    q = Q.cuda().clone()
+    k_all, v_all = cache_k.cuda()[:, :keys], cache_v.cuda()[:, :keys]
+    ops[1].decoder_attention(q.view(-1, 256), k_all, v_all, None, q.view(-1, 256), S)      # flat rows, out aliases Q
+    for e in range(episodes):
+        ref = torch.zeros(408, 256)
+        ref_ops[1].decoder_attention(Q[e].float(), cache_k[e, :keys].float(), cache_v[e, :keys].float(), None, ref, S)
+        assert_close(q[e], ref, what=f"decoder_attention, episode {e} of {episodes}")
+    # mask property per episode: the state token's rows must not depend on keys past S
+    k2, v2 = cache_k.clone(), cache_v.clone()
+    k2[:, S + 1:] += 1.0
+    v2[:, S + 1:] -= 1.0
+    q2 = Q.cuda().clone()
+    ops[1].decoder_attention(q2.view(-1, 256), k2.cuda()[:, :keys], v2.cuda()[:, :keys], None, q2.view(-1, 256), S)
+    assert torch.equal(q2[:, :8], q[:, :8])
+    assert not torch.equal(q2[:, 8:], q[:, 8:])
+
+
 @pytest.mark.parametrize("M", [51, 1])
 @pytest.mark.parametrize("fused", [False, True])
 def test_decoder_norm_gated_ffn(ops, ref_ops, M, fused):
