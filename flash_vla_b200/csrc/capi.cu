@@ -498,20 +498,26 @@ int fvla_linear_residual(const void* x, const void* weight, void* out, int out_i
         sa.x = x; sa.x_f32 = 0; sa.ldx = K; sa.M = rows; sa.N = N; sa.K = K; sa.groups = groups;
         sa.out = out; sa.out_f32 = out_is_f32; sa.ldo = N; sa.out_shadow = Bm(out_shadow);
         sa.status = device_status_ptr(); FVLA_DBG_ATTACH(sa);
-        // With several row groups a long K (the down projection: 64 k-blocks, 8-way split, 256 CTAs for four
-        // groups, three waves of clusters) is better taken as two launches over half of K each: each half
-        // splits 4 ways and all its clusters are resident at once. The second launch accumulates onto the first.
+        // With several row groups the clusters of one launch may not all be resident at once (about 15 clusters of
+        // 8, 33 of 4, 74 of 2), and a second round of clusters costs as much as the first. K is then cut into 2, 4 or
+        // 8 parts, one launch each, with the widest split whose clusters of all groups ARE resident together; every
+        // launch after the first accumulates onto the result of the one before (the residual form does that anyway).
+        auto resident = [](int splits) { return splits >= 8 ? 15 * 8 : (splits == 4 ? 33 * 4 : 148); };
         const skinny::SkinnyPlan whole = skinny::plan_skinny(rows, N, K, false, groups);
-        if (groups > 1 && whole.splits == 8 && whole.tiles * whole.splits * groups > 15 * 8 && (K / 2) % 64 == 0 &&
-            skinny::plan_skinny(rows, N, K / 2, false, groups).ok) {
-            const skinny::SkinnyPlan half = skinny::plan_skinny(rows, N, K / 2, false, groups);
-            if (half.tiles * half.splits * groups <= (half.splits >= 8 ? 15 * 8 : 33 * 4)) {
-                sa.K = K / 2;
-                int rc = skinny::launch_skinny<skinny::EPI_RESIDUAL>(sa, weight, nullptr, N, S(stream));
-                if (rc) return rc;
-                sa.x = B(x) + K / 2;
-                return skinny::launch_skinny<skinny::EPI_RESIDUAL>(sa, B(weight) + (size_t)(K / 2) * N, nullptr, N, S(stream));
+        if (groups > 1 && whole.tiles * whole.splits * groups > resident(whole.splits)) {
+            for (int parts = 2; parts <= 8; parts *= 2) {
+                if (K % parts || (K / parts) % 64) break;
+                const skinny::SkinnyPlan part = skinny::plan_skinny(rows, N, K / parts, false, groups);
+                if (!part.ok || part.tiles * part.splits * groups > resident(part.splits)) continue;
+                sa.K = K / parts;
+                for (int i = 0; i < parts; ++i) {
+                    sa.x = B(x) + (size_t)i * (K / parts);
+                    int rc = skinny::launch_skinny<skinny::EPI_RESIDUAL>(sa, B(weight) + (size_t)i * (K / parts) * N, nullptr, N, S(stream));
+                    if (rc) return rc;
+                }
+                return FVLA_OK;
             }
+            sa.K = K; sa.x = x;
         }
         return skinny::launch_skinny<skinny::EPI_RESIDUAL>(sa, weight, nullptr, N, S(stream));
     }
