@@ -451,7 +451,10 @@ inline int launch_pair(const GemmArgs& g, int splits, void* ws, int* status, cud
     attr[n_attr].id = cudaLaunchAttributeClusterDimension;
     attr[n_attr].val.clusterDim.x = 2; attr[n_attr].val.clusterDim.y = 1; attr[n_attr].val.clusterDim.z = 1;
     ++n_attr;
-    if (splits > 1) {
+    // FVLA_COOP=0 (diagnostic: a profiler that cannot replay cooperative launches) drops the attribute; the waits stay bounded
+    static int coop = -1;
+    if (coop < 0) { const char* v = getenv("FVLA_COOP"); coop = (v != nullptr && v[0] == '0') ? 0 : 1; }
+    if (splits > 1 && coop) {
         // The items of a tile wait for one another (shared-out final sum): a cooperative launch makes the whole grid
         // resident at once, so no item can wait for a mate that another grid keeps off the SMs.
         attr[n_attr].id = cudaLaunchAttributeCooperative;
