@@ -451,9 +451,13 @@ inline int launch_pair(const GemmArgs& g, int splits, void* ws, int* status, cud
     attr[n_attr].id = cudaLaunchAttributeClusterDimension;
     attr[n_attr].val.clusterDim.x = 2; attr[n_attr].val.clusterDim.y = 1; attr[n_attr].val.clusterDim.z = 1;
     ++n_attr;
-    // FVLA_COOP=0 (diagnostic: a profiler that cannot replay cooperative launches) drops the attribute; the waits stay bounded
+    // Nsight Compute reports a launch failure for this cooperative cluster launch: when the process runs under it (it
+    // exports NV_COMPUTE_PROFILER_PERFWORKS_DIR), or with FVLA_COOP=0, the attribute is dropped; the waits stay bounded.
     static int coop = -1;
-    if (coop < 0) { const char* v = getenv("FVLA_COOP"); coop = (v != nullptr && v[0] == '0') ? 0 : 1; }
+    if (coop < 0) {
+        const char* v = getenv("FVLA_COOP");
+        coop = v != nullptr ? (v[0] == '0' ? 0 : 1) : (getenv("NV_COMPUTE_PROFILER_PERFWORKS_DIR") != nullptr ? 0 : 1);
+    }
     if (splits > 1 && coop) {
         // The items of a tile wait for one another (shared-out final sum): a cooperative launch makes the whole grid
         // resident at once, so no item can wait for a mate that another grid keeps off the SMs.
