@@ -197,7 +197,8 @@ int fvla_decoder_norm_qkv_rope(const void* x, int x_is_f32, const void* x_shadow
  * the stream writes the prefix rows must put an event or another kernel between the two.
  * episodes > 1 (an extension): that many independent episodes in one launch; `queries` and `keys` are
  * per episode, episode e reads Q + e * q_episode_stride and K / V + e * kv_episode_stride (strides in
- * elements, multiples of 8) and writes out + e * q_episode_stride. Needs keys <= 1408. */
+ * elements, multiples of 8) and writes out + e * q_episode_stride. A batch runs on the tcgen05 flash
+ * kernel (one grid row per episode), which waits for its predecessor before any read. */
 int fvla_decoder_attention(const void* Q, const void* K, const void* V, void* out, int queries,
                            int keys, int head_dim, int heads, int encoder_seq_len, int episodes,
                            long long q_episode_stride, long long kv_episode_stride, void* ws,
