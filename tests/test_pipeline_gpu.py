@@ -179,6 +179,23 @@ def test_fused_and_unfused_tables_agree(full_checkpoint):
         assert cosine(outs[fused], gold["actions"]) >= FINAL_COSINE, fused
 
 
+def test_many_replays_stay_identical_and_healthy(full_checkpoint):
+    """The kernels' inter-CTA hand-offs (cluster exchanges, the shared-out split-K sum, self-resetting counters)
+    must leave no state behind: 150 replays of the captured forward give the first result bit for bit, and no
+    bounded device wait has expired."""
+    from flash_vla_b200 import Pi0Inference
+    from flash_vla_b200.hardware.nvidia.b200.pi0.backends.cuda import _lib
+
+    engine = Pi0Inference(full_checkpoint, num_views=3, chunk_size=50)
+    images, state, noise = bench_inputs()
+    first = engine.forward(images, state, noise).clone()
+    for _ in range(150):
+        engine.graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(engine.forward(images, state, noise), first)
+    assert _lib.load().fvla_device_status(None) == 0
+
+
 def test_frozen_pool_refuses_new_scratch(full_checkpoint):
     """After capture a scratch request that warm-up never made raises instead of allocating."""
     from flash_vla_b200.runtime.cuda import ScratchPool
