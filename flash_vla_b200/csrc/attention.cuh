@@ -13,6 +13,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "gemm_tc5.cuh"
 
 namespace fvla {
 
@@ -303,12 +304,20 @@ namespace decattn {
 constexpr int HD = 256, BQ = 32, MIN_SPL = 8, MAX_SPL = 11, PITCH = HD * 2 + 16, CH = HD / 8, THREADS = 256;
 constexpr int OP = HD + 8;                          // fp32 row pitch of the merge / staging buffers: rows 8 banks apart
 constexpr int SLICE = 4 * OP * 4;                   // bytes of the 4 staged rows one owner receives from one rank
-constexpr int Q_BYTES = BQ * PITCH, KV_BYTES = 128 * PITCH;
-constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + KV_BYTES;
-constexpr int OFF_SX = OFF_V + KV_BYTES;                                                 // score swap: [warp 8][32][lane 32] fp32
+// K and V tiles: 128 keys x 256 dims as four 64-dim blocks of [128 rows][128 bytes] in the 128-byte swizzle a tensor
+// load writes (16-byte piece c of row r at piece c ^ (r & 7): eight consecutive keys of one piece sit in eight
+// different bank groups, which is what ldmatrix wants); the tiles lead the buffer so that they are 1 KB aligned.
+// Q keeps the padded row pitch.
+constexpr int Q_BYTES = BQ * PITCH, KV_BYTES = 128 * HD * 2, KV_BLOCK = 128 * 128;
+constexpr int OFF_K = 0, OFF_V = OFF_K + KV_BYTES, OFF_Q = OFF_V + KV_BYTES;
+constexpr int OFF_SX = OFF_Q + Q_BYTES;                                                  // score swap: [warp 8][32][lane 32] fp32
 constexpr int OFF_BAR = OFF_SX + 8 * 32 * 32 * 4;
 constexpr int OFF_RED = OFF_BAR + 64;                                                    // RED: [src spl][4 rows][OP] fp32, then LSE_IN [src spl][4] fp32
-constexpr int smem_bytes(int spl) { return OFF_RED + spl * (SLICE + 16); }
+constexpr int smem_bytes(int spl) { return 1024 + OFF_RED + spl * (SLICE + 16); }      // 1 KB of slack to align the tiles
+// shared-memory address of 16-byte piece `piece` (0..31) of row `row` of a K / V tile
+__device__ __forceinline__ uint32_t kv_piece(uint32_t tile, int row, int piece) {
+    return tile + (uint32_t)(piece >> 3) * KV_BLOCK + (uint32_t)row * 128u + (uint32_t)(((piece & 7) ^ (row & 7)) << 4);
+}
 static_assert(smem_bytes(MAX_SPL) <= 227 * 1024, "the largest cluster's receive buffers must fit in shared memory");
 // staging areas alias K (half-merge buffer) and V (final partial) once the MMAs are done
 constexpr int OFF_HALF = OFF_K;                    // [32 rows][OP] fp32 + m[32] + l[32]
@@ -322,11 +331,13 @@ __device__ __forceinline__ uint32_t dsm_map(uint32_t local_addr, uint32_t rank) 
     return r;
 }
 
-__global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster_kernel(const DecAttnArgs p) {
+__global__ void __launch_bounds__(decattn::THREADS, 1)
+decoder_attention_cluster_kernel(const DecAttnArgs p, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
     using namespace decattn;
-    extern __shared__ __align__(128) uint8_t smem[];
-    const uint32_t sbase = smem_u32(smem);
-    const uint32_t sQ = sbase, sK = sbase + OFF_K, sV = sbase + OFF_V;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (sbase - smem_u32(smem_raw));
+    const uint32_t sQ = sbase + OFF_Q, sK = sbase + OFF_K, sV = sbase + OFF_V;
     const uint32_t in_bar = sbase + OFF_BAR;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_BAR + 16);
     const int SPL = p.splits;
@@ -353,26 +364,21 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
     const int pre_end = min(key_end, p.prefix_keys);
     const uint32_t pre_bar = sbase + OFF_BAR + 24;
     if (tid == 0) {
-        const int n_pre = max(0, min(pre_end - key_beg, 128));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(in_bar) : "memory");
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pre_bar) : "memory");
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         if (i_own)
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(in_bar), "r"(SPL * (SLICE + 16)) : "memory");
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pre_bar), "r"(n_pre * 2 * HD * 2) : "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pre_bar), "r"(2 * KV_BYTES) : "memory");      // whole boxes, zero fill included
     }
     // relaxed: the fence above already published the barrier to the cluster
     asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
-    // The prefix K and V rows (almost all of the tile) arrive as one 512-byte bulk copy per row (a row of the
-    // padded shared-memory tile is 16-byte aligned): thread t < 128 owns K row t, thread t >= 128 owns V row
-    // t - 128. About two hundred copy instructions per CTA instead of several thousand 16-byte ones, which
-    // is what a CTA that could only start after the previous kernel left its SM was waiting on.
-    auto bulk_row = [&](uint32_t dst, const bf16* src, uint32_t bar) {
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(dst), "l"(src), "r"(HD * 2), "r"(bar) : "memory");
-    };
+    // The prefix K and V rows (almost all of the tile) arrive as four tensor loads per tile (64 dims x 128 keys each)
+    // through maps that END at the prefix: the rows behind it, which the preceding kernel is still writing, are
+    // not touched in memory and read as zero. Eight copy requests per CTA, which is what a CTA that could only
+    // start after the previous kernel left its SM waits for.
     auto bounded_wait = [&](uint32_t bar) {
         for (uint32_t i = 0; i < (1u << 22); ++i) {
             uint32_t done;
@@ -383,18 +389,19 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
         }
         *abort_flag = 1;
     };
-    const int my_row = tid & 127;                              // row of this thread's K (tid < 128) or V tile
-    const uint32_t my_tile = tid < 128 ? sK : sV;
-    const bf16* my_src = tid < 128 ? gk : gv;
     __syncthreads();                                           // the barriers are initialised
-    if (key_beg + my_row < pre_end) bulk_row(my_tile + my_row * PITCH, my_src + (size_t)(key_beg + my_row) * HD, pre_bar);
-    for (int idx = tid; idx < 128 * CH; idx += THREADS) {
-        int r = idx / CH, c = idx % CH;
-        if (key_beg + r >= key_end) {
-            *reinterpret_cast<uint4*>(smem + OFF_K + r * PITCH + c * 16) = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(smem + OFF_V + r * PITCH + c * 16) = make_uint4(0, 0, 0, 0);
+    if (tid == 0) {
+#pragma unroll
+        for (int cb = 0; cb < HD / 64; ++cb) {
+            tc5::tma_load_3d(sK + cb * KV_BLOCK, &tmK, pre_bar, cb * 64, key_beg, blockIdx.z);
+            tc5::tma_load_3d(sV + cb * KV_BLOCK, &tmV, pre_bar, cb * 64, key_beg, blockIdx.z);
         }
-        if (r < BQ && q0 + r >= p.nq) *reinterpret_cast<uint4*>(smem + r * PITCH + c * 16) = make_uint4(0, 0, 0, 0);
+    }
+    // (Rows of the tile past this split's last key hold the next split's keys, or zeros past the prefix: their
+    // scores are masked below and their probabilities are zero, so they need no clearing.)
+    for (int idx = tid; idx < BQ * CH; idx += THREADS) {
+        int r = idx / CH, c = idx % CH;
+        if (q0 + r >= p.nq) *reinterpret_cast<uint4*>(smem + OFF_Q + r * PITCH + c * 16) = make_uint4(0, 0, 0, 0);
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -408,16 +415,19 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
             const int r = idx / CH, c = idx % CH;
             if (q0 + r < p.nq) cp_async16(sQ + r * PITCH + c * 16, gq + (size_t)(q0 + r) * HD + c * 8, 16);
         }
+        cp_async_commit();
         if (post_lo < key_end) {
+            // the new keys land on rows the tensor loads zero-filled: wait for those loads first
+            bounded_wait(pre_bar);
             for (int idx = tid; idx < 128 * CH; idx += THREADS) {
                 const int r = idx / CH, c = idx % CH, g = key_beg + r;
                 if (g >= post_lo && g < key_end) {
-                    cp_async16(sK + r * PITCH + c * 16, gk + (size_t)g * HD + c * 8, 16);
-                    cp_async16(sV + r * PITCH + c * 16, gv + (size_t)g * HD + c * 8, 16);
+                    cp_async16(kv_piece(sK, r, c), gk + (size_t)g * HD + c * 8, 16);
+                    cp_async16(kv_piece(sV, r, c), gv + (size_t)g * HD + c * 8, 16);
                 }
             }
+            cp_async_commit();
         }
-        cp_async_commit();
         cp_async_wait<0>();
     }
     bounded_wait(pre_bar);
@@ -429,7 +439,7 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
     float o[HD / 16][4];                               // this warp's 128 output columns
     float m_run[2], l_run[2];
     {
-        const uint32_t sKb = sK + kh * 64 * PITCH, sVb = sV + kh * 64 * PITCH;
+        const int kv_row0 = kh * 64;                       // this warp's half of the tile's keys
         float s[8][4];
 #pragma unroll
         for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
@@ -442,7 +452,7 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
             for (int nj = 0; nj < 4; ++nj) {
                 uint32_t b[4];
                 int key = nj * 16 + (lane & 7) + (lane >> 4) * 8;
-                ldmatrix_x4(b, sKb + key * PITCH + (kk * 2 + ((lane >> 3) & 1)) * 16);
+                ldmatrix_x4(b, kv_piece(sK, kv_row0 + key, kk * 2 + ((lane >> 3) & 1)));
                 mma_bf16_16816(s[2 * nj], a, b[0], b[1]);
                 mma_bf16_16816(s[2 * nj + 1], a, b[2], b[3]);
             }
@@ -512,7 +522,7 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
                 const int dj = dh * (HD / 32) + dl;
                 uint32_t b[4];
                 int key = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                ldmatrix_x4_trans(b, sVb + key * PITCH + (dj * 2 + (lane >> 4)) * 16);
+                ldmatrix_x4_trans(b, kv_piece(sV, kv_row0 + key, dj * 2 + (lane >> 4)));
                 mma_bf16_16816(o[2 * dl], a, b[0], b[1]);
                 mma_bf16_16816(o[2 * dl + 1], a, b[2], b[3]);
             }
@@ -619,6 +629,15 @@ __global__ void __launch_bounds__(decattn::THREADS, 1) decoder_attention_cluster
 
 inline int launch_decoder_attention_cluster(const DecAttnArgs& a, bool pdl, cudaStream_t st) {
     auto kern = decoder_attention_cluster_kernel;
+    // K / V maps that end at the prefix (rows the preceding kernel may still be writing are never fetched by them)
+    CUtensorMap tmK, tmV;
+    const int seqs = a.episodes > 1 ? a.episodes : 1;
+    const int pre_rows = a.prefix_keys < a.nk ? a.prefix_keys : a.nk;
+    if (pre_rows <= 0) { set_error("decoder attention: no prefix keys"); return FVLA_ERR_UNSUPPORTED; }
+    int rc = tc5::make_map3d(&tmK, a.k, decattn::HD, (uint64_t)pre_rows, (uint64_t)seqs, decattn::HD, (uint64_t)a.kv_episode_stride, 64, 128);
+    if (rc) return rc;
+    rc = tc5::make_map3d(&tmV, a.v, decattn::HD, (uint64_t)pre_rows, (uint64_t)seqs, decattn::HD, (uint64_t)a.kv_episode_stride, 64, 128);
+    if (rc) return rc;
     static PerDeviceFlag configured;
     if (!configured.get()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, decattn::smem_bytes(decattn::MAX_SPL));
@@ -642,7 +661,7 @@ inline int launch_decoder_attention_cluster(const DecAttnArgs& a, bool pdl, cuda
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, tmK, tmV);
     if (e != cudaSuccess) { set_error("decoder_attention_cluster_kernel: %s", cudaGetErrorString(e)); return FVLA_ERR_LAUNCH; }
     return check_launch("decoder_attention_cluster_kernel");
 }
