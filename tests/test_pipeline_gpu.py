@@ -196,6 +196,24 @@ def test_many_replays_stay_identical_and_healthy(full_checkpoint):
     assert _lib.load().fvla_device_status(None) == 0
 
 
+def test_one_view_forward(full_checkpoint):
+    """One camera view (prefix 256, decoder keys 307): the M = 256 shapes of every prefix kernel and a decoder
+    attention whose later key splits lie wholly behind the prefix, against the oracle's forward on the same
+    inputs (computed here: about two seconds of CPU)."""
+    from flash_vla_b200 import Pi0Inference
+    from oracle import pi0_ref as O
+
+    images, state, noise = bench_inputs()
+    images = images[:1]
+    ref, _ = O.forward({k: v.float() for k, v in full_checkpoint.items()}, images.float(), state.float(), noise.float(), num_views=1)
+    engine = Pi0Inference(full_checkpoint, num_views=1, chunk_size=50)
+    assert engine.encoder_seq_len == 256
+    out = engine.forward(images, state, noise)
+    cos = cosine(out, ref)
+    print(f"\none view: final actions cosine {cos:.6f}, max-abs {(out.float().cpu() - ref.float()).abs().max().item():.4g}")
+    assert cos >= FINAL_COSINE
+
+
 def test_frozen_pool_refuses_new_scratch(full_checkpoint):
     """After capture a scratch request that warm-up never made raises instead of allocating."""
     from flash_vla_b200.runtime.cuda import ScratchPool
