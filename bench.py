@@ -1,6 +1,6 @@
 """Benchmark of the Pi0 forward pass on B200: one JSON line per run.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|reference-gpu]
 
 Workload (N = 1): the full Pi0 forward at the published shape - 3 views of 224x224x3, empty
 prompt, chunk 50, 10 Euler steps, 18 decoder layers, bf16, batch 1, whole pass in one CUDA
@@ -26,7 +26,11 @@ Reported:
   cpu_baseline the CPU fp32 oracle (a port: the reference has no CPU path) on this host's cores.
   env          GPU, driver, CUDA, torch, CPU model and core count of the run.
 
-`--impl reference` times that CPU oracle alone, as the reference arm. `--episodes E` switches to the
+`--impl reference` times that CPU oracle alone, as the reference arm. `--impl reference-gpu` runs the UNMODIFIED
+reference itself (its TileLang kernels and engine, from an installed copy under baseline/_ref, which is not part of
+this repository) on the GPU for the same metric and workload, and prints `unavailable` when that copy or TileLang
+is missing; the main line carries the figure recorded when the parity fixture was made (`reference_gpu_recorded`).
+`--episodes E` switches to the
 throughput profile (E independent episodes per GPU inside the graph; `ms_per_step` is then the time of one
 replay = E forwards); `--sweep` times the FFN GEMMs and the prefix attention alone.
 """
@@ -254,6 +258,80 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def reference_gpu_recorded():
+    """The reference engine's own time on a B200, recorded by tests/golden/make_reference_gpu_golden.py when the
+    parity fixture was made. Not measured by this run."""
+    path = ROOT / "tests" / "golden" / "reference_gpu.pt"
+    if not path.exists():
+        return None
+    data = torch.load(path)
+    if "timing" not in data:
+        return None
+    return {"ms_per_forward": data["timing"]["ms_per_replay"], "gpu": data["meta"]["gpu"], "tilelang": data["meta"]["tilelang"],
+            "source": "recorded in tests/golden/reference_gpu.pt: one graph replay of the reference's own engine (flash_vla.Pi0Inference, "
+                      "its TileLang kernels) on the same workload; not measured by this run (see --impl reference-gpu)"}
+
+
+def run_reference_gpu(args):
+    """The unmodified reference through its own public API, from the installed copy under baseline/_ref."""
+    rank, local_rank, world = dist_env()
+    if rank != 0:
+        return
+    ref_dir = ROOT / "baseline" / "_ref"
+
+    def unavailable(why):
+        print(json.dumps({"impl": "reference-gpu", "unavailable": why}))
+
+    if not (ref_dir / "flash_vla").is_dir():
+        return unavailable("no installed copy of the reference under baseline/_ref (pip install --no-deps --target baseline/_ref <checkout>)")
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device")
+    try:
+        import tilelang  # noqa: F401
+    except Exception as e:      # the reference's only hard dependency besides torch
+        return unavailable(f"tilelang cannot be imported: {type(e).__name__}")
+    os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
+    sys.path.insert(0, str(ref_dir))
+    import flash_vla
+    from flash_vla_b200.synthetic import bench_inputs
+    torch.cuda.set_device(local_rank)
+    ck = flash_vla.random_checkpoint(prompt_len=0, wscale=0.02, seed=0, device="cuda")
+    engine = flash_vla.Pi0Inference(ck, num_views=3, chunk_size=50)
+    host = [t.to(torch.bfloat16).pin_memory() for t in bench_inputs()]
+    dev = [t.cuda() for t in host]
+    K, W = args.steps, max(3, args.warmup)
+    engine.forward(*dev)
+    for _ in range(W):
+        engine.graph.replay()
+    with ClockSampler(local_rank) as clocks:
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        for _ in range(K):
+            engine.graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e) / K
+        out_host = torch.empty((50, 32), dtype=torch.bfloat16).pin_memory()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(K):
+            out_host.copy_(engine.forward(*host), non_blocking=True)
+            torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1000.0 / K
+    line = {
+        "impl": "reference-gpu", "metric": "pi0_forwards_per_s", "value": 1000.0 / ms, "unit": "forwards/s",
+        "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": (1000.0 / ms) / (1000.0 / H100_PUBLISHED_MS), "dtype": "bf16", "data": "synthetic", "config": workload_config(1),
+        "e2e": {"value": 1000.0 / e2e_ms, "unit": "forwards/s", "ms_per_forward": e2e_ms,
+                "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host), "d2h_bytes_per_step": out_host.numel() * 2},
+        "clocks": clocks.summary(),
+        "note": "the unmodified reference (flash_vla.Pi0Inference, TileLang kernels) from baseline/_ref on this GPU",
+        "env": env_block(),
+    }
+    print(json.dumps(line))
+
+
 def workload_config(n_gpus: int, episodes: int = 1):
     return {"workload": "Pi0 full forward: 3 views 224x224x3, empty prompt (prefix 768), chunk 50, 10 Euler steps, "
                         "27 SigLIP + 18 prefix + 18 decoder layers, batch 1, one CUDA graph" +
@@ -431,6 +509,9 @@ def run_ours(args):
             value, _, cores, sample = time_cpu_oracle(3, 1, budget_s=30.0)
             line["cpu_baseline"] = {"value": value, "unit": "forwards/s", "cores": cores, "kind": "port", "sample": sample}
     line["env"] = env_block()
+    recorded = reference_gpu_recorded()
+    if recorded is not None and E == 1:
+        line["reference_gpu_recorded"] = recorded
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -588,7 +669,7 @@ def main():
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=30)
     p.add_argument("--warmup", type=int, default=3)
-    p.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    p.add_argument("--impl", choices=["ours", "reference", "reference-gpu"], default="ours")
     p.add_argument("--episodes", type=int, default=1,
                    help="independent episodes per GPU inside the graph (throughput profile; the default 1 is the headline workload)")
     p.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle leg (faster iteration)")
@@ -615,6 +696,8 @@ def main():
         run_sweep(args)
     elif args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu(args)
     else:
         run_ours(args)
 

@@ -4,15 +4,20 @@ This file is the parity oracle and the timed CPU baseline. It is never on the
 product path: only `tests/`, `__graft_entry__.smoke()` and the `cpu_baseline` /
 `--impl reference` legs of `bench.py` import it.
 
-PARITY UNPINNED BY THE REFERENCE: the reference ships no golden vectors, no
-known-answer tests and no CPU or PyTorch implementation of its pipeline; its
-kernels are TileLang programs that need an H100 and cannot run where this
-oracle is built. The oracle is therefore a line-by-line restatement of the
-reference's kernel sources (citations below are paths inside that project),
-cross-checked in `tests/test_oracle.py` against independent one-line torch
-expressions and, where the reference has CPU-runnable pieces (`rope_table`,
-`random_checkpoint`, its torch attention functions, its `pipeline.py`
-orchestration), against those pieces themselves via committed fixtures
+PARITY PINNED BY THE REFERENCE'S OWN GPU CODE: the reference ships no golden vectors, no
+known-answer tests and no CPU or PyTorch implementation of its pipeline, so the oracle is a
+line-by-line restatement of the reference's kernel sources (citations below are paths inside that
+project). What pins it is a fixture made by running the reference itself (its TileLang kernels, op
+table, pipeline and engine, from an installed copy, on a B200):
+`tests/golden/reference_gpu.pt`, produced by `tests/golden/make_reference_gpu_golden.py`.
+`tests/test_reference_gpu_parity.py` holds every op of this oracle's table, its whole forward and
+its one-decoder-step configuration to those outputs (every op inside the default elementwise bound).
+Only the reference's fused op table (its engine's default) was run: the three unfused decoder
+forms it replaces (three-kernel attention, separate norm-factor forms of the gated FFN and the
+action projection) are pinned through the fused forms only. Beside that, `tests/test_oracle.py`
+checks the ops against independent one-line torch expressions and, where the reference has
+CPU-runnable pieces (`rope_table`, `random_checkpoint`, its torch attention functions, its
+`pipeline.py` orchestration), against those pieces themselves via committed fixtures
 (`tests/golden/make_golden.py`).
 
 Every op has the positional signature of the reference's call-site wrapper of
