@@ -26,7 +26,9 @@ Reported:
   cpu_baseline the CPU fp32 oracle (a port: the reference has no CPU path) on this host's cores.
   env          GPU, driver, CUDA, torch, CPU model and core count of the run.
 
-`--impl reference` times that CPU oracle alone, as the reference arm. `--impl reference-gpu` runs the UNMODIFIED
+`--impl reference` times that CPU oracle alone, as the reference arm (and adds, as `reference_gpu`, what
+`--impl reference-gpu` measures in a child process when an installed copy of the reference is present).
+`--impl reference-gpu` runs the UNMODIFIED
 reference itself (its TileLang kernels and engine, from an installed copy under baseline/_ref, which is not part of
 this repository) on the GPU for the same metric and workload, and prints `unavailable` when that copy or TileLang
 is missing; the main line carries the figure recorded when the parity fixture was made (`reference_gpu_recorded`).
@@ -255,6 +257,19 @@ def run_reference(args):
         "note": "the reference has no CPU implementation; this is the CPU fp32 restatement (oracle/pi0_ref.py)",
         "env": env_block(),
     }
+    # Beside the CPU figure: the unmodified reference itself on this GPU, where an installed copy exists. It runs in
+    # a child process with a time limit, so that whatever happens to it the line above is still printed.
+    if (ROOT / "baseline" / "_ref" / "flash_vla").is_dir() and torch.cuda.is_available():
+        try:
+            child = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference-gpu", "--steps", str(min(args.steps, 20)),
+                                    "--warmup", "3"], capture_output=True, text=True, timeout=420)
+            rows = [r for r in child.stdout.splitlines() if r.startswith("{")]
+            got = json.loads(rows[-1]) if rows else {"unavailable": f"no output (exit code {child.returncode})"}
+        except subprocess.TimeoutExpired:
+            got = {"unavailable": "the reference's GPU run did not finish within 420 s"}
+        except Exception as e:
+            got = {"unavailable": f"{type(e).__name__}: {e}"}
+        line["reference_gpu"] = {k: got[k] for k in ("value", "unit", "ms_per_step", "e2e", "clocks", "note", "unavailable") if k in got}
     print(json.dumps(line))
 
 
