@@ -7,7 +7,7 @@ kernels, its op table, its pipeline and its engine, unmodified, from an installe
      of this repository. The reference pins tilelang 0.1.11 for Hopper; its kernels also compile and run with
      tilelang 0.1.9 on a B200, which is how the committed fixture was made; the fixture records both versions.)
 
-Parts (default: all): forward decoder_step ops.
+Parts (default: forward decoder_step ops): forward decoder_step ops prompts.
 
 What the fixture pins, all of it output of the reference's own GPU code on seeded inputs that the tests
 regenerate (`flash_vla_b200.synthetic`, `tests/reference_cases.py`):
@@ -17,6 +17,9 @@ regenerate (`flash_vla_b200.synthetic`, `tests/reference_cases.py`):
                     encoder_V the oracle fixtures hold. Only the reference's fused op table (its engine's default) is
                     run: with its unfused table the first attempt on a B200 made no progress for 17 minutes after the
                     kernels had compiled and was ended by its time limit, so that table stays off the GPU.
+  * prompts       - the same forward with a prompt of 48 and of 256 tokens (prefix 816 and 1024, the second being the
+                    reference's other benchmark workload, benchmarks/e2e.py:8-11): `language_embeds` are the rows
+                    `flash_vla_b200.synthetic.prompt_embeds` draws, as in the oracle's fixtures.
   * decoder_step  - the "one decoder diffusion step" configuration (prefix K/V ~ N(0,1) and N(0,0.1)) through the
                     reference's `transformer_decoder(steps=1)`, fused table.
   * ops           - every call-site wrapper of the reference's (fused) op table on the inputs of
@@ -50,7 +53,7 @@ from flash_vla.hardware.nvidia.h100.pi0.buffers import allocate_static_buffers a
 from flash_vla.hardware.nvidia.h100.pi0.ops import op_table as ref_op_table  # noqa: E402
 from flash_vla.runtime.cuda import ScratchPool as RefScratchPool  # noqa: E402
 
-from flash_vla_b200.synthetic import bench_inputs, decoder_step_inputs  # noqa: E402
+from flash_vla_b200.synthetic import bench_inputs, decoder_step_inputs, prompt_embeds  # noqa: E402
 
 bf16 = torch.bfloat16
 result = {"meta": {"tilelang": tilelang.__version__, "torch": str(torch.__version__), "gpu": torch.cuda.get_device_name(0),
@@ -109,6 +112,32 @@ def part_forward():
         result["forward_fused" if fused else "forward_unfused"] = entry
         save()
         print(f"forward fused={fused}: {time.time() - t0:.0f}s, |a| max {out.abs().max().item():.4g}, replays identical {entry['replay_identical']}", flush=True)
+        del engine
+        torch.cuda.empty_cache()
+
+
+def part_prompts():
+    images, state, noise = [t.cuda().to(bf16) for t in bench_inputs()]
+    for prompt_len in (48, 256):
+        t0 = time.time()
+        ck = dict(checkpoint())
+        ck["language_embeds"] = prompt_embeds(prompt_len)[1].cuda()
+        engine = flash_vla.Pi0Inference(ck, num_views=3, chunk_size=50)
+        out = engine.forward(images, state, noise).float().cpu().clone()
+        torch.cuda.synchronize()
+        entry = {"actions": out, **probes(engine.buffers)}
+        for _ in range(5):
+            engine.graph.replay()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(20):
+            engine.graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        entry["ms_per_replay"] = s.elapsed_time(e) / 20
+        result[f"forward_fused_p{prompt_len}"] = entry
+        save()
+        print(f"forward prompt {prompt_len}: {time.time() - t0:.0f}s, {entry['ms_per_replay']:.2f} ms per replay, |a| max {out.abs().max().item():.4g}", flush=True)
         del engine
         torch.cuda.empty_cache()
 
