@@ -305,9 +305,10 @@ def run_reference_gpu(args):
         import tilelang  # noqa: F401
     except Exception as e:      # the reference's only hard dependency besides torch
         return unavailable(f"tilelang cannot be imported: {type(e).__name__}")
-    os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
     sys.path.insert(0, str(ref_dir))
     import flash_vla
+    if args.sweep:
+        return run_reference_gpu_sweep(args)
     from flash_vla_b200.synthetic import bench_inputs
     torch.cuda.set_device(local_rank)
     ck = flash_vla.random_checkpoint(prompt_len=0, wscale=0.02, seed=0, device="cuda")
@@ -341,10 +342,20 @@ def run_reference_gpu(args):
         "e2e": {"value": 1000.0 / e2e_ms, "unit": "forwards/s", "ms_per_forward": e2e_ms,
                 "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host), "d2h_bytes_per_step": out_host.numel() * 2},
         "clocks": clocks.summary(),
-        "note": "the unmodified reference (flash_vla.Pi0Inference, TileLang kernels) from baseline/_ref on this GPU",
+        "note": "the unmodified reference (flash_vla.Pi0Inference, TileLang kernels) from baseline/_ref on this GPU; its two torch "
+                "attention functions " + ("run eagerly (TORCHDYNAMO_DISABLE is set)" if os.environ.get("TORCHDYNAMO_DISABLE") else "are compiled by torch.compile, as shipped"),
         "env": env_block(),
     }
     print(json.dumps(line))
+
+
+def run_reference_gpu_sweep(args):
+    """The isolated-kernel sweep of `sweep_rows` through the REFERENCE's op table (and its two torch attention
+    functions): the same call sites, shapes and cold-weight method, for a per-kernel comparison on this GPU."""
+    names = [args.sweep_only] if args.sweep_only else list(SWEEP)
+    rows = sweep_rows(names, args.sweep_layers, args.sweep_reps, reference=True)
+    print(json.dumps({"impl": "reference-gpu", "metric": "isolated_kernels", "kernels": rows,
+                      "note": "the reference's TileLang wrappers (fused table) and torch attention functions on this GPU, bf16 buffers throughout"}))
 
 
 def workload_config(n_gpus: int, episodes: int = 1):
@@ -554,15 +565,28 @@ SWEEP = {   # name: (M, K, N, gated, residual, layers cycled)
 }
 
 
-def sweep_rows(names, layers_cap: int, reps: int, fused: bool = True):
+def sweep_rows(names, layers_cap: int, reps: int, fused: bool = True, reference: bool = False):
     """Isolated kernel timings: bf16 weights ~ N(0, 0.02), activations ~ N(0, 1), fp32 accumulate, distinct
     weight copies cycled inside one CUDA graph so every launch streams its weights cold. Returns
     {name: {ms_per_launch, tflops, gbs, algorithmic_bytes, flops, frac_of_hbm, frac_of_bf16, ...}}."""
-    from flash_vla_b200 import op_table
-    from flash_vla_b200.hardware.nvidia.b200.pi0.backends.cuda import wrappers
-    from flash_vla_b200.hardware.nvidia.b200.pi0.buffers import rope_table
-    from flash_vla_b200.runtime.cuda import ScratchPool
-    ops, peaks, bf16 = op_table(fused), measured_peaks(), torch.bfloat16
+    if reference:       # the reference's own table (bf16 buffers only; attention for SigLIP and the prefix is plain torch there)
+        from types import SimpleNamespace
+        from flash_vla.hardware.nvidia.h100.pi0.backends.tilelang import wrappers
+        from flash_vla.hardware.nvidia.h100.pi0.backends.tilelang.kernels import attention as ref_attention
+        from flash_vla.hardware.nvidia.h100.pi0.buffers import rope_table
+        from flash_vla.hardware.nvidia.h100.pi0.ops import op_table
+        from flash_vla.runtime.cuda import ScratchPool
+        table = op_table(True)
+        ops = SimpleNamespace(**vars(table))
+        ops.encoder_attention = lambda Q, K, V, scale, out: out.view(-1, 2048).copy_(ref_attention.encoder_attention(Q, K, V, scale))
+        ops.vision_attention = lambda QKV, out: out.copy_(ref_attention.vision_attention(QKV))
+    else:
+        from flash_vla_b200 import op_table
+        from flash_vla_b200.hardware.nvidia.b200.pi0.backends.cuda import wrappers
+        from flash_vla_b200.hardware.nvidia.b200.pi0.buffers import rope_table
+        from flash_vla_b200.runtime.cuda import ScratchPool
+        ops = op_table(fused)
+    peaks, bf16 = measured_peaks(), torch.bfloat16
     g = torch.Generator(device="cuda").manual_seed(0)
     rows = {}
 
@@ -613,8 +637,10 @@ def sweep_rows(names, layers_cap: int, reps: int, fused: bool = True):
                     fn = lambda i: ops.vision_norm_qkv(x.view(3, 256, K), nw, nb, w[i], bias, out.view(3, 256, N), xn.view(3, 256, K))
                 elif name == "vis_up":
                     fn = lambda i: ops.vision_norm_ffn_up(x.view(3, 256, K), nw, nb, w[i], bias, out.view(3, 256, N), xn.view(3, 256, K))
-                else:       # vis_o, vis_down: out = x @ W + b + out, in place
-                    fn = lambda i: ops.vision_ffn_down_residual(x, w[i], bias, out, out)
+                elif name == "vis_o":     # out = x @ W + b + out, in place
+                    fn = lambda i: ops.vision_out_proj_residual(x.view(3, 256, K), w[i], bias, out.view(3, 256, N), out.view(3, 256, N))
+                else:
+                    fn = lambda i: ops.vision_ffn_down_residual(x.view(3, 256, K), w[i], bias, out.view(3, 256, N), out.view(3, 256, N))
                 ms = time_isolated_op(fn, layers, reps)
                 nbytes = K * N * 2 + M * K * 2 + M * N * 2 * (2 if residual else 1)
                 rows[name] = row(ms, 2.0 * M * K * N, nbytes, M=M, K=K, N=N)
@@ -622,8 +648,8 @@ def sweep_rows(names, layers_cap: int, reps: int, fused: bool = True):
                 torch.cuda.empty_cache()
                 continue
             x32 = torch.randn(M, K, device="cuda", generator=g)
-            f32_in = name in ("dec_gate", "dec_qkv")                   # the decoder's residual stream is fp32 ...
-            f32_out = name in ("dec_down", "dec_o")
+            f32_in = name in ("dec_gate", "dec_qkv") and not reference   # the decoder's residual stream is fp32 ...
+            f32_out = name in ("dec_down", "dec_o") and not reference
             x = x32 if f32_in else x32.to(bf16)
             if f32_in:                                                 # ... with a bf16 shadow its GEMMs read, as in the engine
                 shadow = torch.zeros(M, K, device="cuda", dtype=bf16)
@@ -633,7 +659,8 @@ def sweep_rows(names, layers_cap: int, reps: int, fused: bool = True):
                 wrappers.register_bf16_shadow(out, torch.zeros(M, N, device="cuda", dtype=bf16))
             xn = torch.zeros(M, K, device="cuda", dtype=bf16)
             if name == "dec_gate":
-                fn = lambda i: ops.decoder_norm_gated_ffn(x, w[2 * i], w[2 * i + 1], out, None)
+                nfg = torch.zeros(M, device="cuda", dtype=bf16) if reference else None
+                fn = lambda i: ops.decoder_norm_gated_ffn(x, w[2 * i], w[2 * i + 1], out, nfg)
             elif name == "enc_gate":
                 fn = lambda i: ops.encoder_norm_gated_ffn(x, w[2 * i], w[2 * i + 1], out, xn)
             elif name in ("dec_down", "dec_o"):
@@ -707,6 +734,8 @@ def main():
         print(json.dumps({"metric": "autotune", "plans": table["plans"], "report": table["report"]}))
     elif args.profile_pass:
         run_profile_pass()
+    elif args.sweep and args.impl == "reference-gpu":
+        run_reference_gpu(args)
     elif args.sweep:
         run_sweep(args)
     elif args.impl == "reference":
