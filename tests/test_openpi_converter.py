@@ -22,7 +22,7 @@ from flash_vla_b200.models.pi0 import openpi, weight_shapes
 
 
 def _sha(t: torch.Tensor) -> str:
-    return hashlib.sha256(t.contiguous().view(torch.uint8).numpy().tobytes()).hexdigest()
+    return hashlib.sha256(memoryview(t.contiguous().view(torch.uint8).numpy().reshape(-1))).hexdigest()      # hashed in place: no second copy of a 1.2 GB tensor
 
 
 def test_converter_reproduces_the_reference_converter_bit_for_bit():
