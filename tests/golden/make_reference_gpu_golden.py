@@ -7,7 +7,7 @@ kernels, its op table, its pipeline and its engine, unmodified, from an installe
      of this repository. The reference pins tilelang 0.1.11 for Hopper; its kernels also compile and run with
      tilelang 0.1.9 on a B200, which is how the committed fixture was made; the fixture records both versions.)
 
-Parts (default: forward decoder_step ops): forward decoder_step ops prompts.
+Parts (default: forward decoder_step ops): forward decoder_step ops prompts episodes.
 
 What the fixture pins, all of it output of the reference's own GPU code on seeded inputs that the tests
 regenerate (`flash_vla_b200.synthetic`, `tests/reference_cases.py`):
@@ -17,7 +17,9 @@ regenerate (`flash_vla_b200.synthetic`, `tests/reference_cases.py`):
                     encoder_V the oracle fixtures hold. Only the reference's fused op table (its engine's default) is
                     run: with its unfused table the first attempt on a B200 made no progress for 17 minutes after the
                     kernels had compiled and was ended by its time limit, so that table stays off the GPU.
-  * prompts       - the same forward with a prompt of 48 and of 256 tokens (prefix 816 and 1024, the second being the
+  * episodes      - the forward on the inputs of episodes 1 and 2 of the throughput profile (`bench_inputs(seed)`),
+                    final actions only.
+  * prompts       - the same forward with a prompt of 48, 49 and 256 tokens (prefix 816, 817 and 1024, the last being the
                     reference's other benchmark workload, benchmarks/e2e.py:8-11): `language_embeds` are the rows
                     `flash_vla_b200.synthetic.prompt_embeds` draws, as in the oracle's fixtures.
   * decoder_step  - the "one decoder diffusion step" configuration (prefix K/V ~ N(0,1) and N(0,0.1)) through the
@@ -63,6 +65,7 @@ if OUT.exists():
     result["meta"].update({"tilelang": tilelang.__version__, "gpu": torch.cuda.get_device_name(0)})
 
 _ck = None
+PROMPTS = tuple(int(x) for x in os.environ.get("REFERENCE_PROMPTS", "48,49,256").split(","))
 
 
 def save():
@@ -118,7 +121,7 @@ def part_forward():
 
 def part_prompts():
     images, state, noise = [t.cuda().to(bf16) for t in bench_inputs()]
-    for prompt_len in (48, 256):
+    for prompt_len in PROMPTS:
         t0 = time.time()
         ck = dict(checkpoint())
         ck["language_embeds"] = prompt_embeds(prompt_len)[1].cuda()
@@ -140,6 +143,19 @@ def part_prompts():
         print(f"forward prompt {prompt_len}: {time.time() - t0:.0f}s, {entry['ms_per_replay']:.2f} ms per replay, |a| max {out.abs().max().item():.4g}", flush=True)
         del engine
         torch.cuda.empty_cache()
+
+
+def part_episodes():
+    engine = flash_vla.Pi0Inference(checkpoint(), num_views=3, chunk_size=50)
+    for seed in (1, 2):
+        images, state, noise = [t.cuda().to(bf16) for t in bench_inputs(seed=seed)]
+        out = engine.forward(images, state, noise).float().cpu().clone()
+        torch.cuda.synchronize()
+        result[f"forward_fused_seed{seed}"] = {"actions": out}
+        save()
+        print(f"forward seed {seed}: |a| max {out.abs().max().item():.4g}", flush=True)
+    del engine
+    torch.cuda.empty_cache()
 
 
 def part_decoder_step():

@@ -52,9 +52,9 @@ def ref_forward(reference, prompt_len):
     return reference["forward_fused" if prompt_len == 0 else f"forward_fused_p{prompt_len}"]
 
 
-@pytest.mark.parametrize("prompt_len", [0, 48, 256])
+@pytest.mark.parametrize("prompt_len", [0, 48, 49, 256])
 def test_oracle_forward_matches_the_reference_engine(reference, prompt_len):
-    """The oracle's forward fixtures (fp32, `forward_p{0,48,256}.pt`) against the reference engine's forward on the
+    """The oracle's forward fixtures (fp32, `forward_p{0,48,49,256}.pt`; 49 gives the ragged prefix 817) against the reference engine's forward on the
     same checkpoint, prompt rows and inputs: final actions and the stage probes. Bounds are twice what was measured
     (actions 1.0 - 1.1e-2 of max |a|, rel-rms 0.6 - 0.8e-2; probes rel-rms 1.1 - 1.6e-2, max 1.5 - 2.9e-2 of max |ref|)."""
     ours, ref = torch.load(GOLDEN / f"forward_p{prompt_len}.pt"), ref_forward(reference, prompt_len)
@@ -70,6 +70,15 @@ def test_oracle_forward_matches_the_reference_engine(reference, prompt_len):
         rel_max = (e.max() / b.abs().max()).item()
         print(f"\n[p{prompt_len}] oracle vs reference engine, {name}: rel-rms {rel_rms:.4g}, max-abs {e.max().item():.4g} ({rel_max:.4g} of max |ref|), cos {cosine(a, b):.6f}")
         assert cosine(a, b) >= 0.9995 and rel_rms <= 3.2e-2 and rel_max <= 6e-2, name
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_oracle_forward_of_other_episodes_matches_the_reference_engine(reference, seed):
+    """The inputs of episodes 1 and 2 of the throughput profile through the reference engine, against the oracle."""
+    ours, ref = torch.load(GOLDEN / f"forward_p0_seed{seed}.pt")["actions"].float(), reference[f"forward_fused_seed{seed}"]["actions"].float()
+    e = (ours - ref).abs()
+    print(f"\n[seed {seed}] oracle vs reference engine: max-abs {e.max().item():.4g} ({(e.max() / ref.abs().max()).item():.4g} of max |a|), cos {cosine(ours, ref):.6f}")
+    assert cosine(ours, ref) >= 0.9995 and (e.max() / ref.abs().max()).item() <= 3e-2
 
 
 def test_reference_decoder_step_against_the_oracle(reference):
@@ -100,7 +109,7 @@ def test_cuda_op_matches_the_reference_kernel(reference, case, fused):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("prompt_len", [0, 256])
+@pytest.mark.parametrize("prompt_len", [0, 49, 256])
 def test_cuda_forward_matches_the_reference_engine(reference, full_checkpoint, prompt_len):
     """This engine's forward against the reference engine's on the same checkpoint and inputs; prompt 256 (prefix
     1024, 1 075 decoder keys) is the reference's second benchmark workload."""
